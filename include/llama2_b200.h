@@ -1,0 +1,188 @@
+/*
+ * llama2_b200.h -- C ABI of the B200 (sm_100a) per-token decode library.
+ *
+ * This is the boundary a Llama2.jl maintainer binds with `ccall`.  The reference has no
+ * FFI of its own; each entry point below names the reference function or type it
+ * replaces (paths relative to the reference project root).
+ *
+ * Conventions
+ *   - every function returns an int32 status (L2B_OK == 0); no exception, abort or exit
+ *     crosses the boundary; l2b_last_error_string() gives the text of the last failure
+ *     on the calling thread;
+ *   - token ids and positions are 0-BASED here (the Julia shim subtracts 1);
+ *   - pointers named host_* are host memory, borrowed for the duration of the call only
+ *     (they may point into a read-only mmap, as src/load_gguf.jl:160-185 produces);
+ *   - matrices are given exactly as the reference stores them: `in` contiguous weights
+ *     (or in/256 contiguous super-blocks) per output row, `out` rows
+ *     (src/inference.jl:32-47, src/matmul.jl:1);
+ *   - a session is used by one host thread at a time; different sessions may be used
+ *     concurrently;
+ *   - there is no CPU fallback: without a CUDA device every compute entry point returns
+ *     L2B_ERR_NO_DEVICE.
+ */
+#ifndef LLAMA2_B200_H
+#define LLAMA2_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct l2b_model l2b_model;     /* TransformerWeights + ModelConfig on the device */
+typedef struct l2b_session l2b_session; /* RunState: activations, KV cache, captured token graph */
+typedef struct l2b_matrix l2b_matrix;   /* one weight matrix resident on the device */
+
+enum l2b_status {
+    L2B_OK = 0,
+    L2B_ERR_BAD_ARG = 1,
+    L2B_ERR_UNSUPPORTED_TYPE = 2, /* src/load_gguf.jl:153,179 "tensor type ... not implemented" */
+    L2B_ERR_CUDA = 3,
+    L2B_ERR_NCCL = 4,
+    L2B_ERR_TIMEOUT = 5, /* a bounded device-side wait ran out */
+    L2B_ERR_OOM = 6,
+    L2B_ERR_STATE = 7, /* call order: e.g. forward before finalize */
+    L2B_ERR_NO_DEVICE = 8
+};
+
+/* GGML tensor types the reference can load (src/load_gguf.jl:26-42,135-154). */
+enum l2b_ggml_type { L2B_TYPE_F32 = 0, L2B_TYPE_Q4_K = 12, L2B_TYPE_Q5_K = 13, L2B_TYPE_Q6_K = 14 };
+
+/* Tensor roles = the fields of TransformerWeights / TransformerLayerWeights
+ * (src/inference.jl:27-48). */
+enum l2b_role {
+    L2B_ROLE_TOKEN_EMBEDDING = 0, /* token_embedding_table (dim, vocab) */
+    L2B_ROLE_RMS_ATT = 1,         /* rms_att_weight (dim,)  f32 */
+    L2B_ROLE_WQ = 2,
+    L2B_ROLE_WK = 3,
+    L2B_ROLE_WV = 4,
+    L2B_ROLE_WO = 5,
+    L2B_ROLE_RMS_FFN = 6, /* rms_ffn_weight (dim,) f32 */
+    L2B_ROLE_W1 = 7,      /* ffn gate */
+    L2B_ROLE_W2 = 8,      /* ffn down */
+    L2B_ROLE_W3 = 9,      /* ffn up */
+    L2B_ROLE_RMS_FINAL = 10,
+    L2B_ROLE_OUTPUT = 11 /* output_weight (dim, vocab) */
+};
+
+/* ModelConfig (src/inference.jl:1-11), field for field, followed by library options. */
+typedef struct l2b_config {
+    int32_t dim;
+    int32_t hidden_dim;
+    int32_t n_layers;
+    int32_t n_heads;
+    int32_t n_kv_heads;
+    int32_t vocab_size;
+    int32_t seq_len; /* the reference pins GGUF models to 512 (src/load_gguf.jl:237); any value is accepted here */
+    float rope_freq_base;
+    int32_t rope_is_neox;
+    /* ---- options with no counterpart in the reference ---- */
+    int32_t act_planes; /* int8 planes per activation value fed to the k-quant integer dot products:
+                           1 = one q8_K plane (8-bit activations), 2 = two (~15 bit), 3 = three (~23 bit,
+                           indistinguishable from the reference's f32 activations); 0 selects 3 */
+    int32_t device;     /* CUDA device ordinal; -1 = current device */
+    int32_t tp_size;    /* tensor-parallel world size (1 = single GPU) */
+    int32_t tp_rank;
+    int32_t reserved[7];
+} l2b_config;
+
+/* ---- library ------------------------------------------------------------------ */
+int32_t l2b_version(void);
+const char* l2b_last_error_string(void);
+const char* l2b_status_string(int32_t status);
+int32_t l2b_device_count(int32_t* count);
+
+/* ---- model: replaces the TransformerWeights the loaders build
+ *      (src/load_gguf.jl:229-253,291-315; src/load_karpathy.jl:36-56) ------------- */
+int32_t l2b_model_create(const l2b_config* config, l2b_model** model);
+/* Upload one tensor.  `layer` is 0-based and ignored for the three model-level roles.
+ * ggml_type is one of l2b_ggml_type; in_dim % 256 == 0 is required for k-quants
+ * (src/load_gguf.jl:141,145,149).  Norm gains are f32 with out_dim == 1. */
+int32_t l2b_model_upload_tensor(l2b_model* model, int32_t role, int32_t layer, int32_t ggml_type, const void* host_data,
+                                int64_t in_dim, int64_t out_dim);
+int32_t l2b_model_finalize(l2b_model* model); /* checks that every tensor is present and shapes agree */
+int32_t l2b_model_destroy(l2b_model* model);
+int32_t l2b_model_weight_bytes(const l2b_model* model, int64_t* bytes_per_token); /* bytes a decoded token streams from HBM */
+
+/* ---- session: replaces RunState / KVCache (src/inference.jl:62-100) ----------------
+ * `stream` is a cudaStream_t passed as a pointer (NULL = the library creates its own). */
+int32_t l2b_session_create(l2b_model* model, void* stream, l2b_session** session);
+int32_t l2b_session_reset(l2b_session* session); /* zero the KV cache, as a fresh RunState */
+int32_t l2b_session_destroy(l2b_session* session);
+
+/* transformer!(token, pos, config, s, weights) (src/inference.jl:222-315): one token
+ * through every layer; the KV cache advances; logits (vocab_size floats) are copied to
+ * host_logits when it is non-NULL. */
+int32_t l2b_forward(l2b_session* session, int32_t token, int32_t pos, float* host_logits);
+
+/* One iteration of the loop in `sample` (src/inference.jl:349-385): forward, then
+ * temperature == 0 ? argmax (first maximal index) : softmax(logits / temperature) sampled
+ * by inverse CDF with the caller's uniform variate in [0,1) (StatsBase.wsample draws its
+ * own from Julia's global RNG; that stream cannot be reproduced outside Julia). */
+int32_t l2b_decode_next(l2b_session* session, int32_t token, int32_t pos, float temperature, double uniform, int32_t* next_token);
+
+/* The whole loop of `sample` on the device: positions 0 .. n_positions-1, teacher-forced
+ * while inside the prompt, then greedy (temperature 0) or sampled with uniforms drawn from
+ * a counter-based generator seeded by `seed`.  host_out_tokens[p] = token chosen after
+ * position p.  No stop on BOS/EOS (stop_on_special_token=false); the shim truncates.
+ * device_ms (optional) = CUDA-event time of the loop. */
+int32_t l2b_generate(l2b_session* session, const int32_t* host_prompt, int32_t n_prompt, int32_t n_positions,
+                     float temperature, uint64_t seed, int32_t* host_out_tokens, float* device_ms);
+
+/* Copy the logits of the most recent position to the host (state.logits). */
+int32_t l2b_session_logits(l2b_session* session, float* host_logits);
+/* Copy an activation buffer of the most recent forward for stage-wise checks:
+ * which: 0 = x (residual stream after the last layer, before the final norm is applied in place),
+ *        2 = q (after RoPE, last layer), 5 = hb (SwiGLU output, last layer).  Returns element count in *n. */
+int32_t l2b_session_read(l2b_session* session, int32_t which, float* host_out, int64_t capacity, int64_t* n);
+/* Device time (ms, CUDA events on the session stream) of the most recent forward/decode/generate call. */
+int32_t l2b_session_last_device_ms(l2b_session* session, float* ms);
+/* Number of kernel launches the captured token graph contains. */
+int32_t l2b_session_kernels_per_token(l2b_session* session, int32_t* n);
+
+/* ---- isolated operators (host buffers in, host buffers out) ------------------------ */
+/* dequantize! (src/kquants.jl:44-47,70-125,186-251,322-363); bit-exact. n_elems % 256 == 0 for k-quants. */
+int32_t l2b_dequantize(int32_t ggml_type, const void* host_blocks, int64_t n_elems, float* host_out);
+/* Quantise f32 activations to `planes` int8 planes in the layout of block_q8_K (src/kquants.jl:38-42):
+ * host_q[p][n] int8, host_d[p][n/256] f32 (scale of plane p), host_sums[n/16] f32 = sums of the represented
+ * values over groups of 16 (the role of bsums).  The reference declares block_q8_K but has no quantiser. */
+int32_t l2b_quantize_q8k(const float* host_x, int64_t n, int32_t planes, int8_t* host_q, float* host_d, float* host_sums);
+/* matmul!(y, A, x) (src/matmul.jl:3-23) for ncols activation columns: x is [ncols][in], y is [ncols][out]. */
+int32_t l2b_matvec(int32_t ggml_type, const void* host_W, int64_t in_dim, int64_t out_dim, const float* host_x,
+                   int32_t ncols, float* host_y, int32_t act_planes);
+/* rmsnorm!(o, x, w) (src/inference.jl:102-110). */
+int32_t l2b_rmsnorm(float* host_o, const float* host_x, const float* host_w, int64_t n);
+/* rope!(x, pos, config) (src/inference.jl:112-167); x is [n_heads][head_size], rotated in place. */
+int32_t l2b_rope(float* host_x, int32_t head_size, int32_t n_heads, int32_t pos, float freq_base, int32_t is_neox);
+/* attention_weights! + scale + softmax! + combine_values! (src/inference.jl:263-278) for one layer:
+ * q [n_heads][hs]; k, v [n_pos][n_kv_heads][hs] (position-major); out [n_heads][hs]. */
+int32_t l2b_attention(float* host_out, const float* host_q, const float* host_k, const float* host_v, int32_t n_pos,
+                      int32_t n_heads, int32_t n_kv_heads, int32_t head_size);
+/* hb = silu(hb) .* hb2 (src/inference.jl:295-299); written to host_hb. */
+int32_t l2b_swiglu(float* host_hb, const float* host_hb2, int64_t n);
+/* argmax(logits) (src/inference.jl:360), first maximal index, 0-based. */
+int32_t l2b_argmax(const float* host_logits, int64_t n, int32_t* index);
+/* logits ./= T; softmax!; wsample (src/inference.jl:361-368) with a supplied uniform in [0,1). */
+int32_t l2b_sample_temperature(const float* host_logits, int64_t n, float temperature, double uniform, int32_t* index);
+
+/* ---- resident matrices (for measurement with inputs already in HBM) ----------------- */
+/* Upload `copies` identical copies of one matrix (copies > 1 lets a benchmark rotate through more than the L2). */
+int32_t l2b_matrix_create(int32_t ggml_type, const void* host_W, int64_t in_dim, int64_t out_dim, int32_t copies, l2b_matrix** m);
+int32_t l2b_matrix_destroy(l2b_matrix* m);
+/* y = A' x on device pointers (x: [in] f32, y: [out] f32), copy index `copy`, on `stream` (cudaStream_t; NULL = default). */
+int32_t l2b_matrix_matvec_device(l2b_matrix* m, int32_t copy, const float* dev_x, float* dev_y, int32_t act_planes, void* stream);
+/* The same through host buffers (x: [ncols][in], y: [ncols][out]). */
+int32_t l2b_matrix_matvec(l2b_matrix* m, const float* host_x, int32_t ncols, float* host_y, int32_t act_planes);
+
+/* ---- seeded synthetic data (counter-based, integer-only, identical on every machine) -- */
+/* n f32 values ~ N(0, std^2) (Irwin-Hall of 12 16-bit uniforms), or the constant `std` when constant != 0. */
+int32_t l2b_synth_f32(float* host_out, int64_t n, uint64_t seed, float std, int32_t constant);
+/* n_blocks k-quant super-blocks: fp16 d, dmin = |N(0, 0.01^2)|, every other byte uniform random. */
+int32_t l2b_synth_kquant(int32_t ggml_type, void* host_out, int64_t n_blocks, uint64_t seed);
+/* n token ids uniform in [lo, hi). */
+int32_t l2b_synth_tokens(int32_t* host_out, int64_t n, uint64_t seed, int32_t lo, int32_t hi);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* LLAMA2_B200_H */

@@ -1,0 +1,30 @@
+"""In-tree build of the CUDA library for sm_100a (cross-compiles without a GPU)."""
+import os
+import subprocess
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+SOURCES = ["csrc/api.cu", "csrc/synth.cpp"]
+HEADERS = ["csrc/common.cuh", "csrc/kquants.cuh", "csrc/fused_matvec.cuh", "csrc/attention.cuh", "csrc/sampling.cuh",
+           "csrc/small_ops.cuh", "../include/llama2_b200.h"]
+OUTPUT = os.path.join(_HERE, "libllama2_b200.so")
+NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC", "-shared"]
+
+
+def needs_build():
+    if not os.path.exists(OUTPUT):
+        return True
+    t = os.path.getmtime(OUTPUT)
+    return any(os.path.getmtime(os.path.join(_HERE, f)) > t for f in SOURCES + HEADERS)
+
+
+def build(force=False, verbose=False):
+    if not force and not needs_build():
+        return OUTPUT
+    nvcc = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
+    cmd = [nvcc] + NVCC_FLAGS + (["-Xptxas", "-v"] if verbose else []) + ["-o", OUTPUT] + [os.path.join(_HERE, s) for s in SOURCES]
+    subprocess.run(cmd, check=True)
+    return OUTPUT
+
+
+if __name__ == "__main__":
+    print(build(force=True, verbose=True))

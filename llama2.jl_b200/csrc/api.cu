@@ -1,0 +1,1180 @@
+// C ABI of the library (see include/llama2_b200.h): model / session objects, the captured
+// per-token CUDA graph, and the isolated-operator entry points.
+#include "../../include/llama2_b200.h"
+
+#include <cmath>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <mutex>
+#include <string>
+#include <vector>
+
+#include "attention.cuh"
+#include "fused_matvec.cuh"
+#include "sampling.cuh"
+#include "small_ops.cuh"
+
+using namespace l2b;
+
+// ---------------------------------------------------------------------------------------------
+// errors
+// ---------------------------------------------------------------------------------------------
+static thread_local std::string g_last_error;
+
+static int32_t fail(int32_t code, const std::string& msg) {
+    g_last_error = msg;
+    return code;
+}
+
+#define CU(call)                                                                                         \
+    do {                                                                                                 \
+        cudaError_t e_ = (call);                                                                         \
+        if (e_ != cudaSuccess) {                                                                         \
+            (void)cudaGetLastError();                                                                    \
+            return fail(e_ == cudaErrorMemoryAllocation ? L2B_ERR_OOM : L2B_ERR_CUDA,                    \
+                        std::string(#call) + ": " + cudaGetErrorString(e_) + " (" + __FILE__ + ":" + std::to_string(__LINE__) + ")"); \
+        }                                                                                                \
+    } while (0)
+
+#define L2B_TRY(expr)              \
+    do {                           \
+        int32_t s_ = (expr);       \
+        if (s_ != L2B_OK) return s_; \
+    } while (0)
+
+static int32_t require_device() {
+    int n = 0;
+    cudaError_t e = cudaGetDeviceCount(&n);
+    if (e != cudaSuccess || n == 0) {
+        (void)cudaGetLastError();
+        return fail(L2B_ERR_NO_DEVICE, "no CUDA device is visible; this library has no CPU path");
+    }
+    return L2B_OK;
+}
+
+// ---------------------------------------------------------------------------------------------
+// device matrices
+// ---------------------------------------------------------------------------------------------
+struct DevMatrix {
+    int type = -1;
+    int64_t in = 0, out = 0;
+    uint8_t* data = nullptr;  // f32 rows, or block records
+    __half* d6 = nullptr;     // q6_K super-block scales
+    int64_t file_bytes = 0;   // bytes in the stored (file) format
+    bool present() const { return data != nullptr; }
+};
+
+static bool type_supported(int t) { return t == T_F32 || t == T_Q4_K || t == T_Q5_K || t == T_Q6_K; }
+
+static void free_matrix(DevMatrix& m) {
+    if (m.data) cudaFree(m.data);
+    if (m.d6) cudaFree(m.d6);
+    m = DevMatrix();
+}
+
+// Copy one matrix to the device (repacking q6_K).  `rows` x `in` weights.
+static int32_t upload_matrix(DevMatrix& m, int type, const void* host, int64_t in, int64_t out, cudaStream_t st) {
+    if (!type_supported(type)) return fail(L2B_ERR_UNSUPPORTED_TYPE, "tensor type " + std::to_string(type) + " not implemented");
+    if (!host || in <= 0 || out <= 0) return fail(L2B_ERR_BAD_ARG, "upload: null pointer or empty shape");
+    if (type != T_F32 && in % QK_K != 0) return fail(L2B_ERR_BAD_ARG, "k-quant tensors need in_dim % 256 == 0");
+    if (type == T_F32 && in % 8 != 0 && out > 1) return fail(L2B_ERR_BAD_ARG, "f32 matrices need in_dim % 8 == 0");
+    free_matrix(m);
+    m.type = type;
+    m.in = in;
+    m.out = out;
+    if (type == T_F32) {
+        m.file_bytes = in * out * 4;
+        CU(cudaMalloc(&m.data, (size_t)m.file_bytes));
+        CU(cudaMemcpyAsync(m.data, host, (size_t)m.file_bytes, cudaMemcpyHostToDevice, st));
+        CU(cudaStreamSynchronize(st));
+        return L2B_OK;
+    }
+    const int64_t nblocks = (in / QK_K) * out;
+    m.file_bytes = nblocks * file_block_bytes(type);
+    if (type != T_Q6_K) {
+        CU(cudaMalloc(&m.data, (size_t)m.file_bytes));
+        CU(cudaMemcpyAsync(m.data, host, (size_t)m.file_bytes, cudaMemcpyHostToDevice, st));
+        CU(cudaStreamSynchronize(st));
+        return L2B_OK;
+    }
+    uint8_t* raw = nullptr;
+    CU(cudaMalloc(&raw, (size_t)m.file_bytes));
+    cudaError_t e = cudaMalloc(&m.data, (size_t)nblocks * 208);
+    if (e == cudaSuccess) e = cudaMalloc(&m.d6, (size_t)nblocks * sizeof(__half));
+    if (e == cudaSuccess) e = cudaMemcpyAsync(raw, host, (size_t)m.file_bytes, cudaMemcpyHostToDevice, st);
+    if (e == cudaSuccess) {
+        repack_q6k_kernel<<<1184, 256, 0, st>>>(raw, m.data, m.d6, nblocks);
+        e = cudaGetLastError();
+    }
+    if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+    cudaFree(raw);
+    CU(e);
+    return L2B_OK;
+}
+
+// ---------------------------------------------------------------------------------------------
+// kernel launch helpers
+// ---------------------------------------------------------------------------------------------
+struct DeviceInfo {
+    int sms = 148;
+    int max_smem_optin = 227 * 1024;
+};
+
+static int32_t query_device(DeviceInfo& di) {
+    int dev = 0;
+    CU(cudaGetDevice(&dev));
+    CU(cudaDeviceGetAttribute(&di.sms, cudaDevAttrMultiProcessorCount, dev));
+    CU(cudaDeviceGetAttribute(&di.max_smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev));
+    return L2B_OK;
+}
+
+template <typename Kernel, typename Params>
+static cudaError_t launch_kernel(Kernel k, dim3 grid, dim3 block, size_t smem, cudaStream_t st, bool pdl, const Params& prm) {
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, k, prm);
+}
+
+static long env_long(const char* name, long dflt) {
+    const char* v = getenv(name);
+    return v && *v ? atol(v) : dflt;
+}
+
+// A fused matrix-vector launch, fully planned on the host.
+struct MvLaunch {
+    MvParams p;
+    bool kq = true;
+    int planes = 3;
+    int grid = 0, warps = 0;
+    size_t smem = 0;
+};
+
+static int choose_lgG(int nb) {
+    int best = 1;
+    double best_waste = 1e9;
+    for (int lg = 1; lg <= 5; ++lg) {
+        const int G = 1 << lg;
+        const int its = (nb + G - 1) / G;
+        const double waste = (double)(its * G) / nb;
+        if (waste < best_waste - 1e-9 || (fabs(waste - best_waste) < 1e-9 && lg > best)) {
+            best_waste = waste;
+            best = lg;
+        }
+    }
+    return best;
+}
+
+// Decide grid, warps per block, ring depth and shared memory for a launch whose segments, n_in,
+// prologue and epilogue fields are already filled in.
+static int32_t plan_matvec(MvLaunch& L, const DeviceInfo& di) {
+    MvParams& p = L.p;
+    L.kq = p.seg[0].type != T_F32;
+    for (int s = 0; s < p.nseg; ++s)
+        if ((p.seg[s].type != T_F32) != L.kq) return fail(L2B_ERR_UNSUPPORTED_TYPE, "f32 and k-quant matrices cannot share one launch");
+    p.planes = L.planes;
+    L.grid = di.sms;
+    if (!L.kq) {
+        int steps = 0;
+        for (int s = 0; s < p.nseg; ++s) steps += p.seg[s].npairs;
+        p.lgG = 5;
+        p.nstages = 0;
+        int w = (steps + L.grid - 1) / L.grid;
+        L.warps = std::max(4, std::min(MV_MAX_WARPS, w));
+        L.smem = mv_smem_layout(p.n_in, 1, false, L.warps, 0, 0).total;
+        return L2B_OK;
+    }
+    const int nb = p.n_in / QK_K;
+    p.lgG = choose_lgG(nb);
+    const int G = 1 << p.lgG, PW = 32 >> p.lgG, nit = (nb + G - 1) / G;
+    int steps = 0, max_bb = 0;
+    for (int s = 0; s < p.nseg; ++s) {
+        steps += (p.seg[s].npairs + PW - 1) / PW;
+        max_bb = std::max(max_bb, dev_block_bytes(p.seg[s].type));
+    }
+    const int slot = 64 * max_bb;
+    const int base = mv_smem_layout(p.n_in, L.planes, true, 0, 0, max_bb).total;
+    const long cap = env_long("L2B_MV_SMEM_KB", 112) * 1024;
+    long ring_cap = cap - base;
+    const long ring_min = env_long("L2B_MV_RING_MIN_KB", 56) * 1024;
+    if (ring_cap < ring_min) ring_cap = ring_min;
+    if (base + ring_cap > di.max_smem_optin) ring_cap = di.max_smem_optin - base;
+    int slots = (int)(ring_cap / slot);
+    if (slots < 1) return fail(L2B_ERR_BAD_ARG, "input dimension too large for the activation planes to fit in shared memory");
+    const int steps_per_block = (steps + L.grid - 1) / L.grid;
+    const long stages_per_block = (long)steps_per_block * nit;
+    // One slot per warp, or two when a block has enough stages for every warp to overlap a copy with
+    // its arithmetic.  At least four warps so the prologue has hands.
+    const int warp_cap = (int)std::min<long>(MV_MAX_WARPS, env_long("L2B_MV_WARPS", MV_MAX_WARPS));
+    int nst = 1;
+    int warps = std::min(warp_cap, std::min(slots, std::max(steps_per_block, 4)));
+    {
+        const int w2 = std::min(warp_cap, std::min(slots / 2, std::max(steps_per_block, 4)));
+        if (w2 >= 4 && stages_per_block >= 2L * w2) {
+            warps = w2;
+            nst = 2;
+        }
+    }
+    const long force_nst = env_long("L2B_MV_STAGES", 0);
+    if (force_nst > 0) {
+        nst = (int)std::min<long>(force_nst, MV_MAX_STAGES);
+        warps = std::max(1, std::min(warp_cap, std::min(slots / nst, std::max(steps_per_block, 4))));
+    }
+    if (warps < 1) warps = 1;
+    L.warps = warps;
+    p.nstages = nst;
+    L.smem = mv_smem_layout(p.n_in, L.planes, true, warps, nst, max_bb).total;
+    if ((long)L.smem > di.max_smem_optin) return fail(L2B_ERR_BAD_ARG, "shared memory plan exceeds the device limit");
+    return L2B_OK;
+}
+
+static std::once_flag g_attr_once;
+static cudaError_t g_attr_err = cudaSuccess;
+static void set_kernel_attrs() {
+    std::call_once(g_attr_once, [] {
+        int dev = 0, optin = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev);
+        auto set = [&](const void* f) {
+            cudaError_t e = cudaFuncSetAttribute(f, cudaFuncAttributeMaxDynamicSharedMemorySize, optin);
+            if (e != cudaSuccess) g_attr_err = e;
+        };
+        set((const void*)fused_matvec_kernel<true, 1>);
+        set((const void*)fused_matvec_kernel<true, 2>);
+        set((const void*)fused_matvec_kernel<true, 3>);
+        set((const void*)fused_matvec_kernel<false, 1>);
+        set((const void*)export_activation_kernel<true, 1>);
+        set((const void*)export_activation_kernel<true, 2>);
+        set((const void*)export_activation_kernel<true, 3>);
+        set((const void*)export_activation_kernel<false, 1>);
+    });
+}
+
+static cudaError_t launch_matvec(const MvLaunch& L, cudaStream_t st, bool pdl) {
+    const dim3 grid(L.grid), block(L.warps * 32);
+    if (!L.kq) return launch_kernel(fused_matvec_kernel<false, 1>, grid, block, L.smem, st, pdl, L.p);
+    switch (L.planes) {
+        case 1: return launch_kernel(fused_matvec_kernel<true, 1>, grid, block, L.smem, st, pdl, L.p);
+        case 2: return launch_kernel(fused_matvec_kernel<true, 2>, grid, block, L.smem, st, pdl, L.p);
+        default: return launch_kernel(fused_matvec_kernel<true, 3>, grid, block, L.smem, st, pdl, L.p);
+    }
+}
+
+static MvSegment make_segment(const DevMatrix& m, int pair_mode, int epi, float* out, int head_size) {
+    MvSegment s;
+    memset(&s, 0, sizeof(s));
+    s.w = m.data;
+    s.d6 = m.d6;
+    s.type = m.type;
+    s.npairs = (int)(m.out / 2);
+    s.pair_mode = pair_mode;
+    s.epi = epi;
+    s.out = out;
+    s.head_size = head_size;
+    return s;
+}
+
+static cudaError_t launch_attention(const AttnParams& a, int gq, cudaStream_t st, bool pdl) {
+    const dim3 grid((a.n_heads / gq) * a.nsplit), block(ATTN_WARPS * 32);
+    switch (gq) {
+        case 8: return launch_kernel(attention_split_kernel<8>, grid, block, 0, st, pdl, a);
+        case 4: return launch_kernel(attention_split_kernel<4>, grid, block, 0, st, pdl, a);
+        case 2: return launch_kernel(attention_split_kernel<2>, grid, block, 0, st, pdl, a);
+        default: return launch_kernel(attention_split_kernel<1>, grid, block, 0, st, pdl, a);
+    }
+}
+static int choose_gq(int n_heads, int n_kv) {
+    const int r = n_heads / n_kv;
+    return (r == 8 || r == 4 || r == 2) ? r : 1;
+}
+
+// cos/sin of the iterated f32 angle, exactly as rope_normal!/rope_neox! advance it
+// (src/inference.jl:119-127, 140-153): theta_scale = base^(-1/(hs/2)) in f32 (Julia evaluates the
+// f32 power in f64 and rounds once), theta_0 = Float32(pos), theta *= theta_scale; cis(theta) is
+// evaluated in f64 and rounded.
+static void rope_table_host(std::vector<float>& cs, int seq_len, int hs, float base) {
+    const int h2 = hs / 2;
+    cs.resize((size_t)seq_len * h2 * 2);
+    const float e = -(1.0f / (float)h2);
+    const float scale = (float)std::pow((double)base, (double)e);
+    for (int pos = 0; pos < seq_len; ++pos) {
+        float theta = 1.0f * (float)pos;
+        for (int i = 0; i < h2; ++i) {
+            cs[((size_t)pos * h2 + i) * 2] = (float)std::cos((double)theta);
+            cs[((size_t)pos * h2 + i) * 2 + 1] = (float)std::sin((double)theta);
+            theta *= scale;
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// model
+// ---------------------------------------------------------------------------------------------
+struct LayerW {
+    float* rms_att = nullptr;
+    float* rms_ffn = nullptr;
+    DevMatrix wq, wk, wv, wo, w1, w2, w3;
+};
+
+struct l2b_model {
+    l2b_config cfg;
+    int device = 0;
+    DevMatrix tok_emb, output;
+    float* rms_final = nullptr;
+    std::vector<LayerW> layers;
+    bool finalized = false;
+    int planes = 3;
+};
+
+struct l2b_session {
+    l2b_model* model = nullptr;
+    cudaStream_t stream = nullptr;
+    bool own_stream = false;
+    DeviceInfo di;
+    // activations
+    float *x = nullptr, *q = nullptr, *hb = nullptr, *logits = nullptr;
+    float *kc = nullptr, *vc = nullptr;  // [layer][kv_head][seq_len][hs]
+    float *part_m = nullptr, *part_l = nullptr, *part_acc = nullptr;
+    float* amax_val = nullptr;
+    int* amax_idx = nullptr;
+    float* rope_cs = nullptr;
+    Control* ctl = nullptr;
+    int* status = nullptr;
+    int* prompt = nullptr;
+    int* out_tokens = nullptr;
+    int* next_token = nullptr;
+    int nsplit = 1, gq = 1;
+    // host pinned mirrors
+    Control* h_ctl = nullptr;
+    int* h_small = nullptr;  // [0] next token, [1] status
+    cudaGraphExec_t graph = nullptr;
+    int kernels_per_token = 0;
+    cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+    float last_ms = 0.f;
+};
+
+static size_t kv_layer_elems(const l2b_config& c) { return (size_t)c.n_kv_heads * c.seq_len * (c.dim / c.n_heads); }
+
+extern "C" int32_t l2b_version(void) { return 100; }
+extern "C" const char* l2b_last_error_string(void) { return g_last_error.c_str(); }
+extern "C" const char* l2b_status_string(int32_t s) {
+    switch (s) {
+        case L2B_OK: return "ok";
+        case L2B_ERR_BAD_ARG: return "bad argument";
+        case L2B_ERR_UNSUPPORTED_TYPE: return "unsupported tensor type";
+        case L2B_ERR_CUDA: return "CUDA error";
+        case L2B_ERR_NCCL: return "NCCL error";
+        case L2B_ERR_TIMEOUT: return "device-side wait timed out";
+        case L2B_ERR_OOM: return "out of device memory";
+        case L2B_ERR_STATE: return "call made in the wrong state";
+        case L2B_ERR_NO_DEVICE: return "no CUDA device";
+        default: return "unknown status";
+    }
+}
+extern "C" int32_t l2b_device_count(int32_t* count) {
+    if (!count) return fail(L2B_ERR_BAD_ARG, "count is null");
+    int n = 0;
+    if (cudaGetDeviceCount(&n) != cudaSuccess) {
+        (void)cudaGetLastError();
+        n = 0;
+    }
+    *count = n;
+    return L2B_OK;
+}
+
+extern "C" int32_t l2b_model_create(const l2b_config* c, l2b_model** out) {
+    if (!c || !out) return fail(L2B_ERR_BAD_ARG, "null argument");
+    *out = nullptr;
+    if (c->dim <= 0 || c->hidden_dim <= 0 || c->n_layers <= 0 || c->n_heads <= 0 || c->n_kv_heads <= 0 || c->vocab_size <= 0 || c->seq_len <= 0)
+        return fail(L2B_ERR_BAD_ARG, "ModelConfig fields must be positive");
+    if (c->dim % c->n_heads != 0 || c->n_heads % c->n_kv_heads != 0) return fail(L2B_ERR_BAD_ARG, "dim % n_heads and n_heads % n_kv_heads must be 0");
+    const int hs = c->dim / c->n_heads;
+    if (hs % 8 != 0 || hs > 128) return fail(L2B_ERR_BAD_ARG, "head size must be a multiple of 8 and at most 128");
+    if (c->dim % 8 != 0 || c->hidden_dim % 8 != 0 || c->vocab_size % 2 != 0) return fail(L2B_ERR_BAD_ARG, "dim, hidden_dim must be multiples of 8 and vocab_size even");
+    if (c->act_planes < 0 || c->act_planes > 3) return fail(L2B_ERR_BAD_ARG, "act_planes must be 0..3");
+    if (c->tp_size > 1) return fail(L2B_ERR_BAD_ARG, "tensor parallelism is not available in this build");
+    L2B_TRY(require_device());
+    l2b_model* m = new l2b_model();
+    m->cfg = *c;
+    m->planes = c->act_planes == 0 ? 3 : c->act_planes;
+    if (c->device >= 0) {
+        cudaError_t e = cudaSetDevice(c->device);
+        if (e != cudaSuccess) {
+            delete m;
+            return fail(L2B_ERR_CUDA, std::string("cudaSetDevice: ") + cudaGetErrorString(e));
+        }
+    }
+    cudaGetDevice(&m->device);
+    m->layers.resize(c->n_layers);
+    *out = m;
+    return L2B_OK;
+}
+
+static int32_t upload_vector(float*& dst, const void* host, int64_t n) {
+    if (dst) cudaFree(dst), dst = nullptr;
+    CU(cudaMalloc(&dst, (size_t)n * 4));
+    CU(cudaMemcpy(dst, host, (size_t)n * 4, cudaMemcpyHostToDevice));
+    return L2B_OK;
+}
+
+extern "C" int32_t l2b_model_upload_tensor(l2b_model* m, int32_t role, int32_t layer, int32_t type, const void* host, int64_t in_dim, int64_t out_dim) {
+    if (!m || !host) return fail(L2B_ERR_BAD_ARG, "null argument");
+    if (m->finalized) return fail(L2B_ERR_STATE, "model already finalized");
+    CU(cudaSetDevice(m->device));
+    const l2b_config& c = m->cfg;
+    const int hs = c.dim / c.n_heads, kv_dim = hs * c.n_kv_heads;
+    const bool per_layer = !(role == L2B_ROLE_TOKEN_EMBEDDING || role == L2B_ROLE_RMS_FINAL || role == L2B_ROLE_OUTPUT);
+    if (per_layer && (layer < 0 || layer >= c.n_layers)) return fail(L2B_ERR_BAD_ARG, "layer index out of range");
+    auto want = [&](int64_t in, int64_t out) -> int32_t {
+        if (in_dim != in || out_dim != out)
+            return fail(L2B_ERR_BAD_ARG, "tensor shape (" + std::to_string(in_dim) + "," + std::to_string(out_dim) + ") does not match the config (" +
+                                             std::to_string(in) + "," + std::to_string(out) + ")");
+        return L2B_OK;
+    };
+    auto norm = [&](float*& dst) -> int32_t {
+        if (type != L2B_TYPE_F32) return fail(L2B_ERR_UNSUPPORTED_TYPE, "norm gains must be f32");
+        if (in_dim * out_dim != c.dim) return fail(L2B_ERR_BAD_ARG, "norm gain length must equal dim");
+        return upload_vector(dst, host, c.dim);
+    };
+    LayerW* lw = per_layer ? &m->layers[layer] : nullptr;
+    switch (role) {
+        case L2B_ROLE_TOKEN_EMBEDDING: L2B_TRY(want(c.dim, c.vocab_size)); return upload_matrix(m->tok_emb, type, host, in_dim, out_dim, 0);
+        case L2B_ROLE_OUTPUT: L2B_TRY(want(c.dim, c.vocab_size)); return upload_matrix(m->output, type, host, in_dim, out_dim, 0);
+        case L2B_ROLE_RMS_FINAL: return norm(m->rms_final);
+        case L2B_ROLE_RMS_ATT: return norm(lw->rms_att);
+        case L2B_ROLE_RMS_FFN: return norm(lw->rms_ffn);
+        case L2B_ROLE_WQ: L2B_TRY(want(c.dim, c.dim)); return upload_matrix(lw->wq, type, host, in_dim, out_dim, 0);
+        case L2B_ROLE_WK: L2B_TRY(want(c.dim, kv_dim)); return upload_matrix(lw->wk, type, host, in_dim, out_dim, 0);
+        case L2B_ROLE_WV: L2B_TRY(want(c.dim, kv_dim)); return upload_matrix(lw->wv, type, host, in_dim, out_dim, 0);
+        case L2B_ROLE_WO: L2B_TRY(want(c.dim, c.dim)); return upload_matrix(lw->wo, type, host, in_dim, out_dim, 0);
+        case L2B_ROLE_W1: L2B_TRY(want(c.dim, c.hidden_dim)); return upload_matrix(lw->w1, type, host, in_dim, out_dim, 0);
+        case L2B_ROLE_W3: L2B_TRY(want(c.dim, c.hidden_dim)); return upload_matrix(lw->w3, type, host, in_dim, out_dim, 0);
+        case L2B_ROLE_W2: L2B_TRY(want(c.hidden_dim, c.dim)); return upload_matrix(lw->w2, type, host, in_dim, out_dim, 0);
+        default: return fail(L2B_ERR_BAD_ARG, "unknown tensor role " + std::to_string(role));
+    }
+}
+
+extern "C" int32_t l2b_model_finalize(l2b_model* m) {
+    if (!m) return fail(L2B_ERR_BAD_ARG, "null model");
+    if (!m->tok_emb.present() || !m->output.present() || !m->rms_final) return fail(L2B_ERR_STATE, "token embedding, output weight or final norm missing");
+    for (int l = 0; l < m->cfg.n_layers; ++l) {
+        const LayerW& w = m->layers[l];
+        if (!w.rms_att || !w.rms_ffn || !w.wq.present() || !w.wk.present() || !w.wv.present() || !w.wo.present() || !w.w1.present() ||
+            !w.w2.present() || !w.w3.present())
+            return fail(L2B_ERR_STATE, "missing blk." + std::to_string(l) + " weights");
+        if (w.w1.type != w.w3.type) return fail(L2B_ERR_UNSUPPORTED_TYPE, "ffn gate and up matrices must have the same tensor type");
+    }
+    m->finalized = true;
+    return L2B_OK;
+}
+
+extern "C" int32_t l2b_model_destroy(l2b_model* m) {
+    if (!m) return L2B_OK;
+    cudaSetDevice(m->device);
+    free_matrix(m->tok_emb);
+    free_matrix(m->output);
+    if (m->rms_final) cudaFree(m->rms_final);
+    for (auto& w : m->layers) {
+        if (w.rms_att) cudaFree(w.rms_att);
+        if (w.rms_ffn) cudaFree(w.rms_ffn);
+        free_matrix(w.wq); free_matrix(w.wk); free_matrix(w.wv); free_matrix(w.wo);
+        free_matrix(w.w1); free_matrix(w.w2); free_matrix(w.w3);
+    }
+    delete m;
+    return L2B_OK;
+}
+
+extern "C" int32_t l2b_model_weight_bytes(const l2b_model* m, int64_t* bytes) {
+    if (!m || !bytes) return fail(L2B_ERR_BAD_ARG, "null argument");
+    int64_t b = m->output.file_bytes + (int64_t)m->cfg.dim * 4;  // output matrix + final norm gain
+    b += m->tok_emb.file_bytes / m->cfg.vocab_size;               // one embedding row
+    for (const auto& w : m->layers)
+        b += w.wq.file_bytes + w.wk.file_bytes + w.wv.file_bytes + w.wo.file_bytes + w.w1.file_bytes + w.w2.file_bytes + w.w3.file_bytes +
+             2 * (int64_t)m->cfg.dim * 4;
+    *bytes = b;
+    return L2B_OK;
+}
+
+// ---------------------------------------------------------------------------------------------
+// session
+// ---------------------------------------------------------------------------------------------
+static void session_free(l2b_session* s) {
+    if (!s) return;
+    if (s->graph) cudaGraphExecDestroy(s->graph);
+    void* bufs[] = {s->x, s->q, s->hb, s->logits, s->kc, s->vc, s->part_m, s->part_l, s->part_acc, s->amax_val, s->amax_idx,
+                    s->rope_cs, s->ctl, s->status, s->prompt, s->out_tokens, s->next_token};
+    for (void* b : bufs)
+        if (b) cudaFree(b);
+    if (s->h_ctl) cudaFreeHost(s->h_ctl);
+    if (s->h_small) cudaFreeHost(s->h_small);
+    if (s->ev0) cudaEventDestroy(s->ev0);
+    if (s->ev1) cudaEventDestroy(s->ev1);
+    if (s->own_stream && s->stream) cudaStreamDestroy(s->stream);
+    delete s;
+}
+
+// Enqueue every kernel of one token on the session stream (this is what the graph captures).
+static int32_t enqueue_token(l2b_session* s, int* nlaunch) {
+    const l2b_model* m = s->model;
+    const l2b_config& c = m->cfg;
+    const int hs = c.dim / c.n_heads;
+    const size_t kvl = kv_layer_elems(c);
+    int count = 0;
+    bool first = true;
+    auto mv = [&](MvLaunch& L) -> int32_t {
+        L.planes = m->planes;
+        L2B_TRY(plan_matvec(L, s->di));
+        CU(launch_matvec(L, s->stream, !first));
+        first = false;
+        ++count;
+        return L2B_OK;
+    };
+    auto base_params = [&](MvLaunch& L, int n_in) {
+        memset(&L.p, 0, sizeof(L.p));
+        L.p.n_in = n_in;
+        L.p.pos = &s->ctl->pos;
+        L.p.token = &s->ctl->token;
+        L.p.rope_cs = s->rope_cs;
+        L.p.seq_len = c.seq_len;
+        L.p.status = s->status;
+    };
+    const int rope_mode = c.rope_is_neox ? PAIR_NEOX : PAIR_ADJACENT;
+    for (int l = 0; l < c.n_layers; ++l) {
+        const LayerW& w = m->layers[l];
+        float* kcl = s->kc + (size_t)l * kvl;
+        float* vcl = s->vc + (size_t)l * kvl;
+        // --- attention rmsnorm + q/k/v projections + RoPE + cache write (inference.jl:236-260)
+        {
+            MvSegment segs[3] = {make_segment(w.wq, rope_mode, EPI_ROPE_Q, s->q, hs), make_segment(w.wk, rope_mode, EPI_ROPE_K, kcl, hs),
+                                 make_segment(w.wv, PAIR_ADJACENT, EPI_STORE_V, vcl, hs)};
+            // matrices of one storage class (f32 or k-quant) share a launch
+            for (int cls = 0; cls < 2; ++cls) {
+                MvLaunch L;
+                base_params(L, c.dim);
+                for (int i = 0; i < 3; ++i)
+                    if ((segs[i].type == T_F32) == (cls == 0)) L.p.seg[L.p.nseg++] = segs[i];
+                if (L.p.nseg == 0) continue;
+                if (l == 0) {
+                    L.p.pro = PRO_EMBED_RMSNORM;
+                    L.p.emb = m->tok_emb.data;
+                    L.p.emb_d6 = m->tok_emb.d6;
+                    L.p.emb_type = m->tok_emb.type;
+                    L.p.x_out = s->x;
+                } else {
+                    L.p.pro = PRO_RMSNORM;
+                    L.p.x_in = s->x;
+                }
+                L.p.gain = w.rms_att;
+                L2B_TRY(mv(L));
+            }
+        }
+        // --- attention over the cache (inference.jl:263-278)
+        {
+            AttnParams a;
+            memset(&a, 0, sizeof(a));
+            a.q = s->q; a.kc = kcl; a.vc = vcl;
+            a.part_m = s->part_m; a.part_l = s->part_l; a.part_acc = s->part_acc;
+            a.pos = &s->ctl->pos;
+            a.n_heads = c.n_heads; a.n_kv = c.n_kv_heads; a.hs = hs; a.seq_len = c.seq_len; a.nsplit = s->nsplit;
+            CU(launch_attention(a, s->gq, s->stream, true));
+            ++count;
+        }
+        // --- output projection + residual (inference.jl:281-284)
+        {
+            MvLaunch L;
+            base_params(L, c.dim);
+            L.p.seg[L.p.nseg++] = make_segment(w.wo, PAIR_ADJACENT, EPI_RESIDUAL, s->x, hs);
+            L.p.pro = PRO_ATTN_MERGE;
+            L.p.part_m = s->part_m; L.p.part_l = s->part_l; L.p.part_acc = s->part_acc;
+            L.p.nsplit = s->nsplit;
+            L.p.attn_head_size = hs;
+            L.p.resid = s->x;
+            L2B_TRY(mv(L));
+        }
+        // --- ffn rmsnorm + gate/up + SwiGLU (inference.jl:287-299)
+        {
+            MvLaunch L;
+            base_params(L, c.dim);
+            MvSegment g = make_segment(w.w1, PAIR_DUAL, EPI_SWIGLU, s->hb, hs);
+            g.npairs = (int)w.w1.out;
+            g.w2 = w.w3.data;
+            g.d6_2 = w.w3.d6;
+            L.p.seg[L.p.nseg++] = g;
+            L.p.pro = PRO_RMSNORM;
+            L.p.x_in = s->x;
+            L.p.gain = w.rms_ffn;
+            L2B_TRY(mv(L));
+        }
+        // --- down projection + residual (inference.jl:302-305)
+        {
+            MvLaunch L;
+            base_params(L, c.hidden_dim);
+            L.p.seg[L.p.nseg++] = make_segment(w.w2, PAIR_ADJACENT, EPI_RESIDUAL, s->x, hs);
+            L.p.pro = PRO_COPY;
+            L.p.x_in = s->hb;
+            L.p.resid = s->x;
+            L2B_TRY(mv(L));
+        }
+    }
+    // --- final rmsnorm + classifier + per-block argmax (inference.jl:309-312)
+    {
+        MvLaunch L;
+        base_params(L, c.dim);
+        L.p.seg[L.p.nseg++] = make_segment(m->output, PAIR_ADJACENT, EPI_LOGITS, s->logits, hs);
+        L.p.pro = PRO_RMSNORM;
+        L.p.x_in = s->x;
+        L.p.gain = m->rms_final;
+        L.p.amax_val = s->amax_val;
+        L.p.amax_idx = s->amax_idx;
+        L2B_TRY(mv(L));
+    }
+    // --- next token (inference.jl:354-368) and advance
+    {
+        FinalizeParams f;
+        memset(&f, 0, sizeof(f));
+        f.logits = s->logits; f.vocab = c.vocab_size;
+        f.amax_val = s->amax_val; f.amax_idx = s->amax_idx; f.nparts = s->di.sms;
+        f.ctl = s->ctl; f.prompt = s->prompt; f.out_tokens = s->out_tokens; f.advance = 1; f.next_token = s->next_token;
+        CU(launch_kernel(finalize_token_kernel, dim3(1), dim3(FIN_THREADS), 0, s->stream, true, f));
+        ++count;
+    }
+    if (nlaunch) *nlaunch = count;
+    return L2B_OK;
+}
+
+extern "C" int32_t l2b_session_create(l2b_model* m, void* stream, l2b_session** out) {
+    if (!m || !out) return fail(L2B_ERR_BAD_ARG, "null argument");
+    *out = nullptr;
+    if (!m->finalized) return fail(L2B_ERR_STATE, "l2b_model_finalize has not been called");
+    CU(cudaSetDevice(m->device));
+    set_kernel_attrs();
+    if (g_attr_err != cudaSuccess) return fail(L2B_ERR_CUDA, std::string("cudaFuncSetAttribute: ") + cudaGetErrorString(g_attr_err));
+    const l2b_config& c = m->cfg;
+    const int hs = c.dim / c.n_heads;
+    l2b_session* s = new l2b_session();
+    s->model = m;
+    int32_t st = L2B_OK;
+    auto guard = [&](int32_t code) {
+        if (code != L2B_OK && st == L2B_OK) st = code;
+        return code == L2B_OK;
+    };
+    auto run = [&]() -> int32_t {
+        L2B_TRY(query_device(s->di));
+        if (stream) s->stream = (cudaStream_t)stream;
+        else {
+            CU(cudaStreamCreateWithFlags(&s->stream, cudaStreamNonBlocking));
+            s->own_stream = true;
+        }
+        s->gq = choose_gq(c.n_heads, c.n_kv_heads);
+        const int groups = c.n_heads / s->gq;
+        int ns = (s->di.sms + groups - 1) / groups;
+        ns = std::max(1, std::min(ns, std::min(32, (c.seq_len + 7) / 8)));
+        s->nsplit = (int)env_long("L2B_ATTN_SPLITS", ns);
+        const size_t kvl = kv_layer_elems(c);
+        CU(cudaMalloc(&s->x, (size_t)c.dim * 4));
+        CU(cudaMalloc(&s->q, (size_t)c.dim * 4));
+        CU(cudaMalloc(&s->hb, (size_t)c.hidden_dim * 4));
+        CU(cudaMalloc(&s->logits, (size_t)c.vocab_size * 4));
+        CU(cudaMalloc(&s->kc, kvl * c.n_layers * 4));
+        CU(cudaMalloc(&s->vc, kvl * c.n_layers * 4));
+        CU(cudaMalloc(&s->part_m, (size_t)c.n_heads * s->nsplit * 4));
+        CU(cudaMalloc(&s->part_l, (size_t)c.n_heads * s->nsplit * 4));
+        CU(cudaMalloc(&s->part_acc, (size_t)c.n_heads * s->nsplit * hs * 4));
+        CU(cudaMalloc(&s->amax_val, (size_t)s->di.sms * 4));
+        CU(cudaMalloc(&s->amax_idx, (size_t)s->di.sms * 4));
+        CU(cudaMalloc(&s->ctl, sizeof(Control)));
+        CU(cudaMalloc(&s->status, 4));
+        CU(cudaMalloc(&s->prompt, (size_t)c.seq_len * 4));
+        CU(cudaMalloc(&s->out_tokens, (size_t)c.seq_len * 4));
+        CU(cudaMalloc(&s->next_token, 4));
+        CU(cudaMallocHost(&s->h_ctl, sizeof(Control)));
+        CU(cudaMallocHost(&s->h_small, 16));
+        CU(cudaEventCreate(&s->ev0));
+        CU(cudaEventCreate(&s->ev1));
+        CU(cudaMemsetAsync(s->kc, 0, kvl * c.n_layers * 4, s->stream));
+        CU(cudaMemsetAsync(s->vc, 0, kvl * c.n_layers * 4, s->stream));
+        CU(cudaMemsetAsync(s->status, 0, 4, s->stream));
+        CU(cudaMemsetAsync(s->ctl, 0, sizeof(Control), s->stream));
+        CU(cudaMemsetAsync(s->prompt, 0, (size_t)c.seq_len * 4, s->stream));
+        std::vector<float> cs;
+        rope_table_host(cs, c.seq_len, hs, c.rope_freq_base);
+        CU(cudaMalloc(&s->rope_cs, cs.size() * 4));
+        CU(cudaMemcpyAsync(s->rope_cs, cs.data(), cs.size() * 4, cudaMemcpyHostToDevice, s->stream));
+        CU(cudaStreamSynchronize(s->stream));
+        // capture one token
+        cudaGraph_t g = nullptr;
+        CU(cudaStreamBeginCapture(s->stream, cudaStreamCaptureModeThreadLocal));
+        int32_t es = enqueue_token(s, &s->kernels_per_token);
+        cudaError_t ce = cudaStreamEndCapture(s->stream, &g);
+        if (es != L2B_OK) {
+            if (g) cudaGraphDestroy(g);
+            return es;
+        }
+        CU(ce);
+        cudaError_t ie = cudaGraphInstantiate(&s->graph, g, 0);
+        cudaGraphDestroy(g);
+        CU(ie);
+        return L2B_OK;
+    };
+    guard(run());
+    if (st != L2B_OK) {
+        session_free(s);
+        return st;
+    }
+    *out = s;
+    return L2B_OK;
+}
+
+extern "C" int32_t l2b_session_reset(l2b_session* s) {
+    if (!s) return fail(L2B_ERR_BAD_ARG, "null session");
+    CU(cudaSetDevice(s->model->device));
+    const size_t bytes = kv_layer_elems(s->model->cfg) * s->model->cfg.n_layers * 4;
+    CU(cudaMemsetAsync(s->kc, 0, bytes, s->stream));
+    CU(cudaMemsetAsync(s->vc, 0, bytes, s->stream));
+    CU(cudaStreamSynchronize(s->stream));
+    return L2B_OK;
+}
+
+extern "C" int32_t l2b_session_destroy(l2b_session* s) {
+    if (!s) return L2B_OK;
+    cudaSetDevice(s->model->device);
+    if (s->stream) cudaStreamSynchronize(s->stream);
+    session_free(s);
+    return L2B_OK;
+}
+
+static int32_t check_status_word(l2b_session* s) {
+    if (s->h_small[1] == DEV_ERR_TMA_TIMEOUT) {
+        cudaMemsetAsync(s->status, 0, 4, s->stream);
+        return fail(L2B_ERR_TIMEOUT, "a bounded wait on a weight copy ran out inside a kernel");
+    }
+    if (s->h_small[1] != DEV_OK) {
+        cudaMemsetAsync(s->status, 0, 4, s->stream);
+        return fail(L2B_ERR_CUDA, "kernel reported device status " + std::to_string(s->h_small[1]));
+    }
+    return L2B_OK;
+}
+
+// One graph launch with the control block set from the host.
+static int32_t run_one(l2b_session* s, int token, int pos, float temperature, double uniform) {
+    const l2b_config& c = s->model->cfg;
+    if (token < 0 || token >= c.vocab_size) return fail(L2B_ERR_BAD_ARG, "token id out of range");
+    if (pos < 0 || pos >= c.seq_len) return fail(L2B_ERR_BAD_ARG, "position out of range (seq_len)");
+    if (temperature < 0.f) return fail(L2B_ERR_BAD_ARG, "temperature must be >= 0");
+    CU(cudaSetDevice(s->model->device));
+    Control& h = *s->h_ctl;
+    memset(&h, 0, sizeof(h));
+    h.token = token;
+    h.pos = pos;
+    h.n_prompt = 0;
+    h.temperature = temperature;
+    h.uniform = uniform;
+    CU(cudaEventRecord(s->ev0, s->stream));
+    CU(cudaMemcpyAsync(s->ctl, s->h_ctl, sizeof(Control), cudaMemcpyHostToDevice, s->stream));
+    CU(cudaGraphLaunch(s->graph, s->stream));
+    CU(cudaMemcpyAsync(&s->h_small[0], s->next_token, 4, cudaMemcpyDeviceToHost, s->stream));
+    CU(cudaMemcpyAsync(&s->h_small[1], s->status, 4, cudaMemcpyDeviceToHost, s->stream));
+    CU(cudaEventRecord(s->ev1, s->stream));
+    CU(cudaStreamSynchronize(s->stream));
+    CU(cudaEventElapsedTime(&s->last_ms, s->ev0, s->ev1));
+    return check_status_word(s);
+}
+
+extern "C" int32_t l2b_forward(l2b_session* s, int32_t token, int32_t pos, float* host_logits) {
+    if (!s) return fail(L2B_ERR_BAD_ARG, "null session");
+    L2B_TRY(run_one(s, token, pos, 0.f, 0.0));
+    if (host_logits) CU(cudaMemcpy(host_logits, s->logits, (size_t)s->model->cfg.vocab_size * 4, cudaMemcpyDeviceToHost));
+    return L2B_OK;
+}
+
+extern "C" int32_t l2b_decode_next(l2b_session* s, int32_t token, int32_t pos, float temperature, double uniform, int32_t* next) {
+    if (!s || !next) return fail(L2B_ERR_BAD_ARG, "null argument");
+    if (!(uniform >= 0.0 && uniform < 1.0)) return fail(L2B_ERR_BAD_ARG, "uniform must lie in [0,1)");
+    L2B_TRY(run_one(s, token, pos, temperature, uniform));
+    *next = s->h_small[0];
+    return L2B_OK;
+}
+
+extern "C" int32_t l2b_generate(l2b_session* s, const int32_t* prompt, int32_t n_prompt, int32_t n_positions, float temperature, uint64_t seed,
+                                int32_t* out_tokens, float* device_ms) {
+    if (!s || !prompt || !out_tokens) return fail(L2B_ERR_BAD_ARG, "null argument");
+    const l2b_config& c = s->model->cfg;
+    if (n_prompt < 1 || n_prompt > c.seq_len) return fail(L2B_ERR_BAD_ARG, "prompt length must be in 1..seq_len");
+    if (n_positions < 1 || n_positions > c.seq_len) return fail(L2B_ERR_BAD_ARG, "n_positions must be in 1..seq_len");
+    if (temperature < 0.f) return fail(L2B_ERR_BAD_ARG, "temperature must be >= 0");
+    for (int i = 0; i < n_prompt; ++i)
+        if (prompt[i] < 0 || prompt[i] >= c.vocab_size) return fail(L2B_ERR_BAD_ARG, "prompt token id out of range");
+    CU(cudaSetDevice(s->model->device));
+    Control& h = *s->h_ctl;
+    memset(&h, 0, sizeof(h));
+    h.token = prompt[0];
+    h.pos = 0;
+    h.n_prompt = n_prompt;
+    h.temperature = temperature;
+    h.use_seed = 1;
+    h.seed = seed;
+    CU(cudaEventRecord(s->ev0, s->stream));
+    CU(cudaMemcpyAsync(s->prompt, prompt, (size_t)n_prompt * 4, cudaMemcpyHostToDevice, s->stream));
+    CU(cudaMemcpyAsync(s->ctl, s->h_ctl, sizeof(Control), cudaMemcpyHostToDevice, s->stream));
+    for (int i = 0; i < n_positions; ++i) CU(cudaGraphLaunch(s->graph, s->stream));
+    CU(cudaMemcpyAsync(out_tokens, s->out_tokens, (size_t)n_positions * 4, cudaMemcpyDeviceToHost, s->stream));
+    CU(cudaMemcpyAsync(&s->h_small[1], s->status, 4, cudaMemcpyDeviceToHost, s->stream));
+    CU(cudaEventRecord(s->ev1, s->stream));
+    CU(cudaStreamSynchronize(s->stream));
+    CU(cudaEventElapsedTime(&s->last_ms, s->ev0, s->ev1));
+    if (device_ms) *device_ms = s->last_ms;
+    return check_status_word(s);
+}
+
+extern "C" int32_t l2b_session_logits(l2b_session* s, float* host_logits) {
+    if (!s || !host_logits) return fail(L2B_ERR_BAD_ARG, "null argument");
+    CU(cudaSetDevice(s->model->device));
+    CU(cudaStreamSynchronize(s->stream));
+    CU(cudaMemcpy(host_logits, s->logits, (size_t)s->model->cfg.vocab_size * 4, cudaMemcpyDeviceToHost));
+    return L2B_OK;
+}
+
+extern "C" int32_t l2b_session_read(l2b_session* s, int32_t which, float* host_out, int64_t cap, int64_t* n) {
+    if (!s || !host_out) return fail(L2B_ERR_BAD_ARG, "null argument");
+    const l2b_config& c = s->model->cfg;
+    const float* src = nullptr;
+    int64_t len = 0;
+    switch (which) {
+        case 0: src = s->x; len = c.dim; break;
+        case 2: src = s->q; len = c.dim; break;
+        case 5: src = s->hb; len = c.hidden_dim; break;
+        case 6: src = s->logits; len = c.vocab_size; break;
+        default: return fail(L2B_ERR_BAD_ARG, "unknown buffer id");
+    }
+    CU(cudaSetDevice(s->model->device));
+    CU(cudaStreamSynchronize(s->stream));
+    CU(cudaMemcpy(host_out, src, (size_t)std::min(cap, len) * 4, cudaMemcpyDeviceToHost));
+    if (n) *n = len;
+    return L2B_OK;
+}
+
+extern "C" int32_t l2b_session_last_device_ms(l2b_session* s, float* ms) {
+    if (!s || !ms) return fail(L2B_ERR_BAD_ARG, "null argument");
+    *ms = s->last_ms;
+    return L2B_OK;
+}
+extern "C" int32_t l2b_session_kernels_per_token(l2b_session* s, int32_t* n) {
+    if (!s || !n) return fail(L2B_ERR_BAD_ARG, "null argument");
+    *n = s->kernels_per_token;
+    return L2B_OK;
+}
+
+// ---------------------------------------------------------------------------------------------
+// isolated operators
+// ---------------------------------------------------------------------------------------------
+struct DevBuf {
+    void* p = nullptr;
+    ~DevBuf() {
+        if (p) cudaFree(p);
+    }
+    template <typename T>
+    T* as() { return (T*)p; }
+};
+static int32_t dev_alloc(DevBuf& b, size_t bytes) {
+    CU(cudaMalloc(&b.p, bytes ? bytes : 16));
+    return L2B_OK;
+}
+static int32_t dev_upload(DevBuf& b, const void* host, size_t bytes) {
+    L2B_TRY(dev_alloc(b, bytes));
+    CU(cudaMemcpy(b.p, host, bytes, cudaMemcpyHostToDevice));
+    return L2B_OK;
+}
+
+extern "C" int32_t l2b_dequantize(int32_t type, const void* host_blocks, int64_t n, float* host_out) {
+    if (!host_blocks || !host_out || n < 0) return fail(L2B_ERR_BAD_ARG, "null argument");
+    if (!type_supported(type)) return fail(L2B_ERR_UNSUPPORTED_TYPE, "tensor type " + std::to_string(type) + " not implemented");
+    L2B_TRY(require_device());
+    if (n == 0) return L2B_OK;
+    if (type == T_F32) {  // dequantize!(y, x::Vector{Float32}) is a copy; it still goes through the device
+        DevBuf b;
+        L2B_TRY(dev_upload(b, host_blocks, (size_t)n * 4));
+        CU(cudaMemcpy(host_out, b.p, (size_t)n * 4, cudaMemcpyDeviceToHost));
+        return L2B_OK;
+    }
+    if (n % QK_K != 0) return fail(L2B_ERR_BAD_ARG, "element count must be a multiple of 256");
+    DevMatrix m;
+    int32_t st = upload_matrix(m, type, host_blocks, n, 1, 0);
+    if (st != L2B_OK) return st;
+    DevBuf out;
+    st = dev_alloc(out, (size_t)n * 4);
+    if (st == L2B_OK) {
+        const int grid = (int)std::min<int64_t>(4096, (n + 255) / 256);
+        dequantize_kernel<<<grid, 256>>>(type, m.data, m.d6, n, out.as<float>());
+        cudaError_t e = cudaGetLastError();
+        if (e == cudaSuccess) e = cudaMemcpy(host_out, out.p, (size_t)n * 4, cudaMemcpyDeviceToHost);
+        if (e != cudaSuccess) st = fail(L2B_ERR_CUDA, cudaGetErrorString(e));
+    }
+    free_matrix(m);
+    return st;
+}
+
+// Run the fused kernel's prologue on one block and export what it built.
+static int32_t run_export(MvParams& p, bool kq, int planes, int8_t* q_out, float* d_out, float* sums_out, float* f_out) {
+    set_kernel_attrs();
+    const int warps = 8;
+    const size_t smem = mv_smem_layout(p.n_in, planes, kq, warps, 0, 0).total;
+    int optin = 0, dev = 0;
+    CU(cudaGetDevice(&dev));
+    CU(cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev));
+    if ((long)smem > optin) return fail(L2B_ERR_BAD_ARG, "vector too long for one block's shared memory");
+    if (!kq) export_activation_kernel<false, 1><<<1, warps * 32, smem>>>(p, q_out, d_out, sums_out, f_out);
+    else if (planes == 1) export_activation_kernel<true, 1><<<1, warps * 32, smem>>>(p, q_out, d_out, sums_out, f_out);
+    else if (planes == 2) export_activation_kernel<true, 2><<<1, warps * 32, smem>>>(p, q_out, d_out, sums_out, f_out);
+    else export_activation_kernel<true, 3><<<1, warps * 32, smem>>>(p, q_out, d_out, sums_out, f_out);
+    CU(cudaGetLastError());
+    CU(cudaDeviceSynchronize());
+    return L2B_OK;
+}
+
+extern "C" int32_t l2b_quantize_q8k(const float* host_x, int64_t n, int32_t planes, int8_t* host_q, float* host_d, float* host_sums) {
+    if (!host_x || !host_q || !host_d || !host_sums) return fail(L2B_ERR_BAD_ARG, "null argument");
+    if (n <= 0 || n % QK_K != 0) return fail(L2B_ERR_BAD_ARG, "n must be a positive multiple of 256");
+    if (planes < 1 || planes > 3) return fail(L2B_ERR_BAD_ARG, "planes must be 1..3");
+    L2B_TRY(require_device());
+    DevBuf x, q, d, sums;
+    L2B_TRY(dev_upload(x, host_x, (size_t)n * 4));
+    L2B_TRY(dev_alloc(q, (size_t)planes * n));
+    L2B_TRY(dev_alloc(d, (size_t)planes * (n / QK_K) * 4));
+    L2B_TRY(dev_alloc(sums, (size_t)(n / 16) * 4));
+    MvParams p;
+    memset(&p, 0, sizeof(p));
+    p.n_in = (int)n;
+    p.pro = PRO_COPY;
+    p.x_in = x.as<float>();
+    L2B_TRY(run_export(p, true, planes, q.as<int8_t>(), d.as<float>(), sums.as<float>(), nullptr));
+    CU(cudaMemcpy(host_q, q.p, (size_t)planes * n, cudaMemcpyDeviceToHost));
+    CU(cudaMemcpy(host_d, d.p, (size_t)planes * (n / QK_K) * 4, cudaMemcpyDeviceToHost));
+    CU(cudaMemcpy(host_sums, sums.p, (size_t)(n / 16) * 4, cudaMemcpyDeviceToHost));
+    return L2B_OK;
+}
+
+extern "C" int32_t l2b_rmsnorm(float* host_o, const float* host_x, const float* host_w, int64_t n) {
+    if (!host_o || !host_x || !host_w) return fail(L2B_ERR_BAD_ARG, "null argument");
+    if (n <= 0 || n % 8 != 0) return fail(L2B_ERR_BAD_ARG, "n must be a positive multiple of 8");
+    L2B_TRY(require_device());
+    DevBuf x, w, o;
+    L2B_TRY(dev_upload(x, host_x, (size_t)n * 4));
+    L2B_TRY(dev_upload(w, host_w, (size_t)n * 4));
+    L2B_TRY(dev_alloc(o, (size_t)n * 4));
+    MvParams p;
+    memset(&p, 0, sizeof(p));
+    p.n_in = (int)n;
+    p.pro = PRO_RMSNORM;
+    p.x_in = x.as<float>();
+    p.gain = w.as<float>();
+    L2B_TRY(run_export(p, false, 1, nullptr, nullptr, nullptr, o.as<float>()));
+    CU(cudaMemcpy(host_o, o.p, (size_t)n * 4, cudaMemcpyDeviceToHost));
+    return L2B_OK;
+}
+
+extern "C" int32_t l2b_rope(float* host_x, int32_t hs, int32_t n_heads, int32_t pos, float base, int32_t neox) {
+    if (!host_x) return fail(L2B_ERR_BAD_ARG, "null argument");
+    if (hs <= 0 || hs % 2 != 0 || n_heads <= 0 || pos < 0) return fail(L2B_ERR_BAD_ARG, "bad head size / head count / position");
+    L2B_TRY(require_device());
+    std::vector<float> cs;
+    rope_table_host(cs, pos + 1, hs, base);
+    DevBuf x, row;
+    L2B_TRY(dev_upload(x, host_x, (size_t)hs * n_heads * 4));
+    L2B_TRY(dev_upload(row, cs.data() + (size_t)pos * hs, (size_t)hs * 4));
+    rope_kernel<<<(n_heads * hs / 2 + 255) / 256, 256>>>(x.as<float>(), hs, n_heads, neox, row.as<float>());
+    CU(cudaGetLastError());
+    CU(cudaMemcpy(host_x, x.p, (size_t)hs * n_heads * 4, cudaMemcpyDeviceToHost));
+    return L2B_OK;
+}
+
+extern "C" int32_t l2b_attention(float* host_out, const float* host_q, const float* host_k, const float* host_v, int32_t n_pos, int32_t n_heads,
+                                 int32_t n_kv, int32_t hs) {
+    if (!host_out || !host_q || !host_k || !host_v) return fail(L2B_ERR_BAD_ARG, "null argument");
+    if (n_pos <= 0 || n_heads <= 0 || n_kv <= 0 || n_heads % n_kv != 0 || hs % 8 != 0 || hs > 128 || hs <= 0)
+        return fail(L2B_ERR_BAD_ARG, "bad attention shape");
+    L2B_TRY(require_device());
+    // position-major input -> cache layout [kv][pos][hs]
+    std::vector<float> kc((size_t)n_kv * n_pos * hs), vc(kc.size());
+    for (int t = 0; t < n_pos; ++t)
+        for (int h = 0; h < n_kv; ++h) {
+            memcpy(&kc[((size_t)h * n_pos + t) * hs], host_k + ((size_t)t * n_kv + h) * hs, (size_t)hs * 4);
+            memcpy(&vc[((size_t)h * n_pos + t) * hs], host_v + ((size_t)t * n_kv + h) * hs, (size_t)hs * 4);
+        }
+    const int gq = choose_gq(n_heads, n_kv);
+    const int nsplit = std::max(1, std::min(32, std::min((n_pos + 7) / 8, (int)env_long("L2B_ATTN_SPLITS", 16))));
+    DevBuf q, k, v, pm, pl, pa, out;
+    L2B_TRY(dev_upload(q, host_q, (size_t)n_heads * hs * 4));
+    L2B_TRY(dev_upload(k, kc.data(), kc.size() * 4));
+    L2B_TRY(dev_upload(v, vc.data(), vc.size() * 4));
+    L2B_TRY(dev_alloc(pm, (size_t)n_heads * nsplit * 4));
+    L2B_TRY(dev_alloc(pl, (size_t)n_heads * nsplit * 4));
+    L2B_TRY(dev_alloc(pa, (size_t)n_heads * nsplit * hs * 4));
+    L2B_TRY(dev_alloc(out, (size_t)n_heads * hs * 4));
+    AttnParams a;
+    memset(&a, 0, sizeof(a));
+    a.q = q.as<float>(); a.kc = k.as<float>(); a.vc = v.as<float>();
+    a.part_m = pm.as<float>(); a.part_l = pl.as<float>(); a.part_acc = pa.as<float>();
+    a.n_heads = n_heads; a.n_kv = n_kv; a.hs = hs; a.seq_len = n_pos; a.nsplit = nsplit; a.npos_override = n_pos;
+    CU(launch_attention(a, gq, 0, false));
+    MvParams p;
+    memset(&p, 0, sizeof(p));
+    p.n_in = n_heads * hs;
+    p.pro = PRO_ATTN_MERGE;
+    p.part_m = a.part_m; p.part_l = a.part_l; p.part_acc = a.part_acc;
+    p.nsplit = nsplit;
+    p.attn_head_size = hs;
+    L2B_TRY(run_export(p, false, 1, nullptr, nullptr, nullptr, out.as<float>()));
+    CU(cudaMemcpy(host_out, out.p, (size_t)n_heads * hs * 4, cudaMemcpyDeviceToHost));
+    return L2B_OK;
+}
+
+extern "C" int32_t l2b_swiglu(float* host_hb, const float* host_hb2, int64_t n) {
+    if (!host_hb || !host_hb2 || n < 0) return fail(L2B_ERR_BAD_ARG, "null argument");
+    L2B_TRY(require_device());
+    if (n == 0) return L2B_OK;
+    DevBuf a, b;
+    L2B_TRY(dev_upload(a, host_hb, (size_t)n * 4));
+    L2B_TRY(dev_upload(b, host_hb2, (size_t)n * 4));
+    swiglu_kernel<<<(int)std::min<int64_t>(1024, (n + 255) / 256), 256>>>(a.as<float>(), b.as<float>(), n);
+    CU(cudaGetLastError());
+    CU(cudaMemcpy(host_hb, a.p, (size_t)n * 4, cudaMemcpyDeviceToHost));
+    return L2B_OK;
+}
+
+extern "C" int32_t l2b_argmax(const float* host_logits, int64_t n, int32_t* index) {
+    if (!host_logits || !index || n <= 0 || n > 0x7fffffff) return fail(L2B_ERR_BAD_ARG, "bad argument");
+    L2B_TRY(require_device());
+    DevBuf x, v, i;
+    L2B_TRY(dev_upload(x, host_logits, (size_t)n * 4));
+    L2B_TRY(dev_alloc(v, 4));
+    L2B_TRY(dev_alloc(i, 4));
+    argmax_kernel<<<1, FIN_THREADS>>>(x.as<float>(), (int)n, v.as<float>(), i.as<int>());
+    CU(cudaGetLastError());
+    CU(cudaMemcpy(index, i.p, 4, cudaMemcpyDeviceToHost));
+    return L2B_OK;
+}
+
+extern "C" int32_t l2b_sample_temperature(const float* host_logits, int64_t n, float temperature, double uniform, int32_t* index) {
+    if (!host_logits || !index || n <= 0 || n > 0x7fffffff) return fail(L2B_ERR_BAD_ARG, "bad argument");
+    if (!(temperature > 0.f)) return fail(L2B_ERR_BAD_ARG, "temperature must be > 0");
+    if (!(uniform >= 0.0 && uniform < 1.0)) return fail(L2B_ERR_BAD_ARG, "uniform must lie in [0,1)");
+    L2B_TRY(require_device());
+    DevBuf x, v, i, ctl, nt;
+    L2B_TRY(dev_upload(x, host_logits, (size_t)n * 4));
+    L2B_TRY(dev_alloc(v, 4));
+    L2B_TRY(dev_alloc(i, 4));
+    L2B_TRY(dev_alloc(nt, 4));
+    argmax_kernel<<<1, FIN_THREADS>>>(x.as<float>(), (int)n, v.as<float>(), i.as<int>());
+    CU(cudaGetLastError());
+    Control h;
+    memset(&h, 0, sizeof(h));
+    h.temperature = temperature;
+    h.uniform = uniform;
+    L2B_TRY(dev_upload(ctl, &h, sizeof(h)));
+    FinalizeParams f;
+    memset(&f, 0, sizeof(f));
+    f.logits = x.as<float>(); f.vocab = (int)n;
+    f.amax_val = v.as<float>(); f.amax_idx = i.as<int>(); f.nparts = 1;
+    f.ctl = ctl.as<Control>(); f.next_token = nt.as<int>();
+    finalize_token_kernel<<<1, FIN_THREADS>>>(f);
+    CU(cudaGetLastError());
+    CU(cudaMemcpy(index, nt.p, 4, cudaMemcpyDeviceToHost));
+    return L2B_OK;
+}
+
+// ---------------------------------------------------------------------------------------------
+// resident matrices
+// ---------------------------------------------------------------------------------------------
+struct l2b_matrix {
+    std::vector<DevMatrix> copies;
+    int device = 0;
+    DeviceInfo di;
+    int* status = nullptr;
+};
+
+extern "C" int32_t l2b_matrix_create(int32_t type, const void* host_W, int64_t in_dim, int64_t out_dim, int32_t copies, l2b_matrix** out) {
+    if (!host_W || !out || copies < 1) return fail(L2B_ERR_BAD_ARG, "bad argument");
+    *out = nullptr;
+    if (out_dim % 2 != 0) return fail(L2B_ERR_BAD_ARG, "out_dim must be even");
+    L2B_TRY(require_device());
+    set_kernel_attrs();
+    l2b_matrix* m = new l2b_matrix();
+    cudaGetDevice(&m->device);
+    int32_t st = query_device(m->di);
+    m->copies.resize(copies);
+    for (int i = 0; i < copies && st == L2B_OK; ++i) st = upload_matrix(m->copies[i], type, host_W, in_dim, out_dim, 0);
+    if (st == L2B_OK && cudaMalloc(&m->status, 4) != cudaSuccess) st = fail(L2B_ERR_OOM, "cudaMalloc status");
+    if (st == L2B_OK) cudaMemset(m->status, 0, 4);
+    if (st != L2B_OK) {
+        for (auto& c : m->copies) free_matrix(c);
+        delete m;
+        return st;
+    }
+    *out = m;
+    return L2B_OK;
+}
+
+extern "C" int32_t l2b_matrix_destroy(l2b_matrix* m) {
+    if (!m) return L2B_OK;
+    cudaSetDevice(m->device);
+    for (auto& c : m->copies) free_matrix(c);
+    if (m->status) cudaFree(m->status);
+    delete m;
+    return L2B_OK;
+}
+
+extern "C" int32_t l2b_matrix_matvec_device(l2b_matrix* m, int32_t copy, const float* dev_x, float* dev_y, int32_t planes, void* stream) {
+    if (!m || !dev_x || !dev_y) return fail(L2B_ERR_BAD_ARG, "null argument");
+    if (copy < 0 || copy >= (int)m->copies.size()) return fail(L2B_ERR_BAD_ARG, "copy index out of range");
+    if (planes < 0 || planes > 3) return fail(L2B_ERR_BAD_ARG, "act_planes must be 0..3");
+    const DevMatrix& w = m->copies[copy];
+    MvLaunch L;
+    memset(&L.p, 0, sizeof(L.p));
+    L.planes = planes == 0 ? 3 : planes;
+    L.p.n_in = (int)w.in;
+    L.p.seg[L.p.nseg++] = make_segment(w, PAIR_ADJACENT, EPI_STORE, dev_y, 0);
+    L.p.pro = PRO_COPY;
+    L.p.x_in = dev_x;
+    L.p.status = m->status;
+    L2B_TRY(plan_matvec(L, m->di));
+    CU(launch_matvec(L, (cudaStream_t)stream, false));
+    return L2B_OK;
+}
+
+extern "C" int32_t l2b_matrix_matvec(l2b_matrix* m, const float* host_x, int32_t ncols, float* host_y, int32_t planes) {
+    if (!m || !host_x || !host_y || ncols < 1) return fail(L2B_ERR_BAD_ARG, "bad argument");
+    CU(cudaSetDevice(m->device));
+    const DevMatrix& w = m->copies[0];
+    DevBuf x, y;
+    L2B_TRY(dev_upload(x, host_x, (size_t)ncols * w.in * 4));
+    L2B_TRY(dev_alloc(y, (size_t)ncols * w.out * 4));
+    for (int c = 0; c < ncols; ++c)
+        L2B_TRY(l2b_matrix_matvec_device(m, 0, x.as<float>() + (size_t)c * w.in, y.as<float>() + (size_t)c * w.out, planes, nullptr));
+    CU(cudaDeviceSynchronize());
+    int hst = 0;
+    CU(cudaMemcpy(&hst, m->status, 4, cudaMemcpyDeviceToHost));
+    if (hst != DEV_OK) {
+        cudaMemset(m->status, 0, 4);
+        return fail(hst == DEV_ERR_TMA_TIMEOUT ? L2B_ERR_TIMEOUT : L2B_ERR_CUDA, "kernel reported device status " + std::to_string(hst));
+    }
+    CU(cudaMemcpy(host_y, y.p, (size_t)ncols * w.out * 4, cudaMemcpyDeviceToHost));
+    return L2B_OK;
+}
+
+extern "C" int32_t l2b_matvec(int32_t type, const void* host_W, int64_t in_dim, int64_t out_dim, const float* host_x, int32_t ncols, float* host_y,
+                              int32_t planes) {
+    l2b_matrix* m = nullptr;
+    L2B_TRY(l2b_matrix_create(type, host_W, in_dim, out_dim, 1, &m));
+    int32_t st = l2b_matrix_matvec(m, host_x, ncols, host_y, planes);
+    l2b_matrix_destroy(m);
+    return st;
+}

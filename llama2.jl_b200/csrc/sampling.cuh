@@ -1,0 +1,184 @@
+// End-of-token step of the loop in `sample` (src/inference.jl:354-385): choose the next token
+// on the device and advance the position, so that a generation loop needs no host round trip.
+#pragma once
+#include "common.cuh"
+
+namespace l2b {
+
+// Device-resident loop state; kernels read token/pos from here, so one captured graph serves
+// every position.
+struct Control {
+    int token;          // token fed at this position
+    int pos;            // 0-based position
+    int n_prompt;       // prompt length; while pos+1 < n_prompt the next token is forced
+    int use_seed;       // 1: uniform drawn from (seed, pos); 0: `uniform` below
+    float temperature;  // 0 = greedy
+    int pad;
+    double uniform;
+    unsigned long long seed;
+};
+
+__device__ __forceinline__ unsigned long long splitmix64(unsigned long long x) {
+    x += 0x9E3779B97F4A7C15ull;
+    x = (x ^ (x >> 30)) * 0xBF58476D1CE4E5B9ull;
+    x = (x ^ (x >> 27)) * 0x94D049BB133111EBull;
+    return x ^ (x >> 31);
+}
+
+struct FinalizeParams {
+    const float* logits;
+    int vocab;
+    const float* amax_val;  // per-block maxima written by the logits kernel
+    const int* amax_idx;
+    int nparts;
+    Control* ctl;
+    const int* prompt;  // device copy of the prompt (may be null when n_prompt <= 1)
+    int* out_tokens;    // out_tokens[pos] = token chosen after position pos (may be null)
+    int advance;        // 1: ctl->token = next, ctl->pos += 1
+    int* next_token;    // single-slot result for one-step calls
+};
+
+constexpr int FIN_THREADS = 1024;
+
+// One block.  Greedy: argmax = first maximal index (Julia argmax, src/inference.jl:360).
+// Temperature: logits ./= T; softmax!; inverse-CDF walk of StatsBase.wsample (src/inference.jl:361-368),
+// with cumulative sums kept in f64.
+__global__ void __launch_bounds__(FIN_THREADS) finalize_token_kernel(const __grid_constant__ FinalizeParams p) {
+    pdl_launch_dependents();
+    pdl_wait();
+    __shared__ float s_val[32];
+    __shared__ int s_idx[32];
+    __shared__ double s_sum[FIN_THREADS];
+    __shared__ int s_choice;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    float bv = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int i = tid; i < p.nparts; i += FIN_THREADS) {
+        const float v = __ldcg(p.amax_val + i);
+        const int ix = __ldcg(p.amax_idx + i);
+        if (v > bv || (v == bv && ix < bi)) {
+            bv = v;
+            bi = ix;
+        }
+    }
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (ov > bv || (ov == bv && oi < bi)) {
+            bv = ov;
+            bi = oi;
+        }
+    }
+    if (lane == 0) {
+        s_val[warp] = bv;
+        s_idx[warp] = bi;
+    }
+    __syncthreads();
+    if (tid == 0) {
+        for (int w = 1; w < FIN_THREADS / 32; ++w)
+            if (s_val[w] > s_val[0] || (s_val[w] == s_val[0] && s_idx[w] < s_idx[0])) {
+                s_val[0] = s_val[w];
+                s_idx[0] = s_idx[w];
+            }
+        s_choice = s_idx[0];
+    }
+    __syncthreads();
+    const float T = p.ctl->temperature;
+    const int pos = p.ctl->pos;
+    if (T != 0.f) {
+        const float mx = s_val[0] / T;  // maximum of logits ./ T  (T > 0)
+        const int per = (p.vocab + FIN_THREADS - 1) / FIN_THREADS;
+        const int i0 = tid * per, i1 = min(p.vocab, i0 + per);
+        // pass 1: sum of exp
+        float fs = 0.f;
+        for (int i = i0; i < i1; ++i) fs += expf(__ldcg(p.logits + i) / T - mx);
+        // total in f32 like sum(x) of the reference, order: per thread then tree
+        s_sum[tid] = (double)fs;
+        __syncthreads();
+        for (int o = FIN_THREADS / 2; o > 0; o >>= 1) {
+            if (tid < o) s_sum[tid] += s_sum[tid + o];
+            __syncthreads();
+        }
+        const float denom = (float)s_sum[0];
+        __syncthreads();
+        // pass 2: probabilities and their f64 chunk sums
+        double cs = 0.0;
+        for (int i = i0; i < i1; ++i) cs += (double)(expf(__ldcg(p.logits + i) / T - mx) / denom);
+        s_sum[tid] = cs;
+        __syncthreads();
+        if (tid == 0) {
+            double u = p.ctl->uniform;
+            if (p.ctl->use_seed) u = (double)(splitmix64(p.ctl->seed + (unsigned long long)pos) >> 11) * (1.0 / 9007199254740992.0);
+            double total = 0.0;
+            for (int t = 0; t < FIN_THREADS; ++t) total += s_sum[t];
+            const double target = u * total;
+            // find the chunk whose cumulative sum reaches the target, then walk inside it
+            double cw = 0.0;
+            int t = 0;
+            while (t < FIN_THREADS - 1 && cw + s_sum[t] < target) cw += s_sum[t++];
+            int c0 = t * per, c1 = min(p.vocab, c0 + per);
+            if (c0 >= p.vocab) {
+                c0 = p.vocab - 1;
+                c1 = p.vocab;
+            }
+            int i = c0;
+            cw += (double)(expf(__ldcg(p.logits + i) / T - mx) / denom);
+            while (cw < target && i < c1 - 1) {
+                ++i;
+                cw += (double)(expf(__ldcg(p.logits + i) / T - mx) / denom);
+            }
+            s_choice = i;
+        }
+        __syncthreads();
+    }
+    if (tid == 0) {
+        int next = s_choice;
+        if (pos + 1 < p.ctl->n_prompt && p.prompt) next = p.prompt[pos + 1];
+        if (p.out_tokens) p.out_tokens[pos] = next;
+        if (p.next_token) *p.next_token = s_choice;
+        if (p.advance) {
+            p.ctl->token = next;
+            p.ctl->pos = pos + 1;
+        }
+    }
+}
+
+// argmax over a plain vector (isolated-operator entry point): one block.
+__global__ void __launch_bounds__(FIN_THREADS) argmax_kernel(const float* x, int n, float* out_val, int* out_idx) {
+    __shared__ float s_val[32];
+    __shared__ int s_idx[32];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    float bv = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int i = tid; i < n; i += FIN_THREADS) {
+        const float v = x[i];
+        if (v > bv || (v == bv && i < bi)) {
+            bv = v;
+            bi = i;
+        }
+    }
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (ov > bv || (ov == bv && oi < bi)) {
+            bv = ov;
+            bi = oi;
+        }
+    }
+    if (lane == 0) {
+        s_val[warp] = bv;
+        s_idx[warp] = bi;
+    }
+    __syncthreads();
+    if (tid == 0) {
+        for (int w = 1; w < FIN_THREADS / 32; ++w)
+            if (s_val[w] > s_val[0] || (s_val[w] == s_val[0] && s_idx[w] < s_idx[0])) {
+                s_val[0] = s_val[w];
+                s_idx[0] = s_idx[w];
+            }
+        out_val[0] = s_val[0];
+        out_idx[0] = s_idx[0];
+    }
+}
+
+}  // namespace l2b

@@ -1,0 +1,81 @@
+// Small kernels behind the isolated-operator entry points and the upload path.  They call the
+// same device functions as the fused decode kernels, so a parity test of an entry point is a
+// parity test of the arithmetic the token path uses.
+#pragma once
+#include "fused_matvec.cuh"
+
+namespace l2b {
+
+// q6_K file blocks (210 bytes: ql qh scales d) -> 208-byte records + fp16 scale array.
+__global__ void repack_q6k_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ rec, __half* __restrict__ d, int64_t nblocks) {
+    const int64_t total = nblocks * 105;  // 105 half-words per block
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t b = i / 105;
+        const int w = (int)(i % 105);
+        const uint16_t v = reinterpret_cast<const uint16_t*>(src)[b * 105 + w];  // 210*b is even
+        if (w < 104) reinterpret_cast<uint16_t*>(rec)[b * 104 + w] = v;
+        else d[b] = __ushort_as_half(v);
+    }
+}
+
+// dequantize! of n values from device-layout blocks.
+__global__ void dequantize_kernel(int type, const uint8_t* __restrict__ blocks, const __half* __restrict__ d6, int64_t n, float* __restrict__ out) {
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t b = i >> 8;
+        const int k = (int)(i & 255);
+        const uint8_t* blk = blocks + b * dev_block_bytes(type);
+        float v;
+        if (type == T_Q4_K) v = dequant_q45<false>(blk, k);
+        else if (type == T_Q5_K) v = dequant_q45<true>(blk, k);
+        else v = dequant_q6(blk, __half2float(d6[b]), k);
+        out[i] = v;
+    }
+}
+
+// Runs the prologue of the fused kernel on one block and exports what it built.
+// KQ: planes -> q [P][n] int8, dsc [P][n/256], sums [n/16].  else: the f32 vector.
+template <bool KQ, int P>
+__global__ void __launch_bounds__(256) export_activation_kernel(const __grid_constant__ MvParams p, int8_t* q_out, float* d_out, float* sums_out,
+                                                                 float* f_out) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+    const MvSmem L = mv_smem_layout(p.n_in, P, KQ, nwarps, 0, 0);
+    build_activation<KQ, P>(p, smem, L, warp, lane, nwarps);
+    const int n = p.n_in, nb = n / QK_K;
+    if (KQ) {
+        for (int i = threadIdx.x; i < P * n; i += blockDim.x) {
+            const int k = i / n, e = i % n;
+            q_out[i] = (int8_t)smem[L.off_act + k * L.plane_stride + (e >> 8) * ACT_STRIDE + (e & 255)];
+        }
+        for (int i = threadIdx.x; i < P * nb; i += blockDim.x) {
+            const int k = i / nb, b = i % nb;
+            d_out[i] = *reinterpret_cast<const float*>(smem + L.off_act + k * L.plane_stride + b * ACT_STRIDE + 256);
+        }
+        for (int i = threadIdx.x; i < nb * 16; i += blockDim.x) sums_out[i] = reinterpret_cast<const float*>(smem + L.off_xs)[i];
+    } else {
+        for (int i = threadIdx.x; i < n; i += blockDim.x) f_out[i] = reinterpret_cast<const float*>(smem + L.off_xf)[i];
+    }
+}
+
+// rope! on a [n_heads][hs] vector through the epilogue's rotation.
+__global__ void rope_kernel(float* x, int hs, int n_heads, int neox, const float* rope_cs_row) {
+    const int h2 = hs >> 1;
+    for (int t = blockIdx.x * blockDim.x + threadIdx.x; t < n_heads * h2; t += gridDim.x * blockDim.x) {
+        const int head = t / h2, i = t % h2;
+        const int ia = head * hs + (neox ? i : 2 * i), ib = head * hs + (neox ? i + h2 : 2 * i + 1);
+        const float vA = x[ia], vB = x[ib];
+        const float c = rope_cs_row[2 * i], s = rope_cs_row[2 * i + 1];
+        x[ia] = __fsub_rn(__fmul_rn(vA, c), __fmul_rn(vB, s));
+        x[ib] = __fadd_rn(__fmul_rn(vA, s), __fmul_rn(vB, c));
+    }
+}
+
+__global__ void swiglu_kernel(float* hb, const float* hb2, int64_t n) {
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+        const float v = hb[i];
+        const float g = v * (1.0f / (1.0f + expf(-v)));
+        hb[i] = g * hb2[i];
+    }
+}
+
+}  // namespace l2b

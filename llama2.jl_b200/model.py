@@ -1,0 +1,278 @@
+"""Host-side mirror of the reference's inference interface (src/inference.jl), bound to the C ABI.
+
+Names and argument meaning follow the reference: ModelConfig, TransformerLayerWeights,
+TransformerWeights, LanguageModel, matmul!, transformer!, sample.  Python differences:
+`!` becomes a trailing underscore, and token ids / positions are 0-based throughout (the
+reference is 1-based Julia).  Weight matrices are given as the reference stores them:
+`(in, out)` column-major, which is a C-contiguous numpy array of shape (out, in); k-quant
+matrices are `QuantMatrix` (raw super-block bytes, out rows of in/256 blocks).
+"""
+import ctypes as C
+import random
+import sys
+import time
+from dataclasses import dataclass, field
+from typing import List, Optional, Union
+
+import numpy as np
+
+from . import _lib as L
+
+
+@dataclass
+class ModelConfig:
+    """src/inference.jl:1-11 (no defaults there either)."""
+    dim: int
+    hidden_dim: int
+    n_layers: int
+    n_heads: int
+    n_kv_heads: int
+    vocab_size: int
+    seq_len: int
+    rope_freq_base: float
+    rope_is_neox: bool
+
+    def __str__(self):  # Base.show, src/inference.jl:13-25
+        rows = [("dim", self.dim), ("hidden_dim", self.hidden_dim), ("n_layers", self.n_layers), ("n_heads", self.n_heads),
+                ("n_kv_heads", self.n_kv_heads), ("vocab_size", self.vocab_size), ("seq_len", self.seq_len),
+                ("rope_freq_base", self.rope_freq_base), ("rope_is_neox", str(self.rope_is_neox).lower())]
+        return "ModelConfig(\n" + "".join(f"  {k:<14} = {v},\n" for k, v in rows) + ")"
+
+
+class QuantMatrix:
+    """AbstractMatrix{block_q4_K|block_q5_K|block_q6_K} of size (in/256, out) (src/kquants.jl:7-35):
+    `data` is a uint8 array of out * (in/256) * block_bytes raw bytes, rows contiguous."""
+
+    def __init__(self, ggml_type: int, data: np.ndarray, in_dim: int, out_dim: int):
+        if ggml_type not in L.BLOCK_BYTES:
+            raise L.L2BError(L.ERR_UNSUPPORTED_TYPE, f"tensor type {ggml_type} not implemented")
+        if in_dim % 256 != 0:
+            raise ValueError("in_dim % 256 must be 0")
+        self.ggml_type, self.in_dim, self.out_dim = ggml_type, in_dim, out_dim
+        self.data = np.ascontiguousarray(data).reshape(-1).view(np.uint8) if not isinstance(data, np.memmap) else data
+        expect = out_dim * (in_dim // 256) * L.BLOCK_BYTES[ggml_type]
+        if self.data.size != expect:
+            raise ValueError(f"expected {expect} bytes, got {self.data.size}")
+
+    def rows(self, start: int, stop: int) -> "QuantMatrix":
+        """view(A, :, start+1:stop): a contiguous range of output rows (src/load_gguf.jl:264-276)."""
+        rb = (self.in_dim // 256) * L.BLOCK_BYTES[self.ggml_type]
+        return QuantMatrix(self.ggml_type, self.data[start * rb:stop * rb], self.in_dim, stop - start)
+
+
+Matrix = Union[np.ndarray, QuantMatrix]
+
+
+def _matrix_info(a: Matrix):
+    if isinstance(a, QuantMatrix):
+        return a.ggml_type, a.data, a.in_dim, a.out_dim
+    a32 = np.ascontiguousarray(a, dtype=np.float32)
+    if a32.ndim != 2:
+        raise ValueError("f32 weight matrices are 2-D (out, in)")
+    return L.TYPE_F32, a32, a32.shape[1], a32.shape[0]
+
+
+@dataclass
+class TransformerLayerWeights:
+    """src/inference.jl:27-40."""
+    rms_att_weight: np.ndarray
+    rms_ffn_weight: np.ndarray
+    wq: Matrix
+    wk: Matrix
+    wv: Matrix
+    wo: Matrix
+    w1: Matrix
+    w2: Matrix
+    w3: Matrix
+
+
+@dataclass
+class TransformerWeights:
+    """src/inference.jl:42-48."""
+    token_embedding_table: Matrix
+    layers: List[TransformerLayerWeights]
+    rms_final_weight: np.ndarray
+    output_weight: Matrix
+
+
+class _DeviceModel:
+    """Owns an l2b_model and one l2b_session (RunState)."""
+
+    def __init__(self, config: ModelConfig, weights: TransformerWeights, act_planes=0, device=-1, stream=None):
+        lib = L.lib()
+        cfg = L.Config(dim=config.dim, hidden_dim=config.hidden_dim, n_layers=config.n_layers, n_heads=config.n_heads,
+                       n_kv_heads=config.n_kv_heads, vocab_size=config.vocab_size, seq_len=config.seq_len,
+                       rope_freq_base=float(config.rope_freq_base), rope_is_neox=int(bool(config.rope_is_neox)),
+                       act_planes=act_planes, device=device, tp_size=1, tp_rank=0)
+        self.model = C.c_void_p()
+        self.session = C.c_void_p()
+        L.check(lib.l2b_model_create(C.byref(cfg), C.byref(self.model)))
+        try:
+            def up(role, layer, a, vector=False):
+                if vector:
+                    v = np.ascontiguousarray(a, dtype=np.float32).reshape(-1)
+                    L.check(lib.l2b_model_upload_tensor(self.model, role, layer, L.TYPE_F32, L.ptr(v), v.size, 1))
+                else:
+                    t, data, i, o = _matrix_info(a)
+                    L.check(lib.l2b_model_upload_tensor(self.model, role, layer, t, L.ptr(data), i, o))
+            up(L.ROLE_TOKEN_EMBEDDING, 0, weights.token_embedding_table)
+            up(L.ROLE_OUTPUT, 0, weights.output_weight)
+            up(L.ROLE_RMS_FINAL, 0, weights.rms_final_weight, vector=True)
+            for l, w in enumerate(weights.layers):
+                up(L.ROLE_RMS_ATT, l, w.rms_att_weight, vector=True)
+                up(L.ROLE_RMS_FFN, l, w.rms_ffn_weight, vector=True)
+                for role, a in ((L.ROLE_WQ, w.wq), (L.ROLE_WK, w.wk), (L.ROLE_WV, w.wv), (L.ROLE_WO, w.wo),
+                                (L.ROLE_W1, w.w1), (L.ROLE_W2, w.w2), (L.ROLE_W3, w.w3)):
+                    up(role, l, a)
+            L.check(lib.l2b_model_finalize(self.model))
+            L.check(lib.l2b_session_create(self.model, stream, C.byref(self.session)))
+        except Exception:
+            self.close()
+            raise
+
+    def close(self):
+        lib = L.lib()
+        if self.session:
+            lib.l2b_session_destroy(self.session)
+            self.session = C.c_void_p()
+        if self.model:
+            lib.l2b_model_destroy(self.model)
+            self.model = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+class LanguageModel:
+    """src/inference.jl:50-54.  Constructible from plain arrays: LanguageModel(config, tokenizer, weights).
+
+    `act_planes` (1..3, 0 = library default 3) selects how many int8 planes represent an activation in the
+    k-quant integer dot products; the device copy of the weights is made on first use.
+    """
+
+    def __init__(self, config: ModelConfig, tokenizer, weights: TransformerWeights, act_planes: int = 0, device: int = -1, stream=None):
+        self.config, self.tokenizer, self.weights = config, tokenizer, weights
+        self.act_planes, self.device, self.stream = act_planes, device, stream
+        self._dev: Optional[_DeviceModel] = None
+
+    def device_model(self) -> _DeviceModel:
+        if self._dev is None:
+            self._dev = _DeviceModel(self.config, self.weights, self.act_planes, self.device, self.stream)
+        return self._dev
+
+    def close(self):
+        if self._dev is not None:
+            self._dev.close()
+            self._dev = None
+
+    def __str__(self):  # src/inference.jl:56-60
+        return "LanguageModel(\n" + str(self.config) + ")"
+
+    # -- measurement helpers --------------------------------------------------------------
+    def weight_bytes_per_token(self) -> int:
+        n = C.c_int64()
+        L.check(L.lib().l2b_model_weight_bytes(self.device_model().model, C.byref(n)))
+        return n.value
+
+    def kernels_per_token(self) -> int:
+        n = C.c_int32()
+        L.check(L.lib().l2b_session_kernels_per_token(self.device_model().session, C.byref(n)))
+        return n.value
+
+    def last_device_ms(self) -> float:
+        ms = C.c_float()
+        L.check(L.lib().l2b_session_last_device_ms(self.device_model().session, C.byref(ms)))
+        return ms.value
+
+
+class RunState:
+    """src/inference.jl:72-100: the per-call state.  Here it is a handle on the device session;
+    creating one zeroes the KV cache exactly like `RunState(config)`."""
+
+    def __init__(self, model: LanguageModel):
+        self.model = model
+        self.session = model.device_model().session
+        L.check(L.lib().l2b_session_reset(self.session))
+        self.logits = np.zeros(model.config.vocab_size, dtype=np.float32)
+
+
+def matmul_(y: np.ndarray, A: Matrix, x: np.ndarray, act_planes: int = 0) -> None:
+    """matmul!(y, A, x): y .= A' * x (src/matmul.jl:3-23).  x may hold several columns, shape (ncols, in)."""
+    t, data, i, o = _matrix_info(A)
+    x32 = np.ascontiguousarray(x, dtype=np.float32)
+    ncols = 1 if x32.ndim == 1 else x32.shape[0]
+    if x32.size != ncols * i:
+        raise ValueError("length(x) must equal the matrix input dimension")
+    if y.dtype != np.float32 or not y.flags.c_contiguous or y.size != ncols * o:
+        raise ValueError("y must be a contiguous float32 array of ncols * out elements")
+    L.check(L.lib().l2b_matvec(t, L.ptr(data), i, o, L.ptr(x32), ncols, L.ptr(y), act_planes))
+
+
+def dequantize(x: QuantMatrix) -> np.ndarray:
+    """dequantize(x) (src/kquants.jl:49-53)."""
+    n = x.in_dim * x.out_dim
+    y = np.zeros(n, dtype=np.float32)
+    L.check(L.lib().l2b_dequantize(x.ggml_type, L.ptr(x.data), n, L.ptr(y)))
+    return y
+
+
+def transformer_(token: int, pos: int, config: ModelConfig, s: RunState, weights: TransformerWeights = None) -> None:
+    """transformer!(token, pos, config, s, weights) (src/inference.jl:222-315): fills s.logits, advances the KV cache.
+    token and pos are 0-based."""
+    L.check(L.lib().l2b_forward(s.session, int(token), int(pos), L.ptr(s.logits)))
+
+
+def generate(model: LanguageModel, prompt_tokens, n_positions: int, temperature: float = 0.0, seed: int = 0):
+    """The loop of `sample` without text: returns (tokens chosen after each position, device milliseconds)."""
+    dev = model.device_model()
+    L.check(L.lib().l2b_session_reset(dev.session))
+    p = np.ascontiguousarray(prompt_tokens, dtype=np.int32)
+    out = np.zeros(n_positions, dtype=np.int32)
+    ms = C.c_float()
+    L.check(L.lib().l2b_generate(dev.session, L.ptr(p), p.size, n_positions, float(temperature), int(seed), L.ptr(out), C.byref(ms)))
+    return out, ms.value
+
+
+def _text(tok) -> str:
+    return tok.decode("utf-8", errors="replace") if isinstance(tok, (bytes, bytearray)) else tok
+
+
+def sample(model: LanguageModel, prompt: str = "", *, temperature: float = 0.9, stop_on_special_token: bool = True,
+           max_seq_len: int = sys.maxsize, bos_token: bool = True, rng: Optional[random.Random] = None, out=None) -> None:
+    """sample(model, prompt; temperature, stop_on_special_token, max_seq_len, bos_token) (src/inference.jl:317-395).
+
+    Prints the text and the achieved tok/s like the reference and returns None.  Each position is one
+    l2b_decode_next call (token id in, next token id out)."""
+    from .tokenizer import encode
+    out = out or sys.stdout
+    if not bos_token and prompt == "":
+        raise ValueError("Prompt cannot be empty if bos_token = false")
+    config, tokenizer = model.config, model.tokenizer
+    prompt_tokens = list(encode(prompt, tokenizer))
+    state = RunState(model)
+    rng = rng or random
+    time_start = time.perf_counter_ns()
+    if bos_token:
+        prompt_tokens.insert(0, tokenizer.bos_token_id)
+    else:
+        out.write(_text(tokenizer.id_to_token[prompt_tokens[0]]))
+    token = prompt_tokens[0]
+    generated_seq_len = 0
+    lib = L.lib()
+    nxt = C.c_int32()
+    for pos in range(min(config.seq_len, max_seq_len)):
+        L.check(lib.l2b_decode_next(state.session, int(token), pos, float(temperature), rng.random() if temperature != 0 else 0.0,
+                                    C.byref(nxt)))
+        generated_seq_len += 1
+        next_token = prompt_tokens[pos + 1] if pos + 1 < len(prompt_tokens) else nxt.value
+        if stop_on_special_token and next_token in (tokenizer.bos_token_id, tokenizer.eos_token_id):
+            break
+        out.write(_text(tokenizer.id_to_token[next_token]))
+        token = next_token
+    out.write("\n")
+    dt = time.perf_counter_ns() - time_start
+    out.write("-------\nachieved tok/s: %.2f\n" % (generated_seq_len / dt * 1e9))
+    return None
