@@ -207,7 +207,7 @@ static int32_t plan_matvec(MvLaunch& L, const DeviceInfo& di) {
     long ring_cap = cap - base;
     const long ring_min = env_long("L2B_MV_RING_MIN_KB", 56) * 1024;
     if (ring_cap < ring_min) ring_cap = ring_min;
-    if (base + ring_cap > di.max_smem_optin) ring_cap = di.max_smem_optin - base;
+    if (base + ring_cap > di.max_smem_optin - 1024) ring_cap = di.max_smem_optin - 1024 - base;
     int slots = (int)(ring_cap / slot);
     if (slots < 1) return fail(L2B_ERR_BAD_ARG, "input dimension too large for the activation planes to fit in shared memory");
     const int steps_per_block = (steps + L.grid - 1) / L.grid;
@@ -233,19 +233,22 @@ static int32_t plan_matvec(MvLaunch& L, const DeviceInfo& di) {
     L.warps = warps;
     p.nstages = nst;
     L.smem = mv_smem_layout(p.n_in, L.planes, true, warps, nst, max_bb).total;
-    if ((long)L.smem > di.max_smem_optin) return fail(L2B_ERR_BAD_ARG, "shared memory plan exceeds the device limit");
+    if ((long)L.smem > di.max_smem_optin - 1024) return fail(L2B_ERR_BAD_ARG, "shared memory plan exceeds the device limit");
     return L2B_OK;
 }
 
 static std::once_flag g_attr_once;
 static cudaError_t g_attr_err = cudaSuccess;
+static int32_t check_kernel_attrs();
 static void set_kernel_attrs() {
     std::call_once(g_attr_once, [] {
         int dev = 0, optin = 0;
         cudaGetDevice(&dev);
         cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev);
-        auto set = [&](const void* f) {
-            cudaError_t e = cudaFuncSetAttribute(f, cudaFuncAttributeMaxDynamicSharedMemorySize, optin);
+        auto set = [&](const void* f) {  // the opt-in limit covers static + dynamic shared memory
+            cudaFuncAttributes fa;
+            cudaError_t e = cudaFuncGetAttributes(&fa, f);
+            if (e == cudaSuccess) e = cudaFuncSetAttribute(f, cudaFuncAttributeMaxDynamicSharedMemorySize, optin - (int)fa.sharedSizeBytes);
             if (e != cudaSuccess) g_attr_err = e;
         };
         set((const void*)fused_matvec_kernel<true, 1>);
@@ -257,6 +260,12 @@ static void set_kernel_attrs() {
         set((const void*)export_activation_kernel<true, 3>);
         set((const void*)export_activation_kernel<false, 1>);
     });
+}
+
+static int32_t check_kernel_attrs() {
+    set_kernel_attrs();
+    if (g_attr_err != cudaSuccess) return fail(L2B_ERR_CUDA, std::string("cudaFuncSetAttribute: ") + cudaGetErrorString(g_attr_err));
+    return L2B_OK;
 }
 
 static cudaError_t launch_matvec(const MvLaunch& L, cudaStream_t st, bool pdl) {
@@ -656,8 +665,7 @@ extern "C" int32_t l2b_session_create(l2b_model* m, void* stream, l2b_session** 
     *out = nullptr;
     if (!m->finalized) return fail(L2B_ERR_STATE, "l2b_model_finalize has not been called");
     CU(cudaSetDevice(m->device));
-    set_kernel_attrs();
-    if (g_attr_err != cudaSuccess) return fail(L2B_ERR_CUDA, std::string("cudaFuncSetAttribute: ") + cudaGetErrorString(g_attr_err));
+    L2B_TRY(check_kernel_attrs());
     const l2b_config& c = m->cfg;
     const int hs = c.dim / c.n_heads;
     l2b_session* s = new l2b_session();
@@ -924,13 +932,13 @@ extern "C" int32_t l2b_dequantize(int32_t type, const void* host_blocks, int64_t
 
 // Run the fused kernel's prologue on one block and export what it built.
 static int32_t run_export(MvParams& p, bool kq, int planes, int8_t* q_out, float* d_out, float* sums_out, float* f_out) {
-    set_kernel_attrs();
+    L2B_TRY(check_kernel_attrs());
     const int warps = 8;
     const size_t smem = mv_smem_layout(p.n_in, planes, kq, warps, 0, 0).total;
     int optin = 0, dev = 0;
     CU(cudaGetDevice(&dev));
     CU(cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev));
-    if ((long)smem > optin) return fail(L2B_ERR_BAD_ARG, "vector too long for one block's shared memory");
+    if ((long)smem > optin - 1024) return fail(L2B_ERR_BAD_ARG, "vector too long for one block's shared memory");
     if (!kq) export_activation_kernel<false, 1><<<1, warps * 32, smem>>>(p, q_out, d_out, sums_out, f_out);
     else if (planes == 1) export_activation_kernel<true, 1><<<1, warps * 32, smem>>>(p, q_out, d_out, sums_out, f_out);
     else if (planes == 2) export_activation_kernel<true, 2><<<1, warps * 32, smem>>>(p, q_out, d_out, sums_out, f_out);
@@ -1106,7 +1114,7 @@ extern "C" int32_t l2b_matrix_create(int32_t type, const void* host_W, int64_t i
     *out = nullptr;
     if (out_dim % 2 != 0) return fail(L2B_ERR_BAD_ARG, "out_dim must be even");
     L2B_TRY(require_device());
-    set_kernel_attrs();
+    L2B_TRY(check_kernel_attrs());
     l2b_matrix* m = new l2b_matrix();
     cudaGetDevice(&m->device);
     int32_t st = query_device(m->di);
