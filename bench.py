@@ -1,0 +1,279 @@
+#!/usr/bin/env python
+"""Benchmark of the per-token decode path.
+
+Workload (default): the Llama-3-8B shape, Q4_K_S-style mix (q4_K, attn_v / ffn_down q5_K, output q6_K),
+seeded synthetic weights, a prompt of 128 random ids fed token by token followed by 256 greedy tokens,
+batch 1, seq_len 512 -- the configuration the headline metric is quoted on.  One "step" is that whole
+384-position run.  `value` is positions per second with everything resident on the device (CUDA events
+on the session stream around the token loop); `e2e` drives the same run one l2b_decode_next call per
+position with host token ids in and out.  On N > 1 GPUs every rank runs an independent replica
+(the shape fits one GPU; there is no exchange step), so `value` is the sum over ranks.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload 8b|tiny|phi3]
+"""
+import argparse
+import ctypes as C
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+METRIC = "decode tok/s @Llama-3-8B-shape Q4_K_S, batch 1; % of HBM roofline"
+
+
+def measured_peak():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return 6650.0, "fallback"
+
+
+class ClockSampler(threading.Thread):
+    """nvidia-smi clocks and throttle reasons, sampled while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        super().__init__(daemon=True)
+        self.index, self.rows, self.stop_flag = index, [], threading.Event()
+
+    def run(self):
+        while not self.stop_flag.is_set():
+            try:
+                out = subprocess.run(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-i", str(self.index)],
+                                     capture_output=True, text=True, timeout=5).stdout.strip()
+                if out:
+                    self.rows.append([c.strip() for c in out.split(",")])
+            except Exception:
+                pass
+            self.stop_flag.wait(0.2)
+
+    def summary(self):
+        self.stop_flag.set()
+        self.join(timeout=6)
+        if not self.rows:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
+        sm = sorted(float(r[0]) for r in self.rows if r[0].replace(".", "").isdigit())
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(r[2 + i].lower().startswith("active") for r in self.rows if len(r) > 2 + i)]
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": float(self.rows[0][1]) if self.rows[0][1].isdigit() else None,
+                "reasons": reasons, "samples": len(self.rows)}
+
+
+def workload_spec(synth, name):
+    if name == "8b":
+        return synth.LLAMA3_8B_Q4_K_S, "llama3-8b-shape Q4_K_S, 128 prompt ids + 256 greedy tokens, batch 1, seq_len 512"
+    if name == "tiny":
+        return synth.TINY_F32, "llama2.c f32 dim 288 x 6 layers, 16 prompt ids + 240 greedy tokens"
+    if name == "phi3":
+        return synth.PHI3_MINI_Q5_K_M, "phi3-mini-shape Q5_K_M, 2048 prompt ids + 512 greedy tokens, seq_len 4096"
+    raise SystemExit(f"unknown workload {name}")
+
+
+def kv_bytes_per_run(cfg, n_positions):
+    hs = cfg.dim // cfg.n_heads
+    per_pos = 2 * hs * cfg.n_kv_heads * 4 * cfg.n_layers  # f32 keys + values of one position, all layers
+    return per_pos * sum(p + 1 for p in range(n_positions))
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+    import __graft_entry__ as g
+    pkg = g.load_package()
+    from llama2_jl_b200 import _lib as L
+    from llama2_jl_b200 import synth
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    spec, wl_name = workload_spec(synth, args.workload)
+    cfg = spec["config"]
+    n_pos = spec["n_prompt"] + spec["n_decode"]
+    weights = synth.model_weights(cfg, spec["types"], seed=2024, tied_output=spec["tied"])
+    model = pkg.LanguageModel(cfg, None, weights, act_planes=args.act_planes, device=local)
+    prompt = synth.prompt_tokens(spec, 2024)
+    wbytes = model.weight_bytes_per_token()
+    kpt = model.kernels_per_token()
+    sess = model.device_model().session
+    lib = L.lib()
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    # ---- device-resident loop ------------------------------------------------------------------
+    for _ in range(args.warmup):
+        toks, _ = pkg.generate(model, prompt, n_pos)
+    sampler = ClockSampler(local)
+    sampler.start()
+    barrier()
+    dev_ms = 0.0
+    for _ in range(args.steps):
+        toks, ms = pkg.generate(model, prompt, n_pos)
+        dev_ms += ms
+    barrier()
+    clocks = sampler.summary()
+
+    # ---- end to end: one C-ABI call per position, host ids in and out ------------------------
+    nxt = C.c_int32()
+
+    def e2e_run():
+        L.check(lib.l2b_session_reset(sess))
+        tok = int(prompt[0])
+        out = []
+        for pos in range(n_pos):
+            L.check(lib.l2b_decode_next(sess, tok, pos, 0.0, 0.0, C.byref(nxt)))
+            tok = int(prompt[pos + 1]) if pos + 1 < len(prompt) else nxt.value
+            out.append(tok)
+        return out
+    e2e_steps = max(1, min(args.steps, 3))
+    stream = e2e_run()
+    assert stream == [int(t) for t in toks], "one-step and device-loop token streams differ"
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        e2e_run()
+    torch.cuda.synchronize()
+    e2e_s = time.perf_counter() - t0
+    barrier()
+
+    t = torch.tensor([dev_ms, e2e_s], dtype=torch.float64, device="cuda")
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    dev_ms, e2e_s = float(t[0]), float(t[1])
+    ms_per_step = dev_ms / args.steps
+    value = world * n_pos * args.steps / (dev_ms / 1e3)
+    e2e_value = world * n_pos * e2e_steps / e2e_s
+    peak, peak_kind = measured_peak()
+    algo_bytes = wbytes * n_pos + kv_bytes_per_run(cfg, n_pos)  # per step (one run)
+    achieved = algo_bytes / (ms_per_step / 1e3) / 1e9
+    line = {
+        "metric": METRIC, "value": round(value, 2), "unit": "tok/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": round(ms_per_step, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "int8 x k-quant integer dot products (dp4a), f32 accumulate; %d int8 activation plane(s)" % (args.act_planes or 3),
+        "data": "synthetic (seeded random weights and token ids)",
+        "config": {"workload": wl_name, "positions_per_step": n_pos, "act_planes": args.act_planes or 3,
+                   "l2": "inputs larger than L2 (%.2f GB of weights streamed per position)" % (wbytes / 1e9),
+                   "multi_gpu": "replicas only" if world > 1 else "single GPU"},
+        "e2e": {"value": round(e2e_value, 2), "unit": "tok/s", "h2d_bytes_per_step": 48 * n_pos, "d2h_bytes_per_step": 8 * n_pos,
+                "note": "one l2b_decode_next call per position, wall clock"},
+        "gpu_launches": kpt * n_pos * args.steps,
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s", "frac": round(achieved / peak, 4),
+                     "traffic": None, "peak_kind": peak_kind, "frac_of_nominal_8000": round(achieved / 8000.0, 4),
+                     "scope": "whole token (all kernels): weight + KV bytes per position / device time per position",
+                     "bytes_per_position": int(algo_bytes / n_pos)},
+        "clocks": clocks,
+        "us_per_token": round(ms_per_step * 1e3 / n_pos, 2),
+        "kernels_per_token": kpt,
+    }
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        line["cpu_baseline"] = cpu_baseline(pkg, synth, spec, args)
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    model.close()
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def oracle_positions_per_s(orc, synth, spec, n_layers, n_positions, seed=2024):
+    cfg = synth.scaled(spec, n_layers=n_layers)["config"]
+    w = synth.model_weights(cfg, spec["types"], seed=seed, tied_output=spec["tied"])
+    m = orc.OracleModel(cfg, w)
+    prompt = synth.tokens(n_positions, seed, 3, cfg.vocab_size)
+    m.sample_greedy(prompt, 1, acc=orc.ACC_LANES)  # touch the weights once
+    m.sample_greedy(prompt, n_positions, acc=orc.ACC_LANES)
+    return m.seconds / n_positions
+
+
+def cpu_baseline(pkg, synth, spec, args):
+    """The CPU oracle (a C++ port of the reference arithmetic) on this box's host cores, on a bounded sample:
+    the same shape with 2 layers and with 1 layer, a few positions each, extrapolated linearly to all layers."""
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    import oracle_binding as orc
+    full = spec["config"].n_layers
+    if full <= 8:
+        s = oracle_positions_per_s(orc, synth, spec, full, 16)
+        sample = f"all {full} layers, 16 positions"
+    else:
+        s2 = oracle_positions_per_s(orc, synth, spec, 2, 4)
+        s1 = oracle_positions_per_s(orc, synth, spec, 1, 4)
+        per_layer = max(s2 - s1, 1e-9)
+        s = s1 + per_layer * (full - 1)
+        sample = f"1- and 2-layer models of the same shape (full vocabulary), 4 positions each, extrapolated linearly to {full} layers"
+    return {"value": round(1.0 / s, 3), "unit": "tok/s", "cores": orc.NTHREADS, "kind": "port", "sample": sample}
+
+
+def run_reference(args):
+    """The reference's CPU implementation of the path.  Julia is not installed here, so this is the C++ oracle port of it,
+    with all host threads, on the benchmark's shape at full depth; one step = 2 positions."""
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if rank != 0:
+        return
+    import __graft_entry__ as g
+    pkg = g.load_package()
+    from llama2_jl_b200 import synth
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    import oracle_binding as orc
+    spec, wl_name = workload_spec(synth, args.workload)
+    cfg = spec["config"]
+    w = synth.model_weights(cfg, spec["types"], seed=2024, tied_output=spec["tied"])
+    m = orc.OracleModel(cfg, w)
+    per_step = 2
+    total = per_step * (args.steps + args.warmup)
+    prompt = synth.tokens(max(total, 2), 2024, 3, cfg.vocab_size)
+    m.reset()
+    pos = 0
+    for _ in range(args.warmup * per_step):
+        m.transformer(int(prompt[pos]), pos)
+        pos += 1
+    t0 = time.perf_counter()
+    for _ in range(args.steps * per_step):
+        m.transformer(int(prompt[pos]), pos)
+        pos += 1
+    dt = time.perf_counter() - t0
+    value = args.steps * per_step / dt
+    sample = f"{per_step} positions per step at full depth ({cfg.n_layers} layers), teacher-forced ids, {orc.NTHREADS} threads"
+    line = {"impl": "reference", "metric": METRIC, "value": round(value, 3), "unit": "tok/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": round(dt / args.steps * 1e3, 2), "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f32 (dequantised k-quant weights x f32 activations)", "data": "synthetic (seeded random weights and token ids)",
+            "config": {"workload": wl_name, "positions_per_step": per_step,
+                       "note": "Julia is absent on this box: C++ port of the reference's CPU arithmetic (oracle/), Threads.@threads-style row split"},
+            "cpu_baseline": {"value": round(value, 3), "unit": "tok/s", "cores": orc.NTHREADS, "kind": "port", "sample": sample},
+            "e2e": {"value": round(value, 3), "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=3)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="8b", choices=["8b", "tiny", "phi3"])
+    ap.add_argument("--act-planes", type=int, default=0, help="int8 planes per activation (1..3; 0 = library default 3)")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,12 +1,13 @@
-"""ctypes binding of the CPU oracle (oracle/liboracle.so) for the tests.  Test infrastructure only."""
+"""ctypes binding of the CPU oracle (liboracle.so, beside this file).  Test infrastructure only: imported by tests/,
+by the smoke check and by the CPU-baseline leg of bench.py; the library itself never loads it."""
 import ctypes as C
 import os
 import subprocess
 
 import numpy as np
 
-ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-_PATH = os.path.join(ROOT, "oracle", "liboracle.so")
+HERE = os.path.dirname(os.path.abspath(__file__))
+_PATH = os.path.join(HERE, "liboracle.so")
 ACC_SEQ, ACC_LANES, ACC_F64 = 0, 1, 2
 F32, Q4_K, Q5_K, Q6_K = 0, 12, 13, 14
 BLOCK_BYTES = {Q4_K: 144, Q5_K: 176, Q6_K: 210}
@@ -19,9 +20,9 @@ class _Config(C.Structure):
 
 
 def _load():
-    src = os.path.join(ROOT, "oracle", "oracle.cpp")
+    src = os.path.join(HERE, "oracle.cpp")
     if not os.path.exists(_PATH) or os.path.getmtime(_PATH) < os.path.getmtime(src):
-        subprocess.run(["make", "-s", "-C", os.path.join(ROOT, "oracle")], check=True)
+        subprocess.run(["make", "-s", "-C", HERE], check=True)
     lib = C.CDLL(_PATH)
     P = C.c_void_p
     sig = {
