@@ -83,7 +83,56 @@ def kv_bytes_per_run(cfg, n_positions):
     return per_pos * sum(p + 1 for p in range(n_positions))
 
 
+def run_matvec(args):
+    """Isolated operator: W 14336 x 4096 as k-quant super-blocks, x f32[4096] quantised on the device, batch 1.
+    Eight copies of W (more than the L2) are rotated through, so every launch streams its weights from HBM."""
+    import torch
+    import __graft_entry__ as g
+    pkg = g.load_package()
+    from llama2_jl_b200 import _lib as L
+    from llama2_jl_b200 import synth
+    torch.cuda.set_device(0)
+    t = {"matvec-q4k": 12, "matvec-q5k": 13, "matvec-q6k": 14}[args.workload]
+    n_in, n_out, copies = args.matvec_in, args.matvec_out, args.matvec_copies
+    A = synth.matrix(t, n_in, n_out, seed=77)
+    x = torch.from_numpy(synth.normal_f32(n_in, 78, 1.0)).cuda()
+    y = torch.zeros(n_out, dtype=torch.float32, device="cuda")
+    h = C.c_void_p()
+    L.check(L.lib().l2b_matrix_create(t, L.ptr(A.data), n_in, n_out, copies, C.byref(h)))
+    stream = torch.cuda.current_stream().cuda_stream
+    planes = args.act_planes or 3
+    launches = args.matvec_launches
+
+    def run(n):
+        for i in range(n):
+            L.check(L.lib().l2b_matrix_matvec_device(h, i % copies, x.data_ptr(), y.data_ptr(), planes, stream))
+    run(args.warmup * copies)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ms = 0.0
+    for _ in range(args.steps):
+        e0.record()
+        run(launches)
+        e1.record()
+        torch.cuda.synchronize()
+        ms += e0.elapsed_time(e1)
+    us = ms * 1e3 / (args.steps * launches)
+    nbytes = (n_in // 256) * n_out * L.BLOCK_BYTES[t]
+    peak, kind = measured_peak()
+    line = {"metric": "k-quant dequant-matvec, batch 1", "value": round(us, 3), "unit": "us per matvec", "n_gpus": 1, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": round(ms / args.steps, 4), "higher_is_better": False, "vs_baseline": None,
+            "dtype": f"int8 x k-quant integer dot products (dp4a), f32 accumulate; {planes} int8 activation plane(s)",
+            "data": "synthetic", "config": {"workload": f"{args.workload} W {n_out}x{n_in}, {copies} rotating copies, {launches} launches per step"},
+            "gpu_launches": args.steps * launches,
+            "roofline": {"bound": "hbm", "achieved": round(nbytes / us / 1e3, 1), "peak": peak, "unit": "GB/s",
+                         "frac": round(nbytes / us / 1e3 / peak, 4), "traffic": None, "peak_kind": kind, "bytes_per_launch": nbytes}}
+    print(json.dumps(line), flush=True)
+    L.lib().l2b_matrix_destroy(h)
+
+
 def run_ours(args):
+    if args.workload.startswith("matvec"):
+        return run_matvec(args)
     import torch
     import torch.distributed as dist
     import __graft_entry__ as g
@@ -100,9 +149,12 @@ def run_ours(args):
     spec, wl_name = workload_spec(synth, args.workload)
     cfg = spec["config"]
     n_pos = spec["n_prompt"] + spec["n_decode"]
+    if args.positions > 0:  # shortened run (profiling captures); not the benchmark configuration
+        n_pos = args.positions
+        wl_name += f" [shortened to {n_pos} positions]"
     weights = synth.model_weights(cfg, spec["types"], seed=2024, tied_output=spec["tied"])
     model = pkg.LanguageModel(cfg, None, weights, act_planes=args.act_planes, device=local)
-    prompt = synth.prompt_tokens(spec, 2024)
+    prompt = synth.prompt_tokens(spec, 2024)[:n_pos]
     wbytes = model.weight_bytes_per_token()
     kpt = model.kernels_per_token()
     sess = model.device_model().session
@@ -264,9 +316,14 @@ def main():
     ap.add_argument("--steps", type=int, default=3)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="8b", choices=["8b", "tiny", "phi3"])
+    ap.add_argument("--workload", default="8b", choices=["8b", "tiny", "phi3", "matvec-q4k", "matvec-q5k", "matvec-q6k"])
+    ap.add_argument("--matvec-in", type=int, default=4096)
+    ap.add_argument("--matvec-out", type=int, default=14336)
+    ap.add_argument("--matvec-copies", type=int, default=8)
+    ap.add_argument("--matvec-launches", type=int, default=64)
     ap.add_argument("--act-planes", type=int, default=0, help="int8 planes per activation (1..3; 0 = library default 3)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--positions", type=int, default=0, help="run only this many positions per step (for profiler captures)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.impl == "reference":

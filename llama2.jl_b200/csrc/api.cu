@@ -159,23 +159,18 @@ struct MvLaunch {
     size_t smem = 0;
 };
 
+// Lanes per row pair (log2).  A lane takes half a super-block, so a pair uses 2*GB lanes for GB blocks per turn.
+// GB is the power of two covering a row of nb blocks, at most 16: wide turns keep the bulk copies large (a
+// copy brings GB blocks of one row), which matters more than a few idle lanes in the last turn.
 static int choose_lgG(int nb) {
-    int best = 1;
-    double best_waste = 1e9;
-    for (int lg = 1; lg <= 5; ++lg) {
-        const int G = 1 << lg;
-        const int its = (nb + G - 1) / G;
-        const double waste = (double)(its * G) / nb;
-        if (waste < best_waste - 1e-9 || (fabs(waste - best_waste) < 1e-9 && lg > best)) {
-            best_waste = waste;
-            best = lg;
-        }
-    }
-    return best;
+    int lg = 1;
+    while (lg < 5 && ((1 << lg) >> 1) < nb) ++lg;
+    return lg;
 }
 
-// Decide grid, warps per block, ring depth and shared memory for a launch whose segments, n_in,
-// prologue and epilogue fields are already filled in.
+// Decide grid, consumer warps, ring slots and shared memory for a launch whose segments, n_in, prologue and
+// epilogue fields are already filled in, and precompute the schedule constants the kernel would otherwise
+// derive with serial integer arithmetic.
 static int32_t plan_matvec(MvLaunch& L, const DeviceInfo& di) {
     MvParams& p = L.p;
     L.kq = p.seg[0].type != T_F32;
@@ -183,57 +178,47 @@ static int32_t plan_matvec(MvLaunch& L, const DeviceInfo& di) {
         if ((p.seg[s].type != T_F32) != L.kq) return fail(L2B_ERR_UNSUPPORTED_TYPE, "f32 and k-quant matrices cannot share one launch");
     p.planes = L.planes;
     L.grid = di.sms;
-    if (!L.kq) {
-        int steps = 0;
-        for (int s = 0; s < p.nseg; ++s) steps += p.seg[s].npairs;
-        p.lgG = 5;
-        p.nstages = 0;
-        int w = (steps + L.grid - 1) / L.grid;
-        L.warps = std::max(4, std::min(MV_MAX_WARPS, w));
-        L.smem = mv_smem_layout(p.n_in, 1, false, L.warps, 0, 0).total;
-        return L2B_OK;
-    }
     const int nb = p.n_in / QK_K;
-    p.lgG = choose_lgG(nb);
-    const int G = 1 << p.lgG, PW = 32 >> p.lgG, nit = (nb + G - 1) / G;
+    p.lgG = L.kq ? choose_lgG(nb) : 5;
+    const int GB = (1 << p.lgG) >> 1, lgPW = L.kq ? 5 - p.lgG : 0, PW = 1 << lgPW;
+    p.nit = L.kq ? (nb + GB - 1) / GB : 1;
     int steps = 0, max_bb = 0;
     for (int s = 0; s < p.nseg; ++s) {
+        p.seg_start[s] = steps;
         steps += (p.seg[s].npairs + PW - 1) / PW;
         max_bb = std::max(max_bb, dev_block_bytes(p.seg[s].type));
+        if (p.seg[s].pair_mode == PAIR_NEOX) p.neox_magic = (unsigned)((0x100000000ull + (p.seg[s].head_size / 2) - 1) / (p.seg[s].head_size / 2));
     }
-    const int slot = 64 * max_bb;
-    const int base = mv_smem_layout(p.n_in, L.planes, true, 0, 0, max_bb).total;
-    const long cap = env_long("L2B_MV_SMEM_KB", 112) * 1024;
-    long ring_cap = cap - base;
-    const long ring_min = env_long("L2B_MV_RING_MIN_KB", 56) * 1024;
-    if (ring_cap < ring_min) ring_cap = ring_min;
-    if (base + ring_cap > di.max_smem_optin - 1024) ring_cap = di.max_smem_optin - 1024 - base;
-    int slots = (int)(ring_cap / slot);
-    if (slots < 1) return fail(L2B_ERR_BAD_ARG, "input dimension too large for the activation planes to fit in shared memory");
-    const int steps_per_block = (steps + L.grid - 1) / L.grid;
-    const long stages_per_block = (long)steps_per_block * nit;
-    // One slot per warp, or two when a block has enough stages for every warp to overlap a copy with
-    // its arithmetic.  At least four warps so the prologue has hands.
-    const int warp_cap = (int)std::min<long>(MV_MAX_WARPS, env_long("L2B_MV_WARPS", MV_MAX_WARPS));
-    int nst = 1;
-    int warps = std::min(warp_cap, std::min(slots, std::max(steps_per_block, 4)));
-    {
-        const int w2 = std::min(warp_cap, std::min(slots / 2, std::max(steps_per_block, 4)));
-        if (w2 >= 4 && stages_per_block >= 2L * w2) {
-            warps = w2;
-            nst = 2;
-        }
+    p.seg_start[p.nseg] = steps;
+    if (steps < L.grid) L.grid = std::max(1, steps);
+    p.steps_lo = steps / L.grid;
+    p.steps_rem = steps % L.grid;
+    const int cta_steps = p.steps_lo + (p.steps_rem ? 1 : 0);
+    // consumer warps: as few rounds as possible, spread evenly; at least 4 so the prologue has hands
+    const int max_cons = (int)std::min<long>(L.kq ? MV_MAX_WARPS - 1 : MV_MAX_WARPS, env_long("L2B_MV_WARPS", MV_MAX_WARPS));
+    const int rounds = (cta_steps + max_cons - 1) / max_cons;
+    int W = (cta_steps + rounds - 1) / rounds;
+    W = std::max(std::min(4, max_cons), std::min(W, max_cons));
+    p.consumers = W;
+    p.turns = (p.n_in / 8 + 32 * W - 1) / (32 * W);
+    L.warps = W + (L.kq ? 1 : 0);
+    if (!L.kq) {
+        p.nst = 0;
+        L.smem = mv_smem_layout(p.n_in, 1, false, 0, 0).total;
+        if ((long)L.smem > di.max_smem_optin - 1024) return fail(L2B_ERR_BAD_ARG, "input vector too long for shared memory");
+        return L2B_OK;
     }
-    const long force_nst = env_long("L2B_MV_STAGES", 0);
-    if (force_nst > 0) {
-        nst = (int)std::min<long>(force_nst, MV_MAX_STAGES);
-        warps = std::max(1, std::min(warp_cap, std::min(slots / nst, std::max(steps_per_block, 4))));
-    }
-    if (warps < 1) warps = 1;
-    L.warps = warps;
-    p.nstages = nst;
-    L.smem = mv_smem_layout(p.n_in, L.planes, true, warps, nst, max_bb).total;
-    if ((long)L.smem > di.max_smem_optin - 1024) return fail(L2B_ERR_BAD_ARG, "shared memory plan exceeds the device limit");
+    // ring: every consumer warp owns nst slots of 32 super-blocks; as deep as the shared-memory budget allows (max 4)
+    const int slot = 32 * max_bb;
+    const long base = mv_smem_layout(p.n_in, L.planes, true, 0, max_bb).total;
+    long cap = std::min<long>(env_long("L2B_MV_SMEM_KB", 200) * 1024, di.max_smem_optin - 1024);
+    const long stages_per_warp = (long)((cta_steps + W - 1) / W) * p.nit;
+    int nst = (int)std::min<long>(4, std::min<long>(stages_per_warp, (cap - base) / ((long)slot * W)));
+    const long force = env_long("L2B_MV_STAGES", 0);
+    if (force > 0) nst = (int)std::min<long>(std::min<long>(force, 4), (di.max_smem_optin - 1024 - base) / ((long)slot * W));
+    if (nst < 1) return fail(L2B_ERR_BAD_ARG, "input dimension too large for the activation planes to fit in shared memory");
+    p.nst = nst;
+    L.smem = mv_smem_layout(p.n_in, L.planes, true, W * nst, max_bb).total;
     return L2B_OK;
 }
 
@@ -350,9 +335,10 @@ struct l2b_session {
     bool own_stream = false;
     DeviceInfo di;
     // activations
-    float *x = nullptr, *q = nullptr, *hb = nullptr, *logits = nullptr;
+    float *x = nullptr, *q = nullptr, *att = nullptr, *hb = nullptr, *logits = nullptr;
     float *kc = nullptr, *vc = nullptr;  // [layer][kv_head][seq_len][hs]
     float *part_m = nullptr, *part_l = nullptr, *part_acc = nullptr;
+    int* tickets = nullptr;
     float* amax_val = nullptr;
     int* amax_idx = nullptr;
     float* rope_cs = nullptr;
@@ -519,7 +505,7 @@ extern "C" int32_t l2b_model_weight_bytes(const l2b_model* m, int64_t* bytes) {
 static void session_free(l2b_session* s) {
     if (!s) return;
     if (s->graph) cudaGraphExecDestroy(s->graph);
-    void* bufs[] = {s->x, s->q, s->hb, s->logits, s->kc, s->vc, s->part_m, s->part_l, s->part_acc, s->amax_val, s->amax_idx,
+    void* bufs[] = {s->x, s->q, s->att, s->tickets, s->hb, s->logits, s->kc, s->vc, s->part_m, s->part_l, s->part_acc, s->amax_val, s->amax_idx,
                     s->rope_cs, s->ctl, s->status, s->prompt, s->out_tokens, s->next_token};
     for (void* b : bufs)
         if (b) cudaFree(b);
@@ -531,18 +517,22 @@ static void session_free(l2b_session* s) {
     delete s;
 }
 
+struct l2b_session;
+static cudaError_t cudaLaunchKernelEx_embed(const l2b_model* m, l2b_session* s, int blocks, int threads);
+
 // Enqueue every kernel of one token on the session stream (this is what the graph captures).
 static int32_t enqueue_token(l2b_session* s, int* nlaunch) {
     const l2b_model* m = s->model;
     const l2b_config& c = m->cfg;
     const int hs = c.dim / c.n_heads;
     const size_t kvl = kv_layer_elems(c);
-    int count = 0;
+    int count = 0, last_grid = 0;
     bool first = true;
     auto mv = [&](MvLaunch& L) -> int32_t {
         L.planes = m->planes;
         L2B_TRY(plan_matvec(L, s->di));
         CU(launch_matvec(L, s->stream, !first));
+        last_grid = L.grid;
         first = false;
         ++count;
         return L2B_OK;
@@ -551,12 +541,18 @@ static int32_t enqueue_token(l2b_session* s, int* nlaunch) {
         memset(&L.p, 0, sizeof(L.p));
         L.p.n_in = n_in;
         L.p.pos = &s->ctl->pos;
-        L.p.token = &s->ctl->token;
         L.p.rope_cs = s->rope_cs;
         L.p.seq_len = c.seq_len;
         L.p.status = s->status;
     };
     const int rope_mode = c.rope_is_neox ? PAIR_NEOX : PAIR_ADJACENT;
+    // --- token embedding row -> residual stream (inference.jl:236)
+    {
+        const int threads = 256, blocks = std::max(1, std::min(32, c.dim / 256));
+        CU(cudaLaunchKernelEx_embed(m, s, blocks, threads));
+        first = false;
+        ++count;
+    }
     for (int l = 0; l < c.n_layers; ++l) {
         const LayerW& w = m->layers[l];
         float* kcl = s->kc + (size_t)l * kvl;
@@ -572,16 +568,8 @@ static int32_t enqueue_token(l2b_session* s, int* nlaunch) {
                 for (int i = 0; i < 3; ++i)
                     if ((segs[i].type == T_F32) == (cls == 0)) L.p.seg[L.p.nseg++] = segs[i];
                 if (L.p.nseg == 0) continue;
-                if (l == 0) {
-                    L.p.pro = PRO_EMBED_RMSNORM;
-                    L.p.emb = m->tok_emb.data;
-                    L.p.emb_d6 = m->tok_emb.d6;
-                    L.p.emb_type = m->tok_emb.type;
-                    L.p.x_out = s->x;
-                } else {
-                    L.p.pro = PRO_RMSNORM;
-                    L.p.x_in = s->x;
-                }
+                L.p.pro = PRO_RMSNORM;
+                L.p.x_in = s->x;
                 L.p.gain = w.rms_att;
                 L2B_TRY(mv(L));
             }
@@ -590,7 +578,7 @@ static int32_t enqueue_token(l2b_session* s, int* nlaunch) {
         {
             AttnParams a;
             memset(&a, 0, sizeof(a));
-            a.q = s->q; a.kc = kcl; a.vc = vcl;
+            a.q = s->q; a.kc = kcl; a.vc = vcl; a.out = s->att; a.tickets = s->tickets;
             a.part_m = s->part_m; a.part_l = s->part_l; a.part_acc = s->part_acc;
             a.pos = &s->ctl->pos;
             a.n_heads = c.n_heads; a.n_kv = c.n_kv_heads; a.hs = hs; a.seq_len = c.seq_len; a.nsplit = s->nsplit;
@@ -602,10 +590,8 @@ static int32_t enqueue_token(l2b_session* s, int* nlaunch) {
             MvLaunch L;
             base_params(L, c.dim);
             L.p.seg[L.p.nseg++] = make_segment(w.wo, PAIR_ADJACENT, EPI_RESIDUAL, s->x, hs);
-            L.p.pro = PRO_ATTN_MERGE;
-            L.p.part_m = s->part_m; L.p.part_l = s->part_l; L.p.part_acc = s->part_acc;
-            L.p.nsplit = s->nsplit;
-            L.p.attn_head_size = hs;
+            L.p.pro = PRO_COPY;
+            L.p.x_in = s->att;
             L.p.resid = s->x;
             L2B_TRY(mv(L));
         }
@@ -651,13 +637,23 @@ static int32_t enqueue_token(l2b_session* s, int* nlaunch) {
         FinalizeParams f;
         memset(&f, 0, sizeof(f));
         f.logits = s->logits; f.vocab = c.vocab_size;
-        f.amax_val = s->amax_val; f.amax_idx = s->amax_idx; f.nparts = s->di.sms;
+        f.amax_val = s->amax_val; f.amax_idx = s->amax_idx; f.nparts = last_grid;
         f.ctl = s->ctl; f.prompt = s->prompt; f.out_tokens = s->out_tokens; f.advance = 1; f.next_token = s->next_token;
         CU(launch_kernel(finalize_token_kernel, dim3(1), dim3(FIN_THREADS), 0, s->stream, true, f));
         ++count;
     }
     if (nlaunch) *nlaunch = count;
     return L2B_OK;
+}
+
+static cudaError_t cudaLaunchKernelEx_embed(const l2b_model* m, l2b_session* s, int blocks, int threads) {
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = dim3(blocks);
+    cfg.blockDim = dim3(threads);
+    cfg.stream = s->stream;
+    return cudaLaunchKernelEx(&cfg, embed_row_kernel, m->tok_emb.type, (const uint8_t*)m->tok_emb.data, (const __half*)m->tok_emb.d6,
+                              (const int*)&s->ctl->token, (int)m->cfg.dim, s->x);
 }
 
 extern "C" int32_t l2b_session_create(l2b_model* m, void* stream, l2b_session** out) {
@@ -690,6 +686,8 @@ extern "C" int32_t l2b_session_create(l2b_model* m, void* stream, l2b_session** 
         const size_t kvl = kv_layer_elems(c);
         CU(cudaMalloc(&s->x, (size_t)c.dim * 4));
         CU(cudaMalloc(&s->q, (size_t)c.dim * 4));
+        CU(cudaMalloc(&s->att, (size_t)c.dim * 4));
+        CU(cudaMalloc(&s->tickets, (size_t)c.n_heads * 4));
         CU(cudaMalloc(&s->hb, (size_t)c.hidden_dim * 4));
         CU(cudaMalloc(&s->logits, (size_t)c.vocab_size * 4));
         CU(cudaMalloc(&s->kc, kvl * c.n_layers * 4));
@@ -711,6 +709,7 @@ extern "C" int32_t l2b_session_create(l2b_model* m, void* stream, l2b_session** 
         CU(cudaMemsetAsync(s->kc, 0, kvl * c.n_layers * 4, s->stream));
         CU(cudaMemsetAsync(s->vc, 0, kvl * c.n_layers * 4, s->stream));
         CU(cudaMemsetAsync(s->status, 0, 4, s->stream));
+        CU(cudaMemsetAsync(s->tickets, 0, (size_t)c.n_heads * 4, s->stream));
         CU(cudaMemsetAsync(s->ctl, 0, sizeof(Control), s->stream));
         CU(cudaMemsetAsync(s->prompt, 0, (size_t)c.seq_len * 4, s->stream));
         std::vector<float> cs;
@@ -934,7 +933,9 @@ extern "C" int32_t l2b_dequantize(int32_t type, const void* host_blocks, int64_t
 static int32_t run_export(MvParams& p, bool kq, int planes, int8_t* q_out, float* d_out, float* sums_out, float* f_out) {
     L2B_TRY(check_kernel_attrs());
     const int warps = 8;
-    const size_t smem = mv_smem_layout(p.n_in, planes, kq, warps, 0, 0).total;
+    const size_t smem = mv_smem_layout(p.n_in, planes, kq, 0, 0).total;
+    p.consumers = warps;
+    p.turns = (p.n_in / 8 + 32 * warps - 1) / (32 * warps);
     int optin = 0, dev = 0;
     CU(cudaGetDevice(&dev));
     CU(cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev));
@@ -1019,7 +1020,7 @@ extern "C" int32_t l2b_attention(float* host_out, const float* host_q, const flo
         }
     const int gq = choose_gq(n_heads, n_kv);
     const int nsplit = std::max(1, std::min(32, std::min((n_pos + 7) / 8, (int)env_long("L2B_ATTN_SPLITS", 16))));
-    DevBuf q, k, v, pm, pl, pa, out;
+    DevBuf q, k, v, pm, pl, pa, out, tickets;
     L2B_TRY(dev_upload(q, host_q, (size_t)n_heads * hs * 4));
     L2B_TRY(dev_upload(k, kc.data(), kc.size() * 4));
     L2B_TRY(dev_upload(v, vc.data(), vc.size() * 4));
@@ -1027,20 +1028,15 @@ extern "C" int32_t l2b_attention(float* host_out, const float* host_q, const flo
     L2B_TRY(dev_alloc(pl, (size_t)n_heads * nsplit * 4));
     L2B_TRY(dev_alloc(pa, (size_t)n_heads * nsplit * hs * 4));
     L2B_TRY(dev_alloc(out, (size_t)n_heads * hs * 4));
+    L2B_TRY(dev_alloc(tickets, (size_t)n_heads * 4));
+    CU(cudaMemset(tickets.p, 0, (size_t)n_heads * 4));
     AttnParams a;
     memset(&a, 0, sizeof(a));
-    a.q = q.as<float>(); a.kc = k.as<float>(); a.vc = v.as<float>();
-    a.part_m = pm.as<float>(); a.part_l = pl.as<float>(); a.part_acc = pa.as<float>();
+    a.q = q.as<float>(); a.kc = k.as<float>(); a.vc = v.as<float>(); a.out = out.as<float>();
+    a.part_m = pm.as<float>(); a.part_l = pl.as<float>(); a.part_acc = pa.as<float>(); a.tickets = tickets.as<int>();
     a.n_heads = n_heads; a.n_kv = n_kv; a.hs = hs; a.seq_len = n_pos; a.nsplit = nsplit; a.npos_override = n_pos;
     CU(launch_attention(a, gq, 0, false));
-    MvParams p;
-    memset(&p, 0, sizeof(p));
-    p.n_in = n_heads * hs;
-    p.pro = PRO_ATTN_MERGE;
-    p.part_m = a.part_m; p.part_l = a.part_l; p.part_acc = a.part_acc;
-    p.nsplit = nsplit;
-    p.attn_head_size = hs;
-    L2B_TRY(run_export(p, false, 1, nullptr, nullptr, nullptr, out.as<float>()));
+    CU(cudaDeviceSynchronize());
     CU(cudaMemcpy(host_out, out.p, (size_t)n_heads * hs * 4, cudaMemcpyDeviceToHost));
     return L2B_OK;
 }
@@ -1102,6 +1098,8 @@ extern "C" int32_t l2b_sample_temperature(const float* host_logits, int64_t n, f
 // ---------------------------------------------------------------------------------------------
 // resident matrices
 // ---------------------------------------------------------------------------------------------
+static unsigned long long* g_trace = nullptr;  // set only by the L2B_MV_TRACE debugging path
+
 struct l2b_matrix {
     std::vector<DevMatrix> copies;
     int device = 0;
@@ -1153,6 +1151,7 @@ extern "C" int32_t l2b_matrix_matvec_device(l2b_matrix* m, int32_t copy, const f
     L.p.pro = PRO_COPY;
     L.p.x_in = dev_x;
     L.p.status = m->status;
+    L.p.trace = g_trace;
     L2B_TRY(plan_matvec(L, m->di));
     CU(launch_matvec(L, (cudaStream_t)stream, false));
     return L2B_OK;
@@ -1168,6 +1167,28 @@ extern "C" int32_t l2b_matrix_matvec(l2b_matrix* m, const float* host_x, int32_t
     for (int c = 0; c < ncols; ++c)
         L2B_TRY(l2b_matrix_matvec_device(m, 0, x.as<float>() + (size_t)c * w.in, y.as<float>() + (size_t)c * w.out, planes, nullptr));
     CU(cudaDeviceSynchronize());
+    if (env_long("L2B_MV_TRACE", 0)) {  // debugging aid: per-block timeline of one more launch, printed to stderr
+        DevBuf tr;
+        L2B_TRY(dev_alloc(tr, (size_t)m->di.sms * 8 * 8));
+        CU(cudaMemset(tr.p, 0, (size_t)m->di.sms * 8 * 8));
+        g_trace = tr.as<unsigned long long>();
+        for (int rep = 0; rep < 3; ++rep) L2B_TRY(l2b_matrix_matvec_device(m, 0, x.as<float>(), y.as<float>(), planes, nullptr));
+        g_trace = nullptr;
+        CU(cudaDeviceSynchronize());
+        std::vector<unsigned long long> h((size_t)m->di.sms * 8);
+        CU(cudaMemcpy(h.data(), tr.p, h.size() * 8, cudaMemcpyDeviceToHost));
+        unsigned long long t0 = ~0ull;
+        for (int b = 0; b < m->di.sms; ++b) t0 = std::min(t0, h[b * 8]);
+        double mx[8] = {0}, av[8] = {0};
+        for (int b = 0; b < m->di.sms; ++b)
+            for (int i = 0; i < 8; ++i) {
+                const double v = (double)(h[b * 8 + i] - t0);
+                mx[i] = std::max(mx[i], v);
+                av[i] += v / m->di.sms;
+            }
+        fprintf(stderr, "[l2b trace] ns since first block start (avg/max): start %.0f/%.0f barriers-ready %.0f issued %.0f/%.0f waited %.0f/%.0f act %.0f/%.0f stage0-landed %.0f/%.0f stage0-done %.0f/%.0f end %.0f/%.0f\n",
+                av[0], mx[0], av[7], av[1], mx[1], av[2], mx[2], av[3], mx[3], av[4], mx[4], av[5], mx[5], av[6], mx[6]);
+    }
     int hst = 0;
     CU(cudaMemcpy(&hst, m->status, 4, cudaMemcpyDeviceToHost));
     if (hst != DEV_OK) {

@@ -4,9 +4,11 @@
 //
 // Grid: (n_heads / GQ) * nsplit blocks.  Block (hg, sp) reads the keys and values of positions
 // [sp*chunk, (sp+1)*chunk) of one kv head exactly once and serves GQ query heads that share
-// it (GQ = n_heads / n_kv_heads when that is 1, 2, 4 or 8; otherwise GQ = 1).  Each warp walks positions with an online softmax; warps are
-// merged in shared memory; the block writes (max, sum, unnormalised output) per query head.
-// The merge over splits happens in the prologue of the kernel that consumes the result.
+// it (GQ = n_heads / n_kv_heads when that is 1, 2, 4 or 8; otherwise GQ = 1).  Each warp walks
+// positions with an online softmax, several positions' loads in flight at a time; warps are
+// merged in shared memory; the block writes (max, sum, unnormalised output) per query head to
+// scratch memory.  The block that finishes last for a head group (an atomic ticket) merges the
+// nsplit partial results and writes the attention output, so no further kernel is needed.
 //
 // Cache layout (private to the library): key and value caches are [kv_head][seq_len][head_size]
 // f32 (the reference keeps values transposed, (seq, hs, kv); both are f32).
@@ -19,20 +21,22 @@ struct AttnParams {
     const float* q;   // [n_heads][hs], after RoPE
     const float* kc;  // layer's key cache
     const float* vc;  // layer's value cache
+    float* out;       // [n_heads][hs] attention output
+    // scratch (global memory beyond inputs and outputs)
     float* part_m;    // [n_heads][nsplit]
     float* part_l;    // [n_heads][nsplit]
     float* part_acc;  // [n_heads][nsplit][hs]
+    int* tickets;     // [n_heads / GQ], zero before the launch; left zero after it
     const int* pos;   // device scalar, 0-based position of the query; positions 0..pos are attended
     int n_heads, n_kv, hs, seq_len, nsplit;
     int npos_override;  // >0: attend exactly this many positions (isolated-operator entry point)
 };
 
 constexpr int ATTN_WARPS = 4;
+constexpr int ATTN_UNROLL = 4;  // positions whose key/value loads a warp keeps in flight
 
 template <int GQ>  // query heads served per block; GQ divides n_heads / n_kv
-__global__ void __launch_bounds__(ATTN_WARPS * 32) attention_split_kernel(const __grid_constant__ AttnParams p) {
-    pdl_launch_dependents();
-    pdl_wait();
+__device__ __forceinline__ void attention_split_body(const AttnParams& p) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int hg = blockIdx.x / p.nsplit, sp = blockIdx.x % p.nsplit;
     const int kvh = (hg * GQ) / (p.n_heads / p.n_kv);
@@ -41,48 +45,59 @@ __global__ void __launch_bounds__(ATTN_WARPS * 32) attention_split_kernel(const 
     const int t0 = sp * chunk, t1 = min(npos, t0 + chunk);
     const int hs = p.hs;
     const bool active = 4 * lane < hs;  // lane owns elements 4*lane .. 4*lane+3 of the head
-    const float inv_div = sqrtf((float)hs);
+    const float div = sqrtf((float)hs);
+    const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
 
     float4 qv[GQ], acc[GQ];
     float m[GQ], l[GQ];
 #pragma unroll
     for (int g = 0; g < GQ; ++g) {
         const int h = hg * GQ + g;
-        qv[g] = active ? __ldcg(reinterpret_cast<const float4*>(p.q + (size_t)h * hs) + lane) : make_float4(0, 0, 0, 0);
-        acc[g] = make_float4(0, 0, 0, 0);
+        qv[g] = active ? __ldcg(reinterpret_cast<const float4*>(p.q + (size_t)h * hs) + lane) : zero4;
+        acc[g] = zero4;
         m[g] = -INFINITY;
         l[g] = 0.f;
     }
     const float* kbase = p.kc + (size_t)kvh * p.seq_len * hs;
     const float* vbase = p.vc + (size_t)kvh * p.seq_len * hs;
-    for (int t = t0 + warp; t < t1; t += ATTN_WARPS) {
-        float4 kv4 = make_float4(0, 0, 0, 0), vv4 = make_float4(0, 0, 0, 0);
-        if (active) {
-            kv4 = __ldcg(reinterpret_cast<const float4*>(kbase + (size_t)t * hs) + lane);
-            vv4 = __ldcg(reinterpret_cast<const float4*>(vbase + (size_t)t * hs) + lane);
+    for (int tb = t0 + warp * ATTN_UNROLL; tb < t1; tb += ATTN_WARPS * ATTN_UNROLL) {
+        float4 kk[ATTN_UNROLL], vv[ATTN_UNROLL];
+#pragma unroll
+        for (int u = 0; u < ATTN_UNROLL; ++u) {
+            kk[u] = vv[u] = zero4;
+            if (active && tb + u < t1) {
+                kk[u] = __ldcg(reinterpret_cast<const float4*>(kbase + (size_t)(tb + u) * hs) + lane);
+                vv[u] = __ldcg(reinterpret_cast<const float4*>(vbase + (size_t)(tb + u) * hs) + lane);
+            }
         }
 #pragma unroll
-        for (int g = 0; g < GQ; ++g) {
-            float s = qv[g].x * kv4.x;
-            s = fmaf(qv[g].y, kv4.y, s);
-            s = fmaf(qv[g].z, kv4.z, s);
-            s = fmaf(qv[g].w, kv4.w, s);
-            s = warp_sum(s);
-            s = s / inv_div;  // att ./= sqrt(Float32(head_size))
-            const float mn = fmaxf(m[g], s);
-            const float corr = expf(m[g] - mn);  // 0 on the first position (m = -inf)
-            const float pr = expf(s - mn);
-            l[g] = fmaf(l[g], corr, pr);
-            acc[g].x = fmaf(acc[g].x, corr, pr * vv4.x);
-            acc[g].y = fmaf(acc[g].y, corr, pr * vv4.y);
-            acc[g].z = fmaf(acc[g].z, corr, pr * vv4.z);
-            acc[g].w = fmaf(acc[g].w, corr, pr * vv4.w);
-            m[g] = mn;
+        for (int u = 0; u < ATTN_UNROLL; ++u) {
+            if (tb + u < t1) {
+#pragma unroll
+                for (int g = 0; g < GQ; ++g) {
+                    float s = qv[g].x * kk[u].x;
+                    s = fmaf(qv[g].y, kk[u].y, s);
+                    s = fmaf(qv[g].z, kk[u].z, s);
+                    s = fmaf(qv[g].w, kk[u].w, s);
+                    s = warp_sum(s);
+                    s = s / div;  // att ./= sqrt(Float32(head_size))
+                    const float mn = fmaxf(m[g], s);
+                    const float corr = expf(m[g] - mn);  // 0 on the first position (m = -inf)
+                    const float pr = expf(s - mn);
+                    l[g] = fmaf(l[g], corr, pr);
+                    acc[g].x = fmaf(acc[g].x, corr, pr * vv[u].x);
+                    acc[g].y = fmaf(acc[g].y, corr, pr * vv[u].y);
+                    acc[g].z = fmaf(acc[g].z, corr, pr * vv[u].z);
+                    acc[g].w = fmaf(acc[g].w, corr, pr * vv[u].w);
+                    m[g] = mn;
+                }
+            }
         }
     }
-    // merge the warps
+    // merge the warps of this block
     __shared__ float sm[ATTN_WARPS][GQ], sl[ATTN_WARPS][GQ];
     __shared__ float4 sacc[ATTN_WARPS][GQ][32];
+    __shared__ int s_last;
 #pragma unroll
     for (int g = 0; g < GQ; ++g) {
         if (lane == 0) {
@@ -96,12 +111,12 @@ __global__ void __launch_bounds__(ATTN_WARPS * 32) attention_split_kernel(const 
         float M = -INFINITY;
 #pragma unroll
         for (int w = 0; w < ATTN_WARPS; ++w) M = fmaxf(M, sm[w][g]);
-        float L = 0.f;
-        float4 a = make_float4(0, 0, 0, 0);
+        float Ls = 0.f;
+        float4 a = zero4;
 #pragma unroll
         for (int w = 0; w < ATTN_WARPS; ++w) {
             const float wgt = (sm[w][g] == -INFINITY) ? 0.f : expf(sm[w][g] - M);
-            L = fmaf(sl[w][g], wgt, L);
+            Ls = fmaf(sl[w][g], wgt, Ls);
             const float4 b = sacc[w][g][lane];
             a.x = fmaf(b.x, wgt, a.x);
             a.y = fmaf(b.y, wgt, a.y);
@@ -109,12 +124,72 @@ __global__ void __launch_bounds__(ATTN_WARPS * 32) attention_split_kernel(const 
             a.w = fmaf(b.w, wgt, a.w);
         }
         const int h = hg * GQ + g;
-        if (lane == 0) {
-            p.part_m[(size_t)h * p.nsplit + sp] = M;
-            p.part_l[(size_t)h * p.nsplit + sp] = L;
+        if (p.nsplit == 1) {  // nothing to merge across blocks
+            if (active) {
+                a.x /= Ls; a.y /= Ls; a.z /= Ls; a.w /= Ls;
+                reinterpret_cast<float4*>(p.out + (size_t)h * hs)[lane] = a;
+            }
+        } else {
+            if (lane == 0) {
+                p.part_m[(size_t)h * p.nsplit + sp] = M;
+                p.part_l[(size_t)h * p.nsplit + sp] = Ls;
+            }
+            if (active) reinterpret_cast<float4*>(p.part_acc + ((size_t)h * p.nsplit + sp) * hs)[lane] = a;
         }
-        if (active) reinterpret_cast<float4*>(p.part_acc + ((size_t)h * p.nsplit + sp) * hs)[lane] = a;
     }
+    if (p.nsplit == 1) return;
+    // the last block of this head group merges the splits
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const int ticket = atomicAdd(p.tickets + hg, 1);
+        s_last = (ticket == p.nsplit - 1);
+        if (s_last) p.tickets[hg] = 0;  // ready for the next launch
+    }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    for (int g = warp; g < GQ; g += ATTN_WARPS) {
+        const int h = hg * GQ + g;
+        const float* pm = p.part_m + (size_t)h * p.nsplit;
+        const float* pl = p.part_l + (size_t)h * p.nsplit;
+        // lane s holds split s (nsplit <= 32)
+        const float ms = lane < p.nsplit ? __ldcg(pm + lane) : -INFINITY;
+        const float ls = lane < p.nsplit ? __ldcg(pl + lane) : 0.f;
+        const float M = warp_max(ms);
+        const float wgt = (ms == -INFINITY) ? 0.f : expf(ms - M);
+        const float Ls = warp_sum(ls * wgt);
+        float4 a = zero4;
+        for (int s0 = 0; s0 < p.nsplit; s0 += 4) {
+            float4 b[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                b[u] = zero4;
+                if (active && s0 + u < p.nsplit) b[u] = __ldcg(reinterpret_cast<const float4*>(p.part_acc + ((size_t)h * p.nsplit + s0 + u) * hs) + lane);
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const float wu = __shfl_sync(0xffffffffu, wgt, (s0 + u) & 31);
+                if (s0 + u < p.nsplit) {
+                    a.x = fmaf(b[u].x, wu, a.x);
+                    a.y = fmaf(b[u].y, wu, a.y);
+                    a.z = fmaf(b[u].z, wu, a.z);
+                    a.w = fmaf(b[u].w, wu, a.w);
+                }
+            }
+        }
+        if (active) {
+            a.x /= Ls; a.y /= Ls; a.z /= Ls; a.w /= Ls;
+            reinterpret_cast<float4*>(p.out + (size_t)h * hs)[lane] = a;
+        }
+    }
+}
+
+template <int GQ>
+__global__ void __launch_bounds__(ATTN_WARPS * 32) attention_split_kernel(const __grid_constant__ AttnParams p) {
+    pdl_launch_dependents();
+    pdl_wait();
+    attention_split_body<GQ>(p);
 }
 
 }  // namespace l2b

@@ -25,9 +25,10 @@ __host__ __device__ constexpr int file_block_bytes(int type) {
 // Error codes written to a session's device status word by kernels (0 = fine).
 enum : int { DEV_OK = 0, DEV_ERR_TMA_TIMEOUT = 1, DEV_ERR_BAD_INDEX = 2 };
 
-// Upper bound on polls of an mbarrier before a kernel gives up (each poll is a
-// try_wait with a hardware-side time slice, so this is far beyond any legitimate wait).
-constexpr uint32_t MBAR_MAX_POLLS = 4u * 1000u * 1000u;
+// Upper bound on polls of an mbarrier before a kernel gives up.  Each poll is a try_wait with a
+// hardware-side time slice of about a microsecond, so this is a few tenths of a second: far beyond
+// any legitimate wait (microseconds), short enough that a protocol bug costs little.
+constexpr uint32_t MBAR_MAX_POLLS = 200u * 1000u;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -41,6 +42,10 @@ __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.
 
 __device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 
 __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {

@@ -32,6 +32,28 @@ __global__ void dequantize_kernel(int type, const uint8_t* __restrict__ blocks, 
     }
 }
 
+// x = dequantize!(x, token_embedding_table[:, token]) (src/inference.jl:236): the first kernel of a token.
+// `token` is a device scalar.  For f32 tables the row is copied.
+__global__ void embed_row_kernel(int type, const uint8_t* __restrict__ table, const __half* __restrict__ d6, const int* token, int n, float* __restrict__ x) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int tok = __ldcg(token);
+    const int nb = n / QK_K;
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
+        float v;
+        if (type == T_F32) {
+            v = reinterpret_cast<const float*>(table)[(size_t)tok * n + i];
+        } else {
+            const int b = i >> 8, k = i & 255;
+            const uint8_t* blk = table + ((size_t)tok * nb + b) * dev_block_bytes(type);
+            if (type == T_Q4_K) v = dequant_q45<false>(blk, k);
+            else if (type == T_Q5_K) v = dequant_q45<true>(blk, k);
+            else v = dequant_q6(blk, __half2float(d6[(size_t)tok * nb + b]), k);
+        }
+        x[i] = v;
+    }
+}
+
 // Runs the prologue of the fused kernel on one block and exports what it built.
 // KQ: planes -> q [P][n] int8, dsc [P][n/256], sums [n/16].  else: the f32 vector.
 template <bool KQ, int P>
@@ -39,17 +61,17 @@ __global__ void __launch_bounds__(256) export_activation_kernel(const __grid_con
                                                                  float* f_out) {
     extern __shared__ __align__(128) uint8_t smem[];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
-    const MvSmem L = mv_smem_layout(p.n_in, P, KQ, nwarps, 0, 0);
+    const MvSmem L = mv_smem_layout(p.n_in, P, KQ, 0, 0);
     build_activation<KQ, P>(p, smem, L, warp, lane, nwarps);
     const int n = p.n_in, nb = n / QK_K;
     if (KQ) {
         for (int i = threadIdx.x; i < P * n; i += blockDim.x) {
             const int k = i / n, e = i % n;
-            q_out[i] = (int8_t)smem[L.off_act + k * L.plane_stride + (e >> 8) * ACT_STRIDE + (e & 255)];
+            q_out[i] = (int8_t)smem[L.off_act + k * L.plane_stride + (e >> 8) * ACT_STRIDE + ((e >> 7) & 1) * ACT_HALF + (e & 127)];
         }
         for (int i = threadIdx.x; i < P * nb; i += blockDim.x) {
             const int k = i / nb, b = i % nb;
-            d_out[i] = *reinterpret_cast<const float*>(smem + L.off_act + k * L.plane_stride + b * ACT_STRIDE + 256);
+            d_out[i] = *reinterpret_cast<const float*>(smem + L.off_act + k * L.plane_stride + b * ACT_STRIDE + ACT_SCALE);
         }
         for (int i = threadIdx.x; i < nb * 16; i += blockDim.x) sums_out[i] = reinterpret_cast<const float*>(smem + L.off_xs)[i];
     } else {

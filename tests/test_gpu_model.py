@@ -119,6 +119,6 @@ def test_decode_next_session_semantics(pkg, synth):
     assert L.lib().l2b_forward(sess, 5000, 0, None) == L.ERR_BAD_ARG
     assert L.lib().l2b_forward(sess, 1, 32, None) == L.ERR_BAD_ARG
     assert L.lib().l2b_decode_next(sess, 1, 0, 1.0, 1.5, C.byref(nxt)) == L.ERR_BAD_ARG
-    assert model.kernels_per_token() == 5 * 1 + 2
+    assert model.kernels_per_token() == 5 * 1 + 3
     assert model.weight_bytes_per_token() > 0
     model.close()
