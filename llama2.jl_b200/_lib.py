@@ -8,7 +8,7 @@ import ctypes as C
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libllama2_b200.so")
+LIB_PATH = os.environ.get("L2B_LIBRARY") or os.path.join(_HERE, "libllama2_b200.so")
 
 OK, ERR_BAD_ARG, ERR_UNSUPPORTED_TYPE, ERR_CUDA, ERR_NCCL, ERR_TIMEOUT, ERR_OOM, ERR_STATE, ERR_NO_DEVICE = range(9)
 TYPE_F32, TYPE_Q4_K, TYPE_Q5_K, TYPE_Q6_K = 0, 12, 13, 14

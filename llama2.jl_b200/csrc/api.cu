@@ -159,15 +159,6 @@ struct MvLaunch {
     size_t smem = 0;
 };
 
-// Lanes per row pair (log2).  A lane takes half a super-block, so a pair uses 2*GB lanes for GB blocks per turn.
-// GB is the power of two covering a row of nb blocks, at most 16: wide turns keep the bulk copies large (a
-// copy brings GB blocks of one row), which matters more than a few idle lanes in the last turn.
-static int choose_lgG(int nb) {
-    int lg = 1;
-    while (lg < 5 && ((1 << lg) >> 1) < nb) ++lg;
-    return lg;
-}
-
 // Decide grid, consumer warps, ring slots and shared memory for a launch whose segments, n_in, prologue and
 // epilogue fields are already filled in, and precompute the schedule constants the kernel would otherwise
 // derive with serial integer arithmetic.
@@ -179,46 +170,54 @@ static int32_t plan_matvec(MvLaunch& L, const DeviceInfo& di) {
     p.planes = L.planes;
     L.grid = di.sms;
     const int nb = p.n_in / QK_K;
-    p.lgG = L.kq ? choose_lgG(nb) : 5;
-    const int GB = (1 << p.lgG) >> 1, lgPW = L.kq ? 5 - p.lgG : 0, PW = 1 << lgPW;
-    p.nit = L.kq ? (nb + GB - 1) / GB : 1;
-    int steps = 0, max_bb = 0;
+    const int per_unit = L.kq ? MV_TILE_PAIRS : 1;
+    int units = 0, max_bb = 0;
     for (int s = 0; s < p.nseg; ++s) {
-        p.seg_start[s] = steps;
-        steps += (p.seg[s].npairs + PW - 1) / PW;
+        p.seg_start[s] = units;
+        units += (p.seg[s].npairs + per_unit - 1) / per_unit;
         max_bb = std::max(max_bb, dev_block_bytes(p.seg[s].type));
-        if (p.seg[s].pair_mode == PAIR_NEOX) p.neox_magic = (unsigned)((0x100000000ull + (p.seg[s].head_size / 2) - 1) / (p.seg[s].head_size / 2));
+        if (p.seg[s].pair_mode == PAIR_NEOX) {
+            const int h2 = p.seg[s].head_size / 2;
+            if (L.kq && h2 % MV_TILE_PAIRS != 0) return fail(L2B_ERR_BAD_ARG, "head_size must be a multiple of 16 for NeoX RoPE");
+            p.neox_magic = (unsigned)((0x100000000ull + h2 - 1) / h2);
+        }
     }
-    p.seg_start[p.nseg] = steps;
-    if (steps < L.grid) L.grid = std::max(1, steps);
-    p.steps_lo = steps / L.grid;
-    p.steps_rem = steps % L.grid;
-    const int cta_steps = p.steps_lo + (p.steps_rem ? 1 : 0);
-    // consumer warps: as few rounds as possible, spread evenly; at least 4 so the prologue has hands
-    const int max_cons = (int)std::min<long>(L.kq ? MV_MAX_WARPS - 1 : MV_MAX_WARPS, env_long("L2B_MV_WARPS", MV_MAX_WARPS));
-    const int rounds = (cta_steps + max_cons - 1) / max_cons;
-    int W = (cta_steps + rounds - 1) / rounds;
-    W = std::max(std::min(4, max_cons), std::min(W, max_cons));
-    p.consumers = W;
-    p.turns = (p.n_in / 8 + 32 * W - 1) / (32 * W);
-    L.warps = W + (L.kq ? 1 : 0);
+    p.seg_start[p.nseg] = units;
+    if (units < L.grid) L.grid = std::max(1, units);
+    p.units_lo = units / L.grid;
+    p.units_rem = units % L.grid;
     if (!L.kq) {
-        p.nst = 0;
+        const int per_block = p.units_lo + (p.units_rem ? 1 : 0);
+        const int W = std::max(4, std::min(MV_MAX_CONSUMERS, per_block));
+        p.consumers = W;
+        p.turns = (p.n_in / 8 + 32 * W - 1) / (32 * W);
+        p.nit = 1;
+        p.nslots = 0;
+        p.row_stride = 0;
+        L.warps = W;
         L.smem = mv_smem_layout(p.n_in, 1, false, 0, 0).total;
         if ((long)L.smem > di.max_smem_optin - 1024) return fail(L2B_ERR_BAD_ARG, "input vector too long for shared memory");
         return L2B_OK;
     }
-    // ring: every consumer warp owns nst slots of 32 super-blocks; as deep as the shared-memory budget allows (max 4)
-    const int slot = 32 * max_bb;
-    const long base = mv_smem_layout(p.n_in, L.planes, true, 0, max_bb).total;
-    long cap = std::min<long>(env_long("L2B_MV_SMEM_KB", 200) * 1024, di.max_smem_optin - 1024);
-    const long stages_per_warp = (long)((cta_steps + W - 1) / W) * p.nit;
-    int nst = (int)std::min<long>(4, std::min<long>(stages_per_warp, (cap - base) / ((long)slot * W)));
-    const long force = env_long("L2B_MV_STAGES", 0);
-    if (force > 0) nst = (int)std::min<long>(std::min<long>(force, 4), (di.max_smem_optin - 1024 - base) / ((long)slot * W));
-    if (nst < 1) return fail(L2B_ERR_BAD_ARG, "input dimension too large for the activation planes to fit in shared memory");
-    p.nst = nst;
-    L.smem = mv_smem_layout(p.n_in, L.planes, true, W * nst, max_bb).total;
+    const int kb = std::min(nb, MV_TILE_BLOCKS);  // super-blocks per row and stage
+    p.nit = (nb + MV_TILE_BLOCKS - 1) / MV_TILE_BLOCKS;
+    p.row_stride = mv_row_stride(kb, max_bb);
+    // one consumer warp per super-block column of a stage, at least 8 so the prologue has hands
+    const int W = (int)std::min<long>(MV_MAX_CONSUMERS, std::max<long>(std::min(8, MV_MAX_CONSUMERS), std::min<long>(kb, env_long("L2B_MV_WARPS", MV_MAX_CONSUMERS))));
+    p.consumers = W;
+    p.turns = (p.n_in / 8 + 32 * W - 1) / (32 * W);
+    L.warps = W + 1;
+    // ring: as many tile slots as the shared-memory budget allows
+    const long base = mv_smem_layout(p.n_in, L.planes, true, 0, p.row_stride).total;
+    const long slot = 16L * p.row_stride;
+    const long cap = std::min<long>(env_long("L2B_MV_SMEM_KB", 200) * 1024, di.max_smem_optin - 1024);
+    const long per_block_stages = (long)(p.units_lo + (p.units_rem ? 1 : 0)) * p.nit;
+    long ns = std::min<long>(std::min<long>(MV_MAX_SLOTS, per_block_stages), (cap - base) / slot);
+    const long force = env_long("L2B_MV_SLOTS", 0);
+    if (force > 0) ns = std::min<long>(std::min<long>(force, MV_MAX_SLOTS), (di.max_smem_optin - 1024 - base) / slot);
+    if (ns < 1) return fail(L2B_ERR_BAD_ARG, "input dimension too large for the activation planes to fit in shared memory");
+    p.nslots = (int)ns;
+    L.smem = mv_smem_layout(p.n_in, L.planes, true, p.nslots, p.row_stride).total;
     return L2B_OK;
 }
 

@@ -3,26 +3,23 @@
 // (src/inference.jl:236-312).
 //
 // One launch = prologue (build the activation vector in shared memory) + a stream of
-// weight rows + an epilogue per pair of output rows.
+// weight tiles + an epilogue per pair of output rows.
 //
 //   prologue  : raw copy | rmsnorm (inference.jl:102-110) of a vector in global memory; then, for
 //               k-quant weights, on-device quantisation of the vector to 1..3 int8 planes
 //               (block_q8_K layout, kquants.jl:38-42).
-//   weights   : warp-specialised.  The lanes of one producer warp each serve one consumer warp: they fill
-//               that warp's shared-memory slots with bulk asynchronous copies (TMA), each slot holding 32
-//               super-blocks (a lane works on half a super-block of each of the two rows of a pair).
-//               Every consumer warp owns `nst` slots, used round-robin: it waits on a slot's "full"
-//               barrier, runs the integer dot products, and hands the slot back through its "empty"
-//               barrier.  (Slots are private to a warp because an mbarrier wait only names a phase
-//               parity: a waiter must never be more than one phase ahead of the barrier, which holds
-//               when the same warp consumes successive phases of a slot.)  The producer starts BEFORE the wait on the
-//               previous kernel (programmatic dependent launch): weights are constants, so the ring is
-//               already full when the activations become available.
+//   weights   : warp-specialised.  A tile is 16 output rows (8 row pairs) by up to 16 super-blocks.
+//               The lanes of one producer warp bring the 16 rows of a tile into a ring of
+//               shared-memory slots with one bulk asynchronous copy (TMA) per row; the producer
+//               starts BEFORE the wait on the previous kernel (programmatic dependent launch):
+//               weights are constants, so the ring is already full when the activations arrive.
+//               All consumer warps work on the same slot, one super-block column each, with int8
+//               tensor-core MMAs (kquants.cuh); their partial sums meet in shared memory once per tile.
 //   epilogue  : store | residual add (:284,:305) | SwiGLU (:295-299) | RoPE + KV-cache write
 //               (:255-260) | logits store + running argmax (:312,:360)
 //
 // A kernel here lives for a few microseconds, so serial scalar work on the critical path matters as
-// much as bandwidth: everything that can be computed on the host (step counts, loop bounds, division
+// much as bandwidth: everything that can be computed on the host (tile counts, loop bounds, division
 // magic) arrives in the parameter block.
 #pragma once
 #include "kquants.cuh"
@@ -31,12 +28,18 @@ namespace l2b {
 
 enum : int { PRO_COPY = 0, PRO_RMSNORM = 1 };
 enum : int { EPI_STORE = 0, EPI_RESIDUAL = 1, EPI_SWIGLU = 2, EPI_ROPE_Q = 3, EPI_ROPE_K = 4, EPI_STORE_V = 5, EPI_LOGITS = 6 };
+// How the 8 row pairs (A, B) of a tile map to matrix rows.  Pair j of a tile occupies tile rows j and j+8.
+//   ADJACENT: rows (2t, 2t+1)            -- plain outputs and interleaved RoPE pairs
+//   NEOX    : rows (i, i + head_size/2)  -- NeoX RoPE pairs
+//   DUAL    : row t of `w` and row t of `w2` -- gate and up projections feeding SwiGLU
 enum : int { PAIR_ADJACENT = 0, PAIR_NEOX = 1, PAIR_DUAL = 2 };
 
 constexpr int MV_MAX_SEG = 3;
-constexpr int MV_MAX_WARPS = 16;
-constexpr int MV_MAX_SLOTS = 64;   // consumer warps x ring depth
-constexpr int MV_REG_BLOCKS = 4;  // 256-value blocks a warp keeps in registers across the rmsnorm reduction
+constexpr int MV_MAX_CONSUMERS = 16;
+constexpr int MV_MAX_SLOTS = 8;
+constexpr int MV_TILE_PAIRS = 8;
+constexpr int MV_TILE_BLOCKS = 16;  // super-blocks per row and stage
+constexpr int MV_REG_BLOCKS = 4;    // 256-value blocks a warp keeps in registers across the rmsnorm reduction
 
 struct MvSegment {
     const uint8_t* w;    // rows A (for PAIR_DUAL: the gate matrix)
@@ -55,13 +58,13 @@ struct MvParams {
     MvSegment seg[MV_MAX_SEG];
     int nseg;
     int n_in;        // input length
-    int lgG;         // log2 of lanes per row pair (a lane takes half a super-block, so 2^lgG / 2 blocks per turn)
-    int nst;         // ring depth per consumer warp (slots a warp owns)
     int planes;      // int8 activation planes (k-quant launches)
-    // schedule, precomputed on the host (see mv_fill_schedule)
-    int nit;                         // turns per step = ceil(blocks per row / blocks per turn)
-    int seg_start[MV_MAX_SEG + 1];   // first step of each segment; [nseg] = total number of steps
-    int steps_lo, steps_rem;         // block b runs steps_lo + (b < steps_rem) steps: b, b + grid, ...
+    // schedule, precomputed on the host (plan_matvec)
+    int nslots;                      // ring slots
+    int row_stride;                  // bytes between tile rows inside a slot (a multiple of 16, = 32 mod 128)
+    int nit;                         // stages per tile = ceil(blocks per row / 16)
+    int seg_start[MV_MAX_SEG + 1];   // first unit of each segment; [nseg] = total; a unit is a tile (k-quant) or a pair (f32)
+    int units_lo, units_rem;         // block b runs units_lo + (b < units_rem) units: b, b + grid, ...
     int consumers;                   // consumer warps per block (k-quant: blockDim/32 - 1; f32: blockDim/32)
     int turns;                       // prologue turns per warp = ceil(n_in / (256 * consumers))
     unsigned neox_magic;             // ceil(2^32 / (head_size/2)) for PAIR_NEOX row arithmetic
@@ -82,31 +85,40 @@ struct MvParams {
 
 // ---- shared-memory carve-up (host and device agree through this helper) ------------------
 struct MvSmem {
-    int off_bar, off_act, off_xs, off_xf, off_ring, off_red, total;
+    int off_bar, off_red, off_dpl, off_xs, off_act, off_xf, off_ring, total;
     int plane_stride, slot_bytes;
 };
 
-__host__ __device__ inline MvSmem mv_smem_layout(int n_in, int planes, bool kquant, int slots, int max_block_bytes) {
+__host__ __device__ inline int mv_row_stride(int blocks_per_stage, int block_bytes) {
+    int rs = blocks_per_stage * block_bytes;  // a multiple of 16
+    while ((rs & 127) != 32) rs += 16;        // rows g = 0..3 of a 64-bit fragment load then fall in distinct banks
+    return rs;
+}
+
+__host__ __device__ inline MvSmem mv_smem_layout(int n_in, int planes, bool kquant, int nslots, int row_stride) {
     MvSmem s;
     const int nb = n_in / QK_K;
     int o = 0;
-    s.off_bar = o;  // full[slots] then empty[slots]
+    s.off_bar = o;  // full[MV_MAX_SLOTS] then empty[MV_MAX_SLOTS]
     o += 2 * MV_MAX_SLOTS * 8;
-    s.off_red = o;
-    o += 64 * 4;
+    s.off_red = o;  // [2][MV_MAX_CONSUMERS][16] f32 tile partials (also the block-sum scratch of the prologue)
+    o += 2 * MV_MAX_CONSUMERS * 16 * 4;
+    s.off_dpl = o;
+    if (kquant) o += nb * 8 * 4;
+    s.off_xs = o;
+    if (kquant) o += nb * 16 * 4;
     o = (o + 127) & ~127;
-    s.plane_stride = nb * ACT_STRIDE;
+    s.plane_stride = n_in;
+    while ((s.plane_stride & 127) != 32) s.plane_stride += 16;  // planes 0..2 of a fragment load fall in distinct banks
     s.off_act = o;
     if (kquant) o += planes * s.plane_stride;
     o = (o + 15) & ~15;
-    s.off_xs = o;
-    if (kquant) o += nb * 16 * 4;
     s.off_xf = o;
     if (!kquant) o += n_in * 4;
     o = (o + 127) & ~127;
     s.off_ring = o;
-    s.slot_bytes = 32 * max_block_bytes;
-    if (kquant) o += slots * s.slot_bytes;
+    s.slot_bytes = 16 * row_stride;
+    if (kquant) o += nslots * s.slot_bytes;
     s.total = o;
     return s;
 }
@@ -132,6 +144,7 @@ __device__ __forceinline__ float block_sum(float v, float* red, int warp, int la
     consumer_sync(nwarps * 32);
     float t = 0.f;
     for (int i = 0; i < nwarps; ++i) t += red[i];  // same order in every thread
+    consumer_sync(nwarps * 32);                    // `red` is reused by the tile reduction
     return t;
 }
 
@@ -141,7 +154,7 @@ __device__ __forceinline__ float block_sum(float v, float* red, int warp, int la
 // Rounding to nearest-even uses the 1.5*2^23 trick: the low byte of the float's bits is the int8.
 // Not inlined: it is called from several places in the prologue.
 template <int P>
-__device__ __noinline__ void quantise_block(float4 va, float4 vb, int lane, uint8_t* act, int plane_stride, float* xs16, int b) {
+__device__ __noinline__ void quantise_block(float4 va, float4 vb, int lane, uint8_t* act, int plane_stride, float* dpl, float* xs16, int b) {
     const float v[8] = {va.x, va.y, va.z, va.w, vb.x, vb.y, vb.z, vb.w};
     float amax = 0.f;
 #pragma unroll
@@ -164,12 +177,12 @@ __device__ __noinline__ void quantise_block(float4 va, float4 vb, int lane, uint
         }
         const uint32_t w0 = __byte_perm(__byte_perm(tb[0], tb[1], 0x0040), __byte_perm(tb[2], tb[3], 0x0040), 0x5410);
         const uint32_t w1 = __byte_perm(__byte_perm(tb[4], tb[5], 0x0040), __byte_perm(tb[6], tb[7], 0x0040), 0x5410);
-        uint8_t* rec = act + k * plane_stride + b * ACT_STRIDE;
-        *reinterpret_cast<uint2*>(rec + (lane >> 4) * ACT_HALF + 8 * (lane & 15)) = make_uint2(w0, w1);
-        if (lane == 0) *reinterpret_cast<float*>(rec + ACT_SCALE) = d;
+        *reinterpret_cast<uint2*>(act + k * plane_stride + 256 * b + 8 * lane) = make_uint2(w0, w1);
+        if (lane == k) dpl[8 * b + k] = d;
         d *= (1.0f / 254.f);
         id *= 254.f;
     }
+    if (lane >= P && lane < 8) dpl[8 * b + lane] = 0.f;  // unused MMA columns
     // sum of the represented values = x - final residual
     float s = 0.f;
 #pragma unroll
@@ -185,6 +198,7 @@ __device__ __forceinline__ void build_activation(const MvParams& p, uint8_t* sme
     const int n = p.n_in;
     float* red = reinterpret_cast<float*>(smem + L.off_red);
     uint8_t* act = smem + L.off_act;
+    float* dpl = reinterpret_cast<float*>(smem + L.off_dpl);
     float* xs16 = reinterpret_cast<float*>(smem + L.off_xs);
     float* xf = reinterpret_cast<float*>(smem + L.off_xf);
     const int n8 = n / 8;
@@ -203,7 +217,7 @@ __device__ __forceinline__ void build_activation(const MvParams& p, uint8_t* sme
     auto emit = [&](int turn, float4 a, float4 b) {
         const int g0 = 32 * (warp + nwarps * turn), g = g0 + lane;
         if (g0 >= n8) return;
-        if (KQ) quantise_block<P>(a, b, lane, act, L.plane_stride, xs16, g0 >> 5);
+        if (KQ) quantise_block<P>(a, b, lane, act, L.plane_stride, dpl, xs16, g0 >> 5);
         else if (g < n8) {
             *reinterpret_cast<float4*>(xf + 8 * g) = a;
             *reinterpret_cast<float4*>(xf + 8 * g + 4) = b;
@@ -266,22 +280,22 @@ __device__ __forceinline__ void build_activation(const MvParams& p, uint8_t* sme
 }
 
 // ---- work enumeration ----------------------------------------------------------------------
-// A "step" is PW = 32 >> lgG row pairs of one segment (k-quant) or one pair (f32).  Steps of all
-// segments are numbered consecutively; block b takes steps b, b + grid, b + 2*grid, ... so that every
-// block streams the same number of bytes (+-1 step); inside a block, step number j goes to consumer
-// warp j mod W, round j / W.
-struct StepInfo {
+// A unit is a tile of MV_TILE_PAIRS row pairs of one segment (k-quant) or one pair (f32).  Units of all segments
+// are numbered consecutively; block b takes units b, b + grid, b + 2*grid, ... so that every block streams the
+// same number of bytes (+-1 unit).
+struct UnitInfo {
     int seg;    // segment index
-    int pair0;  // first pair of the step within the segment
+    int pair0;  // first pair of the unit within the segment
 };
 
-__device__ __forceinline__ StepInfo find_step(const MvParams& p, int step, int lgPW) {
-    StepInfo si;
-    si.seg = 0;
-    if (p.nseg > 1 && step >= p.seg_start[1]) si.seg = 1;
-    if (p.nseg > 2 && step >= p.seg_start[2]) si.seg = 2;
-    si.pair0 = (step - p.seg_start[si.seg]) << lgPW;
-    return si;
+template <bool KQ>
+__device__ __forceinline__ UnitInfo find_unit(const MvParams& p, int unit) {
+    UnitInfo u;
+    u.seg = 0;
+    if (p.nseg > 1 && unit >= p.seg_start[1]) u.seg = 1;
+    if (p.nseg > 2 && unit >= p.seg_start[2]) u.seg = 2;
+    u.pair0 = (unit - p.seg_start[u.seg]) * (KQ ? MV_TILE_PAIRS : 1);
+    return u;
 }
 
 __device__ __forceinline__ void pair_rows(const MvParams& p, const MvSegment& sg, int t, int& rowA, int& rowB) {
@@ -364,38 +378,26 @@ __device__ __forceinline__ void epilogue_pair(const MvParams& p, const MvSegment
 
 // ---- the kernel --------------------------------------------------------------------------------
 template <bool KQ, int P>
-__global__ void __launch_bounds__(MV_MAX_WARPS * 32, 1) fused_matvec_kernel(const __grid_constant__ MvParams p) {
+__global__ void __launch_bounds__((MV_MAX_CONSUMERS + 1) * 32, 1) fused_matvec_kernel(const __grid_constant__ MvParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int W = p.consumers;
-    int max_bb = 0;
-    if (KQ)
-        for (int s = 0; s < p.nseg; ++s) max_bb = max(max_bb, dev_block_bytes(p.seg[s].type));
-    const int NST = p.nst;
-    const int N = W * NST;  // slots; warp w owns slots w*NST .. w*NST+NST-1
-    const MvSmem L = mv_smem_layout(p.n_in, P, KQ, KQ ? N : 0, max_bb);
+    const int NS = p.nslots;
+    const MvSmem L = mv_smem_layout(p.n_in, P, KQ, KQ ? NS : 0, p.row_stride);
     MV_TRACE(0);
 
     const int nb = p.n_in / QK_K;
-    const int G2 = 1 << p.lgG;              // lanes per pair
-    const int GB = G2 >> 1;                 // super-blocks per pair and turn
-    const int lgPW = KQ ? (5 - p.lgG) : 0;  // log2 of pairs per step
-    const int PW = 1 << lgPW;
     const int nit = p.nit;
-    const int RS = (nit == 1) ? nb : GB;  // super-blocks between consecutive rows inside a slot
-    const int cta_steps = p.steps_lo + ((int)blockIdx.x < p.steps_rem ? 1 : 0);
-    const int rounds = (cta_steps + W - 1) / W;
+    const int my_units = p.units_lo + ((int)blockIdx.x < p.units_rem ? 1 : 0);
 
     uint64_t* full = reinterpret_cast<uint64_t*>(smem + L.off_bar);
     uint64_t* empty = full + MV_MAX_SLOTS;
     uint8_t* ring = smem + L.off_ring;
 
     if (KQ) {
-        if (threadIdx.x == 0) {
-            for (int i = 0; i < N; ++i) {
-                mbar_init(full + i, 1);
-                mbar_init(empty + i, 1);
-            }
+        if (threadIdx.x < NS) {
+            mbar_init(full + threadIdx.x, 1);
+            mbar_init(empty + threadIdx.x, W);
             fence_barrier_init();
             fence_proxy_async();
         }
@@ -404,45 +406,40 @@ __global__ void __launch_bounds__(MV_MAX_WARPS * 32, 1) fused_matvec_kernel(cons
     MV_TRACE(7);
 
     // ================================ producer warp =============================================
-    // Lane w serves consumer warp w: an independent stream of waits and bulk copies per lane, so that many
-    // copies are issued concurrently (a single issuing thread sustains only about four copies per microsecond).
+    // Lane m brings row m of every tile: 16 bulk copies per stage, issued concurrently.
     if (KQ && warp == W) {
         pdl_launch_dependents();
-        if (lane >= W) return;
+        if (lane >= 16) return;
         const uint64_t policy = policy_evict_first();
-        const int w = lane;
+        const int m = lane;  // tile row: pair j = m & 7, half = m >> 3 (0: row A, 1: row B)
         bool dead = false, first = true;
-        for (int r = 0; r < rounds && !dead; ++r) {
-            if (w >= min(W, cta_steps - r * W)) break;  // this warp has no step in the last, partial round
-            const int step = (int)blockIdx.x + (r * W + w) * (int)gridDim.x;
-            const StepInfo si = find_step(p, step, lgPW);
-            const MvSegment& sg = p.seg[si.seg];
+        int sigma = 0;  // stage number within this block; slot = sigma % NS
+        for (int j = 0; j < my_units && !dead; ++j) {
+            const UnitInfo u = find_unit<true>(p, (int)blockIdx.x + j * (int)gridDim.x);
+            const MvSegment& sg = p.seg[u.seg];
             const int bb = dev_block_bytes(sg.type);
-            const int npair = min(PW, sg.npairs - si.pair0);
-            // adjacent rows of whole-row turns are one contiguous run of bytes: a single copy fills the slot
-            const bool merged = (sg.pair_mode == PAIR_ADJACENT) && nit == 1;
-            for (int it = 0; it < nit; ++it) {
-                const int b0 = it * GB, nblk = min(GB, nb - b0);
-                const int u = r * nit + it;  // stage number of this consumer warp
-                const int slot_i = w * NST + u % NST, ph = u / NST;
-                // wait until the warp has released what this slot held before
+            const int t = u.pair0 + (m & 7);
+            const bool valid = t < sg.npairs;
+            const int nvalid = 2 * min(MV_TILE_PAIRS, sg.npairs - u.pair0);  // rows of this tile that exist
+            const uint8_t* src_row = nullptr;
+            if (valid) {
+                int rowA, rowB;
+                pair_rows(p, sg, t, rowA, rowB);
+                const uint8_t* base = (sg.pair_mode == PAIR_DUAL && (m >> 3)) ? sg.w2 : sg.w;
+                src_row = base + (size_t)((m >> 3) ? rowB : rowA) * nb * bb;
+            }
+            for (int it = 0; it < nit; ++it, ++sigma) {
+                const int b0 = it * MV_TILE_BLOCKS, nblk = min(MV_TILE_BLOCKS, nb - b0);
+                const int slot_i = sigma % NS, ph = sigma / NS;
+                // wait until every consumer warp has released what this slot held before
                 if (ph > 0 && !mbar_wait_bounded(empty + slot_i, (uint32_t)((ph & 1) ^ 1))) {
                     dead = true;
                     break;
                 }
-                uint8_t* slot = ring + (size_t)slot_i * L.slot_bytes;
-                mbar_arrive_expect_tx(full + slot_i, (uint32_t)(2 * npair * nblk * bb));
-                if (merged) {
-                    bulk_g2s(slot, sg.w + (size_t)(2 * si.pair0) * nb * bb, (uint32_t)(2 * npair * nb * bb), full + slot_i, policy);
-                } else {
-                    for (int qq = 0; qq < npair; ++qq) {
-                        int rowA, rowB;
-                        pair_rows(p, sg, si.pair0 + qq, rowA, rowB);
-                        const uint8_t* baseB = (sg.pair_mode == PAIR_DUAL) ? sg.w2 : sg.w;
-                        bulk_g2s(slot + (size_t)((2 * qq) * RS) * bb, sg.w + ((size_t)rowA * nb + b0) * bb, (uint32_t)(nblk * bb), full + slot_i, policy);
-                        bulk_g2s(slot + (size_t)((2 * qq + 1) * RS) * bb, baseB + ((size_t)rowB * nb + b0) * bb, (uint32_t)(nblk * bb), full + slot_i, policy);
-                    }
-                }
+                if (m == 0) mbar_arrive_expect_tx(full + slot_i, (uint32_t)(nvalid * nblk * bb));
+                __syncwarp(0x0000ffffu);
+                if (valid)
+                    bulk_g2s(ring + (size_t)slot_i * L.slot_bytes + (size_t)m * p.row_stride, src_row + (size_t)b0 * bb, (uint32_t)(nblk * bb), full + slot_i, policy);
                 if (first && p.trace && lane == 0) p.trace[blockIdx.x * 8 + 1] = global_ns();
                 first = false;
             }
@@ -468,61 +465,95 @@ __global__ void __launch_bounds__(MV_MAX_WARPS * 32, 1) fused_matvec_kernel(cons
     ArgBest best;
     best.v = -INFINITY;
     best.i = 0x7fffffff;
-    const uint8_t* act = smem + L.off_act;
-    const float* xs16 = reinterpret_cast<const float*>(smem + L.off_xs);
-    const float* xf = reinterpret_cast<const float*>(smem + L.off_xf);
-    const int q = lane >> p.lgG, within = lane & (G2 - 1), jb = within >> 1, hh = within & 1;
-    bool dead = false;
 
-    for (int r = 0; r < rounds; ++r) {
-        const int A = min(W, cta_steps - r * W);
-        if (warp >= A) break;
-        const int step = (int)blockIdx.x + (r * W + warp) * (int)gridDim.x;
-        const StepInfo si = find_step(p, step, lgPW);
-        const MvSegment& sg = p.seg[si.seg];
-        float accA = 0.f, accB = 0.f;
-        if (KQ) {
+    if (KQ) {
+        TileCtx cx;
+        cx.act = smem + L.off_act;
+        cx.dpl = reinterpret_cast<const float*>(smem + L.off_dpl);
+        cx.xs16 = reinterpret_cast<const float*>(smem + L.off_xs);
+        cx.plane_stride = L.plane_stride;
+        cx.g = lane >> 2;
+        cx.t = lane & 3;
+        cx.colv = cx.g < P;
+        float* red = reinterpret_cast<float*>(smem + L.off_red);
+        bool dead = false;
+        int sigma = 0;
+        for (int j = 0; j < my_units; ++j) {
+            const UnitInfo u = find_unit<true>(p, (int)blockIdx.x + j * (int)gridDim.x);
+            const MvSegment& sg = p.seg[u.seg];
             const int bb = dev_block_bytes(sg.type);
-            const int t = si.pair0 + q;
-            const bool have_pair = t < sg.npairs;
-            int rowA = 0, rowB = 0;
-            if (have_pair) pair_rows(p, sg, t, rowA, rowB);
-            const int offA = (2 * q * RS + jb) * bb, offB = ((2 * q + 1) * RS + jb) * bb;
-            for (int it = 0; it < nit; ++it) {
-                const int u = r * nit + it;  // this warp's stage number
-                const int b = it * GB + jb;
-                const bool work = have_pair && b < nb;
-                // q6_K super-block scales travel outside the records: fetch them before waiting on the slot
+            // q6_K super-block scales travel outside the records; rows g (A) and g of the B half
+            const __half* d6A = nullptr;
+            const __half* d6B = nullptr;
+            if (sg.type == T_Q6_K) {
+                const int t = min(u.pair0 + cx.g, sg.npairs - 1);
+                int rowA, rowB;
+                pair_rows(p, sg, t, rowA, rowB);
+                d6A = sg.d6 + (size_t)rowA * nb;
+                d6B = ((sg.pair_mode == PAIR_DUAL) ? sg.d6_2 : sg.d6) + (size_t)rowB * nb;
+            }
+            float accA = 0.f, accB = 0.f;  // rows g and g+8 of the tile = pair g
+            for (int it = 0; it < nit; ++it, ++sigma) {
+                const int b0 = it * MV_TILE_BLOCKS, nblk = min(MV_TILE_BLOCKS, nb - b0);
+                const int slot_i = sigma % NS;
                 float dA = 0.f, dB = 0.f;
-                if (sg.type == T_Q6_K && work) {
-                    const __half* dsrcB = (sg.pair_mode == PAIR_DUAL) ? sg.d6_2 : sg.d6;
-                    dA = __half2float(__ldg(sg.d6 + (size_t)rowA * nb + b));
-                    dB = __half2float(__ldg(dsrcB + (size_t)rowB * nb + b));
+                if (sg.type == T_Q6_K && warp < nblk) {  // fetched before the wait so that the latency overlaps it
+                    dA = __half2float(__ldg(d6A + b0 + warp));
+                    dB = __half2float(__ldg(d6B + b0 + warp));
                 }
-                const int slot_i = warp * NST + u % NST;
-                if (!dead && !mbar_wait_bounded(full + slot_i, (uint32_t)((u / NST) & 1))) dead = true;
+                if (!dead && !mbar_wait_bounded(full + slot_i, (uint32_t)((sigma / NS) & 1))) dead = true;
                 dead = __any_sync(0xffffffffu, dead);
-                if (r == 0 && it == 0) MV_TRACE(4);
-                if (!dead && work) {
+                if (j == 0 && it == 0) MV_TRACE(4);
+                if (!dead) {
                     const uint8_t* slot = ring + (size_t)slot_i * L.slot_bytes;
-                    const uint8_t* ab = act + b * ACT_STRIDE;
-                    const float* xb = xs16 + b * 16;
-                    if (sg.type == T_Q4_K) dot2h_q4k<P>(slot + offA, slot + offB, ab, L.plane_stride, xb, hh, accA, accB);
-                    else if (sg.type == T_Q5_K) dot2h_q5k<P>(slot + offA, slot + offB, ab, L.plane_stride, xb, hh, accA, accB);
-                    else dot2h_q6k<P>(slot + offA, slot + offB, dA, dB, ab, L.plane_stride, xb, hh, accA, accB);
+                    for (int bl = warp; bl < nblk; bl += W) {
+                        const uint8_t* rA = slot + (size_t)cx.g * p.row_stride + (size_t)bl * bb;
+                        const uint8_t* rB = rA + 8 * (size_t)p.row_stride;
+                        if (sg.type == T_Q4_K) tile_q4k(rA, rB, b0 + bl, cx, accA, accB);
+                        else if (sg.type == T_Q5_K) tile_q5k(rA, rB, b0 + bl, cx, accA, accB);
+                        else {
+                            if (bl != warp) {  // a second column for this warp (fewer warps than columns)
+                                dA = __half2float(__ldg(d6A + b0 + bl));
+                                dB = __half2float(__ldg(d6B + b0 + bl));
+                            }
+                            tile_q6k(rA, rB, dA, dB, b0 + bl, cx, accA, accB);
+                        }
+                    }
                 }
                 __syncwarp();  // every lane is done reading the slot
                 if (lane == 0 && !dead) mbar_arrive(empty + slot_i);
-                if (r == 0 && it == 0) MV_TRACE(5);
+                if (j == 0 && it == 0) MV_TRACE(5);
             }
-            // sum over the lanes of the pair
-            for (int o = G2 >> 1; o > 0; o >>= 1) {
-                accA += __shfl_xor_sync(0xffffffffu, accA, o);
-                accB += __shfl_xor_sync(0xffffffffu, accB, o);
+            // this warp's share of the tile: sum over the four lanes of a row group, then across warps
+            accA += __shfl_xor_sync(0xffffffffu, accA, 1);
+            accB += __shfl_xor_sync(0xffffffffu, accB, 1);
+            accA += __shfl_xor_sync(0xffffffffu, accA, 2);
+            accB += __shfl_xor_sync(0xffffffffu, accB, 2);
+            float* rbuf = red + (j & 1) * (MV_MAX_CONSUMERS * 16);
+            if (cx.t == 0) {
+                rbuf[warp * 16 + cx.g] = accA;
+                rbuf[warp * 16 + 8 + cx.g] = accB;
             }
-            if (!dead && have_pair && within == 0) epilogue_pair(p, sg, t, accA, accB, pos, best);
-        } else {
-            const int t = si.pair0;
+            consumer_sync(W * 32);
+            // one warp finishes the tile (a different one each time, so the others run ahead into the next tile)
+            if (warp == j % W && lane < MV_TILE_PAIRS && !dead) {
+                float vA = 0.f, vB = 0.f;
+                for (int w = 0; w < W; ++w) {  // fixed order: results do not depend on timing
+                    vA += rbuf[w * 16 + lane];
+                    vB += rbuf[w * 16 + 8 + lane];
+                }
+                const int t = u.pair0 + lane;
+                if (t < sg.npairs) epilogue_pair(p, sg, t, vA, vB, pos, best);
+            }
+        }
+        if (dead && lane == 0) atomicExch(p.status, DEV_ERR_TMA_TIMEOUT);
+    } else {
+        const float* xf = reinterpret_cast<const float*>(smem + L.off_xf);
+        // f32 weights: one warp per row pair, weights read straight from global memory (they are L2-sized models)
+        for (int j = warp; j < my_units; j += W) {
+            const UnitInfo u = find_unit<false>(p, (int)blockIdx.x + j * (int)gridDim.x);
+            const MvSegment& sg = p.seg[u.seg];
+            const int t = u.pair0;
             int rowA, rowB;
             pair_rows(p, sg, t, rowA, rowB);
             const float* baseB = reinterpret_cast<const float*>(sg.pair_mode == PAIR_DUAL ? sg.w2 : sg.w);
@@ -530,6 +561,7 @@ __global__ void __launch_bounds__(MV_MAX_WARPS * 32, 1) fused_matvec_kernel(cons
             const float4* wb = reinterpret_cast<const float4*>(baseB + (size_t)rowB * p.n_in);
             const float4* xv = reinterpret_cast<const float4*>(xf);
             const int n4 = p.n_in >> 2;
+            float accA = 0.f, accB = 0.f;
             for (int i = lane; i < n4; i += 32) {
                 const float4 x4 = xv[i], a4 = __ldg(wa + i), b4 = __ldg(wb + i);
                 accA = fmaf(a4.x, x4.x, accA); accA = fmaf(a4.y, x4.y, accA); accA = fmaf(a4.z, x4.z, accA); accA = fmaf(a4.w, x4.w, accA);
@@ -541,7 +573,6 @@ __global__ void __launch_bounds__(MV_MAX_WARPS * 32, 1) fused_matvec_kernel(cons
         }
     }
     MV_TRACE(6);
-    if (KQ && dead && lane == 0) atomicExch(p.status, DEV_ERR_TMA_TIMEOUT);
 
     if (p.amax_val) {  // EPI_LOGITS: first maximal index over this block's rows
         for (int o = 16; o > 0; o >>= 1) {
@@ -549,8 +580,8 @@ __global__ void __launch_bounds__(MV_MAX_WARPS * 32, 1) fused_matvec_kernel(cons
             const int oi = __shfl_xor_sync(0xffffffffu, best.i, o);
             arg_update(best, ov, oi);
         }
-        __shared__ float sv[MV_MAX_WARPS];
-        __shared__ int sidx[MV_MAX_WARPS];
+        __shared__ float sv[MV_MAX_CONSUMERS];
+        __shared__ int sidx[MV_MAX_CONSUMERS];
         if (lane == 0) {
             sv[warp] = best.v;
             sidx[warp] = best.i;

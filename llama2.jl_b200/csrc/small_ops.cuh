@@ -67,11 +67,11 @@ __global__ void __launch_bounds__(256) export_activation_kernel(const __grid_con
     if (KQ) {
         for (int i = threadIdx.x; i < P * n; i += blockDim.x) {
             const int k = i / n, e = i % n;
-            q_out[i] = (int8_t)smem[L.off_act + k * L.plane_stride + (e >> 8) * ACT_STRIDE + ((e >> 7) & 1) * ACT_HALF + (e & 127)];
+            q_out[i] = (int8_t)smem[L.off_act + k * L.plane_stride + e];
         }
         for (int i = threadIdx.x; i < P * nb; i += blockDim.x) {
             const int k = i / nb, b = i % nb;
-            d_out[i] = *reinterpret_cast<const float*>(smem + L.off_act + k * L.plane_stride + b * ACT_STRIDE + ACT_SCALE);
+            d_out[i] = reinterpret_cast<const float*>(smem + L.off_dpl)[8 * b + k];
         }
         for (int i = threadIdx.x; i < nb * 16; i += blockDim.x) sums_out[i] = reinterpret_cast<const float*>(smem + L.off_xs)[i];
     } else {
