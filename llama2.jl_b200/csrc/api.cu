@@ -168,6 +168,7 @@ static int32_t plan_matvec(MvLaunch& L, const DeviceInfo& di) {
     for (int s = 0; s < p.nseg; ++s)
         if ((p.seg[s].type != T_F32) != L.kq) return fail(L2B_ERR_UNSUPPORTED_TYPE, "f32 and k-quant matrices cannot share one launch");
     p.planes = L.planes;
+    p.debug = (int)env_long("L2B_MV_DEBUG", 0);
     L.grid = di.sms;
     const int nb = p.n_in / QK_K;
     const int per_unit = L.kq ? MV_TILE_PAIRS : 1;
@@ -190,6 +191,7 @@ static int32_t plan_matvec(MvLaunch& L, const DeviceInfo& di) {
         const int per_block = p.units_lo + (p.units_rem ? 1 : 0);
         const int W = std::max(4, std::min(MV_MAX_CONSUMERS, per_block));
         p.consumers = W;
+        p.cgroups = 1;
         p.turns = (p.n_in / 8 + 32 * W - 1) / (32 * W);
         p.nit = 1;
         p.nslots = 0;
@@ -201,21 +203,34 @@ static int32_t plan_matvec(MvLaunch& L, const DeviceInfo& di) {
     }
     const int kb = std::min(nb, MV_TILE_BLOCKS);  // super-blocks per row and stage
     p.nit = (nb + MV_TILE_BLOCKS - 1) / MV_TILE_BLOCKS;
-    p.row_stride = mv_row_stride(kb, max_bb);
-    // one consumer warp per super-block column of a stage, at least 8 so the prologue has hands
-    const int W = (int)std::min<long>(MV_MAX_CONSUMERS, std::max<long>(std::min(8, MV_MAX_CONSUMERS), std::min<long>(kb, env_long("L2B_MV_WARPS", MV_MAX_CONSUMERS))));
-    p.consumers = W;
-    p.turns = (p.n_in / 8 + 32 * W - 1) / (32 * W);
-    L.warps = W + 1;
+    // a slot holds 16 rows of kb blocks in up to 16 copy groups, each padded to 32 mod 128 bytes
+    p.row_stride = kb * max_bb + 128;
+    for (int s = 0; s < p.nseg; ++s) mv_fill_geometry(p.seg[s], kb, p.nit);
     // ring: as many tile slots as the shared-memory budget allows
+    long slot = 0;
+    for (int s = 0; s < p.nseg; ++s) slot = std::max<long>(slot, (long)p.seg[s].ngroups * p.seg[s].gs);
+    p.row_stride = (int)((slot + 15) / 16);
+    p.row_stride += (16 - p.row_stride % 16) % 16;
+    slot = 16L * p.row_stride;
     const long base = mv_smem_layout(p.n_in, L.planes, true, 0, p.row_stride).total;
-    const long slot = 16L * p.row_stride;
-    const long cap = std::min<long>(env_long("L2B_MV_SMEM_KB", 200) * 1024, di.max_smem_optin - 1024);
+    const long cap = std::min<long>(env_long("L2B_MV_SMEM_KB", 208) * 1024, di.max_smem_optin - 1024);
     const long per_block_stages = (long)(p.units_lo + (p.units_rem ? 1 : 0)) * p.nit;
-    long ns = std::min<long>(std::min<long>(MV_MAX_SLOTS, per_block_stages), (cap - base) / slot);
+    long ns = std::min<long>(std::min<long>(MV_MAX_SLOTS, std::max<long>(per_block_stages, 2)), (cap - base) / slot);
     const long force = env_long("L2B_MV_SLOTS", 0);
     if (force > 0) ns = std::min<long>(std::min<long>(force, MV_MAX_SLOTS), (di.max_smem_optin - 1024 - base) / slot);
-    if (ns < 1) return fail(L2B_ERR_BAD_ARG, "input dimension too large for the activation planes to fit in shared memory");
+    // Two groups of consumer warps alternate over the tiles of a block (one group's waits hide behind the other's
+    // arithmetic) when every group can have two slots of its own; a group has up to 8 warps, each taking one or
+    // two super-block columns of a stage.
+    int groups = (int)std::max<long>(1, std::min<long>(2, env_long("L2B_MV_GROUPS", 2)));
+    if (ns < 4) groups = 1;
+    const int WG = (int)std::min<long>(groups == 2 ? 8 : MV_MAX_CONSUMERS, std::max<long>(4, std::min<long>(kb, env_long("L2B_MV_WARPS", groups == 2 ? 8 : 16))));
+    const int W = WG * groups;
+    p.consumers = W;
+    p.cgroups = groups;
+    p.turns = (p.n_in / 8 + 32 * W - 1) / (32 * W);
+    L.warps = W + 2;  // + producer warp + finisher warp
+    ns -= ns % groups;  // every group owns the same number of slots
+    if (ns < groups) return fail(L2B_ERR_BAD_ARG, "input dimension too large for the activation planes to fit in shared memory");
     p.nslots = (int)ns;
     L.smem = mv_smem_layout(p.n_in, L.planes, true, p.nslots, p.row_stride).total;
     return L2B_OK;
@@ -1168,25 +1183,26 @@ extern "C" int32_t l2b_matrix_matvec(l2b_matrix* m, const float* host_x, int32_t
     CU(cudaDeviceSynchronize());
     if (env_long("L2B_MV_TRACE", 0)) {  // debugging aid: per-block timeline of one more launch, printed to stderr
         DevBuf tr;
-        L2B_TRY(dev_alloc(tr, (size_t)m->di.sms * 8 * 8));
-        CU(cudaMemset(tr.p, 0, (size_t)m->di.sms * 8 * 8));
+        const int NT = 16;
+        L2B_TRY(dev_alloc(tr, (size_t)m->di.sms * NT * 8));
+        CU(cudaMemset(tr.p, 0, (size_t)m->di.sms * NT * 8));
         g_trace = tr.as<unsigned long long>();
         for (int rep = 0; rep < 3; ++rep) L2B_TRY(l2b_matrix_matvec_device(m, 0, x.as<float>(), y.as<float>(), planes, nullptr));
         g_trace = nullptr;
         CU(cudaDeviceSynchronize());
-        std::vector<unsigned long long> h((size_t)m->di.sms * 8);
+        std::vector<unsigned long long> h((size_t)m->di.sms * NT);
         CU(cudaMemcpy(h.data(), tr.p, h.size() * 8, cudaMemcpyDeviceToHost));
         unsigned long long t0 = ~0ull;
-        for (int b = 0; b < m->di.sms; ++b) t0 = std::min(t0, h[b * 8]);
-        double mx[8] = {0}, av[8] = {0};
+        for (int b = 0; b < m->di.sms; ++b) t0 = std::min(t0, h[b * NT]);
+        double mx[NT] = {0}, av[NT] = {0};
         for (int b = 0; b < m->di.sms; ++b)
-            for (int i = 0; i < 8; ++i) {
-                const double v = (double)(h[b * 8 + i] - t0);
+            for (int i = 0; i < 14; ++i) {
+                const double v = h[b * NT + i] ? (double)(h[b * NT + i] - t0) : 0.0;
                 mx[i] = std::max(mx[i], v);
                 av[i] += v / m->di.sms;
             }
-        fprintf(stderr, "[l2b trace] ns since first block start (avg/max): start %.0f/%.0f barriers-ready %.0f issued %.0f/%.0f waited %.0f/%.0f act %.0f/%.0f stage0-landed %.0f/%.0f stage0-done %.0f/%.0f end %.0f/%.0f\n",
-                av[0], mx[0], av[7], av[1], mx[1], av[2], mx[2], av[3], mx[3], av[4], mx[4], av[5], mx[5], av[6], mx[6]);
+        fprintf(stderr, "[l2b trace] ns since first block start (avg/max): start %.0f/%.0f barriers-ready %.0f issued %.0f/%.0f waited %.0f/%.0f act %.0f/%.0f end %.0f/%.0f | tiles/block %llu\n",
+                av[0], mx[0], av[7], av[1], mx[1], av[2], mx[2], av[3], mx[3], av[6], mx[6], h[14]);
     }
     int hst = 0;
     CU(cudaMemcpy(&hst, m->status, 4, cudaMemcpyDeviceToHost));

@@ -25,10 +25,10 @@ __host__ __device__ constexpr int file_block_bytes(int type) {
 // Error codes written to a session's device status word by kernels (0 = fine).
 enum : int { DEV_OK = 0, DEV_ERR_TMA_TIMEOUT = 1, DEV_ERR_BAD_INDEX = 2 };
 
-// Upper bound on polls of an mbarrier before a kernel gives up.  Each poll is a try_wait with a
-// hardware-side time slice of about a microsecond, so this is a few tenths of a second: far beyond
-// any legitimate wait (microseconds), short enough that a protocol bug costs little.
-constexpr uint32_t MBAR_MAX_POLLS = 200u * 1000u;
+// Upper bound on polls of an mbarrier before a kernel gives up.  A poll is a test plus a short sleep
+// (tens of nanoseconds), so this is a few tenths of a second: far beyond any legitimate wait
+// (microseconds), short enough that a protocol bug costs little.
+constexpr uint32_t MBAR_MAX_POLLS = 4u * 1000u * 1000u;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -48,11 +48,11 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 
-__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+__device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
     uint32_t ok;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t}"
         : "=r"(ok)
         : "r"(smem_u32(bar)), "r"(parity)
@@ -60,11 +60,23 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
     return ok != 0;
 }
 
-// Bounded wait.  Returns false when the poll budget ran out.
+// Bounded wait: a non-blocking test in a spin loop.  (The potentially-blocking try_wait form was measured to
+// wake its waiters late, about a microsecond after the phase completed, which is as long as a whole tile.)
+// Returns false when the poll budget ran out.
 __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity) {
-    for (uint32_t i = 0; i < MBAR_MAX_POLLS; ++i)
-        if (mbar_try_wait(bar, parity)) return true;
+    for (uint32_t i = 0; i < MBAR_MAX_POLLS; ++i) {
+        if (mbar_test_wait(bar, parity)) return true;
+        if (i > 64) __nanosleep(32);
+    }
     return false;
+}
+
+// The same wait for a whole warp: one lane polls, the result is broadcast.  (Thirty-two lanes of every warp
+// polling one shared-memory word slow down the arrival they are waiting for.)
+__device__ __forceinline__ bool mbar_wait_bounded_warp(uint64_t* bar, uint32_t parity, int lane) {
+    int ok = 1;
+    if (lane == 0) ok = mbar_wait_bounded(bar, parity) ? 1 : 0;
+    return __shfl_sync(0xffffffffu, ok, 0) != 0;
 }
 
 // L2 policy for weight bytes: they are read once per token, so they should not evict the

@@ -9,12 +9,16 @@
 //               k-quant weights, on-device quantisation of the vector to 1..3 int8 planes
 //               (block_q8_K layout, kquants.jl:38-42).
 //   weights   : warp-specialised.  A tile is 16 output rows (8 row pairs) by up to 16 super-blocks.
-//               The lanes of one producer warp bring the 16 rows of a tile into a ring of
-//               shared-memory slots with one bulk asynchronous copy (TMA) per row; the producer
-//               starts BEFORE the wait on the previous kernel (programmatic dependent launch):
-//               weights are constants, so the ring is already full when the activations arrive.
-//               All consumer warps work on the same slot, one super-block column each, with int8
-//               tensor-core MMAs (kquants.cuh); their partial sums meet in shared memory once per tile.
+//               The lanes of one producer warp bring a tile into a ring of shared-memory slots with
+//               a few large bulk asynchronous copies (TMA): 4 copies of 4 adjacent rows, or 8 copies of
+//               2 rows when the two rows of a pair are far apart (an SM issues only ~23 bulk copies per
+//               microsecond, so 16 row-sized copies per tile would cap the stream below the HBM rate).
+//               The producer starts BEFORE the wait on the previous kernel (programmatic dependent
+//               launch): weights are constants, so the ring is already full when the activations arrive.
+//               All consumer warps work on the same slot, one or two super-block columns each, with int8
+//               tensor-core MMAs (kquants.cuh); their partial sums go to a small ring of shared-memory
+//               buffers, where a dedicated finisher warp adds them in a fixed order and runs the epilogue,
+//               so that no consumer warp ever waits for another one.
 //   epilogue  : store | residual add (:284,:305) | SwiGLU (:295-299) | RoPE + KV-cache write
 //               (:255-260) | logits store + running argmax (:312,:360)
 //
@@ -39,6 +43,7 @@ constexpr int MV_MAX_CONSUMERS = 16;
 constexpr int MV_MAX_SLOTS = 8;
 constexpr int MV_TILE_PAIRS = 8;
 constexpr int MV_TILE_BLOCKS = 16;  // super-blocks per row and stage
+constexpr int MV_RED_BUFS = 8;      // partial-sum buffers between the consumer warps and the finisher warp
 constexpr int MV_REG_BLOCKS = 4;    // 256-value blocks a warp keeps in registers across the rmsnorm reduction
 
 struct MvSegment {
@@ -52,6 +57,11 @@ struct MvSegment {
     int pair_mode;       // PAIR_*
     int epi;             // EPI_*
     int head_size;       // for RoPE / cache addressing
+    // slot geometry, filled by the host (mv_fill_geometry)
+    int ngroups;         // bulk copies per stage
+    int rpg;             // rows per copy
+    int gs;              // bytes between copy groups inside a slot (= 32 mod 128)
+    int rowb;            // bytes of one row in a full-width stage
 };
 
 struct MvParams {
@@ -65,7 +75,9 @@ struct MvParams {
     int nit;                         // stages per tile = ceil(blocks per row / 16)
     int seg_start[MV_MAX_SEG + 1];   // first unit of each segment; [nseg] = total; a unit is a tile (k-quant) or a pair (f32)
     int units_lo, units_rem;         // block b runs units_lo + (b < units_rem) units: b, b + grid, ...
-    int consumers;                   // consumer warps per block (k-quant: blockDim/32 - 1; f32: blockDim/32)
+    int consumers;                   // consumer warps per block (k-quant: blockDim/32 - 2; f32: blockDim/32)
+    int cgroups;                     // consumer groups (1 or 2): tile j is worked on by group j % cgroups, so that one
+                                     // group's barrier and reduction latencies hide behind the other group's arithmetic
     int turns;                       // prologue turns per warp = ceil(n_in / (256 * consumers))
     unsigned neox_magic;             // ceil(2^32 / (head_size/2)) for PAIR_NEOX row arithmetic
     // prologue
@@ -80,7 +92,8 @@ struct MvParams {
     float* amax_val;        // EPI_LOGITS: per-block best value   [gridDim.x]
     int* amax_idx;          // EPI_LOGITS: per-block best index   [gridDim.x]
     int* status;            // device status word
-    unsigned long long* trace;  // optional timeline: 8 globaltimer stamps per block (debugging aid), or null
+    int debug;              // measurement aid: bit 0 = consumers skip the arithmetic, bit 1 = the producer skips the copies (results are wrong)
+    unsigned long long* trace;  // optional timeline: 16 globaltimer stamps per block (debugging aid), or null
 };
 
 // ---- shared-memory carve-up (host and device agree through this helper) ------------------
@@ -99,10 +112,11 @@ __host__ __device__ inline MvSmem mv_smem_layout(int n_in, int planes, bool kqua
     MvSmem s;
     const int nb = n_in / QK_K;
     int o = 0;
-    s.off_bar = o;  // full[MV_MAX_SLOTS] then empty[MV_MAX_SLOTS]
-    o += 2 * MV_MAX_SLOTS * 8;
-    s.off_red = o;  // [2][MV_MAX_CONSUMERS][16] f32 tile partials (also the block-sum scratch of the prologue)
-    o += 2 * MV_MAX_CONSUMERS * 16 * 4;
+    s.off_bar = o;  // full[MV_MAX_SLOTS], empty[MV_MAX_SLOTS], red_full[MV_RED_BUFS], red_empty[MV_RED_BUFS]
+    o += (2 * MV_MAX_SLOTS + 2 * MV_RED_BUFS) * 8;
+    o = (o + 15) & ~15;
+    s.off_red = o;  // [MV_RED_BUFS][MV_MAX_CONSUMERS][16] f32 tile partials (also the block-sum scratch of the prologue)
+    o += MV_RED_BUFS * MV_MAX_CONSUMERS * 16 * 4;
     s.off_dpl = o;
     if (kquant) o += nb * 8 * 4;
     s.off_xs = o;
@@ -132,7 +146,7 @@ __device__ __forceinline__ unsigned long long global_ns() {
 }
 #define MV_TRACE(i)                                                                      \
     do {                                                                                 \
-        if (p.trace && threadIdx.x == 0) p.trace[blockIdx.x * 8 + (i)] = global_ns();   \
+        if (p.trace && threadIdx.x == 0) p.trace[blockIdx.x * 16 + (i)] = global_ns();  \
     } while (0)
 
 // Barrier over the first `nthreads` threads of the block (the consumer warps); the producer warp never joins it.
@@ -298,6 +312,17 @@ __device__ __forceinline__ UnitInfo find_unit(const MvParams& p, int unit) {
     return u;
 }
 
+// Segment descriptor number i, chosen with selects on statically indexed parameters: a dynamically indexed
+// read of the kernel parameter block costs an indexed constant load of a few hundred cycles per field.
+__device__ __forceinline__ MvSegment get_segment(const MvParams& p, int i) {
+    MvSegment a = p.seg[0];
+    if (p.nseg > 1 && i >= 1) {
+        const MvSegment& b = (i == 1) ? p.seg[1] : p.seg[2];
+        a = b;
+    }
+    return a;
+}
+
 __device__ __forceinline__ void pair_rows(const MvParams& p, const MvSegment& sg, int t, int& rowA, int& rowB) {
     if (sg.pair_mode == PAIR_ADJACENT) {
         rowA = 2 * t;
@@ -309,6 +334,42 @@ __device__ __forceinline__ void pair_rows(const MvParams& p, const MvSegment& sg
         rowB = rowA + h2;
     } else {
         rowA = rowB = t;
+    }
+}
+
+// ---- tile geometry in a ring slot ----------------------------------------------------------------
+// Rows of a tile arrive in groups of adjacent matrix rows, one bulk copy per group.  Groups are GS bytes apart,
+// GS = 32 mod 128, and lane group g works on pair PI[g] = (0,2,4,6,1,3,5,7)[g]: the four row groups g = 0..3
+// (and 4..7) that a 64-bit fragment load touches together then sit in four different copy groups, i.e. in
+// different shared-memory banks.  When a row is longer than one stage (nit > 1) the rows of a group are not
+// contiguous in memory and every row is its own copy (16 per stage).  The grouping of a segment is fixed on the host.
+__host__ __device__ inline int pad_32_mod_128(int v) {
+    while ((v & 127) != 32) v += 16;
+    return v;
+}
+// Host side: decide the copy grouping of a segment.  kb = super-blocks per row and stage, nit = stages per row.
+__host__ inline void mv_fill_geometry(MvSegment& sg, int kb, int nit) {
+    sg.rowb = kb * dev_block_bytes(sg.type);
+    if (nit > 1) {
+        sg.ngroups = 16; sg.rpg = 1;
+    } else if (sg.pair_mode == PAIR_ADJACENT) {
+        sg.ngroups = 4; sg.rpg = 4;
+    } else {
+        sg.ngroups = 8; sg.rpg = 2;
+    }
+    sg.gs = pad_32_mod_128(sg.rpg * sg.rowb);
+}
+// Byte offsets of the two rows (A, B) of pair j inside a slot.
+__device__ __forceinline__ void pair_offsets(const MvSegment& t, int j, int& offA, int& offB) {
+    if (t.rpg == 1) {
+        offA = j * t.gs;
+        offB = (j + 8) * t.gs;
+    } else if (t.rpg == 4) {
+        offA = (j >> 1) * t.gs + 2 * (j & 1) * t.rowb;
+        offB = offA + t.rowb;
+    } else {
+        offA = (j >> 1) * t.gs + (j & 1) * t.rowb;
+        offB = offA + 4 * t.gs;
     }
 }
 
@@ -378,7 +439,7 @@ __device__ __forceinline__ void epilogue_pair(const MvParams& p, const MvSegment
 
 // ---- the kernel --------------------------------------------------------------------------------
 template <bool KQ, int P>
-__global__ void __launch_bounds__((MV_MAX_CONSUMERS + 1) * 32, 1) fused_matvec_kernel(const __grid_constant__ MvParams p) {
+__global__ void __launch_bounds__((MV_MAX_CONSUMERS + 2) * 32, 1) fused_matvec_kernel(const __grid_constant__ MvParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int W = p.consumers;
@@ -392,12 +453,20 @@ __global__ void __launch_bounds__((MV_MAX_CONSUMERS + 1) * 32, 1) fused_matvec_k
 
     uint64_t* full = reinterpret_cast<uint64_t*>(smem + L.off_bar);
     uint64_t* empty = full + MV_MAX_SLOTS;
+    uint64_t* red_full = empty + MV_MAX_SLOTS;
+    uint64_t* red_empty = red_full + MV_RED_BUFS;
     uint8_t* ring = smem + L.off_ring;
 
     if (KQ) {
         if (threadIdx.x < NS) {
             mbar_init(full + threadIdx.x, 1);
-            mbar_init(empty + threadIdx.x, W);
+            mbar_init(empty + threadIdx.x, W / p.cgroups);
+        }
+        if (threadIdx.x >= 32 && threadIdx.x < 32 + MV_RED_BUFS) {
+            mbar_init(red_full + (threadIdx.x - 32), W / p.cgroups);
+            mbar_init(red_empty + (threadIdx.x - 32), 1);
+        }
+        if (threadIdx.x < 32 + MV_RED_BUFS) {
             fence_barrier_init();
             fence_proxy_async();
         }
@@ -406,48 +475,169 @@ __global__ void __launch_bounds__((MV_MAX_CONSUMERS + 1) * 32, 1) fused_matvec_k
     MV_TRACE(7);
 
     // ================================ producer warp =============================================
-    // Lane m brings row m of every tile: 16 bulk copies per stage, issued concurrently.
+    // Lane c brings copy group c of every stage.  This warp runs serial address arithmetic on a busy SM, so the
+    // parameters of the NEXT tile are worked out right after a tile's copies are issued, in the shadow of the
+    // wait for a free slot.
     if (KQ && warp == W) {
         pdl_launch_dependents();
         if (lane >= 16) return;
         const uint64_t policy = policy_evict_first();
-        const int m = lane;  // tile row: pair j = m & 7, half = m >> 3 (0: row A, 1: row B)
-        bool dead = false, first = true;
-        int sigma = 0;  // stage number within this block; slot = sigma % NS
-        for (int j = 0; j < my_units && !dead; ++j) {
+        const int c = lane;
+        struct TileSrc {
+            const uint8_t* src;  // first byte of this lane's copy (stage 0)
+            uint32_t bytes0;     // bytes of this lane's copy in a full-width stage (0: nothing to copy)
+            uint32_t tx0;        // bytes of the whole stage (all lanes) in a full-width stage
+            int bb, nrows, nvalid, gs;
+        };
+        auto tile_src = [&](int j) {
+            TileSrc ts;
+            ts.src = nullptr;
+            ts.bytes0 = ts.tx0 = 0;
+            ts.bb = ts.nrows = ts.nvalid = ts.gs = 0;
+            if (j >= my_units) return ts;
             const UnitInfo u = find_unit<true>(p, (int)blockIdx.x + j * (int)gridDim.x);
-            const MvSegment& sg = p.seg[u.seg];
-            const int bb = dev_block_bytes(sg.type);
-            const int t = u.pair0 + (m & 7);
-            const bool valid = t < sg.npairs;
-            const int nvalid = 2 * min(MV_TILE_PAIRS, sg.npairs - u.pair0);  // rows of this tile that exist
-            const uint8_t* src_row = nullptr;
-            if (valid) {
-                int rowA, rowB;
-                pair_rows(p, sg, t, rowA, rowB);
-                const uint8_t* base = (sg.pair_mode == PAIR_DUAL && (m >> 3)) ? sg.w2 : sg.w;
-                src_row = base + (size_t)((m >> 3) ? rowB : rowA) * nb * bb;
-            }
-            for (int it = 0; it < nit; ++it, ++sigma) {
-                const int b0 = it * MV_TILE_BLOCKS, nblk = min(MV_TILE_BLOCKS, nb - b0);
-                const int slot_i = sigma % NS, ph = sigma / NS;
-                // wait until every consumer warp has released what this slot held before
-                if (ph > 0 && !mbar_wait_bounded(empty + slot_i, (uint32_t)((ph & 1) ^ 1))) {
-                    dead = true;
-                    break;
+            const MvSegment sg = get_segment(p, u.seg);
+            ts.bb = dev_block_bytes(sg.type);
+            ts.gs = sg.gs;
+            const int pairs_left = sg.npairs - u.pair0;  // >= 1
+            ts.nvalid = 2 * min(MV_TILE_PAIRS, pairs_left);
+            if (c < sg.ngroups) {
+                if (sg.rpg == 4) {  // adjacent rows 16*tile + 4c ..
+                    ts.nrows = max(0, min(4, 2 * pairs_left - 4 * c));
+                    ts.src = sg.w + (size_t)(2 * u.pair0 + 4 * c) * nb * ts.bb;
+                } else {
+                    const int half = (sg.rpg == 2) ? (c >> 2) : (c >> 3);      // A or B rows
+                    const int jp = (sg.rpg == 2) ? 2 * (c & 3) : (c & 7);      // pair of the copy's first row
+                    ts.nrows = max(0, min(sg.rpg, pairs_left - jp));
+                    if (ts.nrows > 0) {
+                        int rowA, rowB;
+                        pair_rows(p, sg, u.pair0 + jp, rowA, rowB);
+                        const uint8_t* base = (sg.pair_mode == PAIR_DUAL && half) ? sg.w2 : sg.w;
+                        ts.src = base + (size_t)(half ? rowB : rowA) * nb * ts.bb;
+                    }
                 }
-                if (m == 0) mbar_arrive_expect_tx(full + slot_i, (uint32_t)(nvalid * nblk * bb));
-                __syncwarp(0x0000ffffu);
-                if (valid)
-                    bulk_g2s(ring + (size_t)slot_i * L.slot_bytes + (size_t)m * p.row_stride, src_row + (size_t)b0 * bb, (uint32_t)(nblk * bb), full + slot_i, policy);
-                if (first && p.trace && lane == 0) p.trace[blockIdx.x * 8 + 1] = global_ns();
-                first = false;
             }
+            ts.bytes0 = (uint32_t)(ts.nrows * sg.rowb);
+            ts.tx0 = (uint32_t)(ts.nvalid * sg.rowb);
+            return ts;
+        };
+        bool dead = false, first = true;
+        // Stage counters kept as (slot, phase) per consumer group: integer division by a run-time value costs
+        // hundreds of cycles here.  Group g owns slots g*NSG .. g*NSG+NSG-1 and takes tiles g, g+cgroups, ...
+        const int CG = p.cgroups, NSG = NS / CG;
+        int slot_g[2] = {0, NSG}, ph_g[2] = {0, 0};
+        TileSrc ts = tile_src(0);
+        // Fast path for the common case (one segment, adjacent or dual rows, full tiles): the next tile's source
+        // is the current one plus a constant.
+        const bool linear = (p.nseg == 1) && (p.seg[0].pair_mode != PAIR_NEOX);
+        const size_t tile_step = linear ? (size_t)gridDim.x * (p.seg[0].pair_mode == PAIR_ADJACENT ? 16 : 8) * nb * dev_block_bytes(p.seg[0].type) : 0;
+        const int full_tiles = linear ? p.seg[0].npairs / MV_TILE_PAIRS : 0;  // tiles below this index are complete
+        for (int j = 0; j < my_units && !dead; ++j) {
+            const int grp = (CG == 2) ? (j & 1) : 0;
+            int slot_i = grp ? slot_g[1] : slot_g[0], ph = grp ? ph_g[1] : ph_g[0];
+            for (int it = 0; it < nit; ++it) {
+                // wait until every consumer warp of the group has released what this slot held before
+                if (ph > 0) {
+                    int ok = 1;
+                    if (c == 0) ok = mbar_wait_bounded(empty + slot_i, (uint32_t)((ph & 1) ^ 1)) ? 1 : 0;
+                    ok = __shfl_sync(0x0000ffffu, ok, 0);
+                    if (!ok) {
+                        dead = true;
+                        break;
+                    }
+                }
+                uint32_t bytes = ts.bytes0, tx = ts.tx0;
+                if (nit > 1) {  // a stage is a 16-block slice of every row (one row per copy)
+                    const int nblk = min(MV_TILE_BLOCKS, nb - it * MV_TILE_BLOCKS);
+                    bytes = ts.nrows ? (uint32_t)(nblk * ts.bb) : 0u;
+                    tx = (uint32_t)(ts.nvalid * nblk * ts.bb);
+                }
+                if (p.debug & 2) bytes = tx = 0;
+                if (c == 0) mbar_arrive_expect_tx(full + slot_i, tx);
+                __syncwarp(0x0000ffffu);
+                if (bytes)
+                    bulk_g2s(ring + (size_t)slot_i * L.slot_bytes + (size_t)c * ts.gs, ts.src + (size_t)it * (MV_TILE_BLOCKS * ts.bb), bytes, full + slot_i, policy);
+                if (first && p.trace && lane == 0) p.trace[blockIdx.x * 16 + 1] = global_ns();
+                first = false;
+                if (++slot_i == (grp + 1) * NSG) {
+                    slot_i = grp * NSG;
+                    ++ph;
+                }
+            }
+            if (grp) {
+                slot_g[1] = slot_i;
+                ph_g[1] = ph;
+            } else {
+                slot_g[0] = slot_i;
+                ph_g[0] = ph;
+            }
+            // parameters of the next tile (in the shadow of the wait for its slot)
+            const int next_tile = (int)blockIdx.x + (j + 1) * (int)gridDim.x;
+            if (linear && next_tile < full_tiles) ts.src += tile_step;
+            else ts = tile_src(j + 1);
         }
         if (dead) {
             // a consumer gave up: let copies still in flight land (bounded) before shared memory is released
             atomicExch(p.status, DEV_ERR_TMA_TIMEOUT);
             for (int i = 0; i < 2000; ++i) __nanosleep(1000);  // copies land within microseconds; 2 ms is a generous bound
+        }
+        return;
+    }
+
+    // ================================ finisher warp ==============================================
+    // Adds the consumer warps' partial sums of a tile in a fixed order (results do not depend on timing) and runs
+    // the epilogue of its 8 row pairs.
+    if (KQ && warp == W + 1) {
+        pdl_launch_dependents();
+        pdl_wait();
+        const int pos = p.pos ? __ldcg(p.pos) : 0;
+        ArgBest best;
+        best.v = -INFINITY;
+        best.i = 0x7fffffff;
+        const float* red = reinterpret_cast<const float*>(smem + L.off_red);
+        // lane = 16*q + 8*half + pair: sums the partials of warps w = q, q+2, ... of row `half` of pair `pair`
+        const int fq = lane >> 4, fidx = lane & 15;
+        const int WGf = W / p.cgroups;  // warps that contribute to one tile
+        int unit = (int)blockIdx.x, seg_i = -1, seg_end = 0, seg_first = 0, rb = 0;
+        uint32_t par = 0;
+        MvSegment sg = p.seg[0];
+        bool dead = false;
+        for (int j = 0; j < my_units && !dead; ++j, unit += (int)gridDim.x) {
+            if (seg_i < 0 || unit >= seg_end) {
+                seg_i = find_unit<true>(p, unit).seg;
+                sg = get_segment(p, seg_i);
+                seg_first = (seg_i == 0) ? 0 : (seg_i == 1 ? p.seg_start[1] : p.seg_start[2]);
+                seg_end = (seg_i == 0) ? p.seg_start[1] : (seg_i == 1 ? p.seg_start[2] : p.seg_start[3]);
+            }
+            if (!mbar_wait_bounded(red_full + rb, par)) {
+                dead = true;
+                break;
+            }
+            const float* rbuf = red + rb * (MV_MAX_CONSUMERS * 16);
+            float v = 0.f;
+            for (int w = fq; w < WGf; w += 2) v += rbuf[w * 16 + fidx];
+            __syncwarp();
+            if (lane == 0) mbar_arrive(red_empty + rb);  // the buffer may be rewritten
+            v += __shfl_xor_sync(0xffffffffu, v, 16);     // (even warps) + (odd warps)
+            const float vB = __shfl_sync(0xffffffffu, v, (lane & 7) + 8);
+            const int t = (unit - seg_first) * MV_TILE_PAIRS + lane;
+            if (lane < MV_TILE_PAIRS && t < sg.npairs) epilogue_pair(p, sg, t, v, vB, pos, best);
+            if (++rb == MV_RED_BUFS) {
+                rb = 0;
+                par ^= 1u;
+            }
+        }
+        if (dead && lane == 0) atomicExch(p.status, DEV_ERR_TMA_TIMEOUT);
+        if (p.amax_val) {  // EPI_LOGITS: first maximal index over this block's rows
+            for (int o = 16; o > 0; o >>= 1) {
+                const float ov = __shfl_xor_sync(0xffffffffu, best.v, o);
+                const int oi = __shfl_xor_sync(0xffffffffu, best.i, o);
+                arg_update(best, ov, oi);
+            }
+            if (lane == 0) {
+                p.amax_val[blockIdx.x] = best.v;
+                p.amax_idx[blockIdx.x] = best.i;
+            }
         }
         return;
     }
@@ -475,44 +665,61 @@ __global__ void __launch_bounds__((MV_MAX_CONSUMERS + 1) * 32, 1) fused_matvec_k
         cx.g = lane >> 2;
         cx.t = lane & 3;
         cx.colv = cx.g < P;
+        const int pj = ((cx.g & 3) << 1) | (cx.g >> 2);  // the pair of the tile this lane group works on: (0,2,4,6,1,3,5,7)[g]
         float* red = reinterpret_cast<float*>(smem + L.off_red);
         bool dead = false;
-        int sigma = 0;
-        for (int j = 0; j < my_units; ++j) {
-            const UnitInfo u = find_unit<true>(p, (int)blockIdx.x + j * (int)gridDim.x);
-            const MvSegment& sg = p.seg[u.seg];
-            const int bb = dev_block_bytes(sg.type);
-            // q6_K super-block scales travel outside the records; rows g (A) and g of the B half
+        // counters kept incrementally (no run-time divisions in the loop): weight slot and its phase parity,
+        // reduction buffer and its phase parity, and the warp whose turn it is to finish a tile
+        const int CG = p.cgroups, WG = W / CG, NSG = NS / CG;
+        const int grp = warp / WG, wl = warp - grp * WG;  // this warp's group and its index inside the group
+        int slot_i = grp * NSG, rb = grp, red_wrap = 0;
+        uint32_t full_par = 0;
+        // Per-tile bookkeeping is incremental: the segment descriptor and everything derived from it change only
+        // when the unit number crosses into the next segment (serial code here runs at ~20 cycles per instruction).
+        int unit = (int)blockIdx.x + grp * (int)gridDim.x, seg_i = -1, seg_end = 0, seg_first = 0;
+        MvSegment sg = p.seg[0];
+        int bb = 0, offA = 0, offB = 0;
+        for (int j = grp; j < my_units; j += CG, unit += CG * (int)gridDim.x) {
+            if (seg_i < 0 || unit >= seg_end) {
+                const UnitInfo u0 = find_unit<true>(p, unit);
+                seg_i = u0.seg;
+                sg = get_segment(p, seg_i);
+                seg_first = (seg_i == 0) ? 0 : (seg_i == 1 ? p.seg_start[1] : p.seg_start[2]);
+                seg_end = (seg_i == 0) ? p.seg_start[1] : (seg_i == 1 ? p.seg_start[2] : p.seg_start[3]);
+                bb = dev_block_bytes(sg.type);
+                pair_offsets(sg, pj, offA, offB);
+            }
+            UnitInfo u;
+            u.seg = seg_i;
+            u.pair0 = (unit - seg_first) * MV_TILE_PAIRS;
+            // q6_K super-block scales travel outside the records; rows of this lane group's pair
             const __half* d6A = nullptr;
             const __half* d6B = nullptr;
             if (sg.type == T_Q6_K) {
-                const int t = min(u.pair0 + cx.g, sg.npairs - 1);
+                const int t = min(u.pair0 + pj, sg.npairs - 1);
                 int rowA, rowB;
                 pair_rows(p, sg, t, rowA, rowB);
                 d6A = sg.d6 + (size_t)rowA * nb;
                 d6B = ((sg.pair_mode == PAIR_DUAL) ? sg.d6_2 : sg.d6) + (size_t)rowB * nb;
             }
-            float accA = 0.f, accB = 0.f;  // rows g and g+8 of the tile = pair g
-            for (int it = 0; it < nit; ++it, ++sigma) {
+            float accA = 0.f, accB = 0.f;  // the two rows of pair pj of the tile
+            for (int it = 0; it < nit; ++it) {
                 const int b0 = it * MV_TILE_BLOCKS, nblk = min(MV_TILE_BLOCKS, nb - b0);
-                const int slot_i = sigma % NS;
                 float dA = 0.f, dB = 0.f;
-                if (sg.type == T_Q6_K && warp < nblk) {  // fetched before the wait so that the latency overlaps it
-                    dA = __half2float(__ldg(d6A + b0 + warp));
-                    dB = __half2float(__ldg(d6B + b0 + warp));
+                if (sg.type == T_Q6_K && wl < nblk) {  // fetched before the wait so that the latency overlaps it
+                    dA = __half2float(__ldg(d6A + b0 + wl));
+                    dB = __half2float(__ldg(d6B + b0 + wl));
                 }
-                if (!dead && !mbar_wait_bounded(full + slot_i, (uint32_t)((sigma / NS) & 1))) dead = true;
-                dead = __any_sync(0xffffffffu, dead);
-                if (j == 0 && it == 0) MV_TRACE(4);
-                if (!dead) {
+                if (!dead && !mbar_wait_bounded(full + slot_i, full_par)) dead = true;  // uniform across the warp
+                if (!dead && !(p.debug & 1)) {
                     const uint8_t* slot = ring + (size_t)slot_i * L.slot_bytes;
-                    for (int bl = warp; bl < nblk; bl += W) {
-                        const uint8_t* rA = slot + (size_t)cx.g * p.row_stride + (size_t)bl * bb;
-                        const uint8_t* rB = rA + 8 * (size_t)p.row_stride;
+                    for (int bl = wl; bl < nblk; bl += WG) {
+                        const uint8_t* rA = slot + offA + bl * bb;
+                        const uint8_t* rB = slot + offB + bl * bb;
                         if (sg.type == T_Q4_K) tile_q4k(rA, rB, b0 + bl, cx, accA, accB);
                         else if (sg.type == T_Q5_K) tile_q5k(rA, rB, b0 + bl, cx, accA, accB);
                         else {
-                            if (bl != warp) {  // a second column for this warp (fewer warps than columns)
+                            if (bl != wl) {  // a second column for this warp (fewer warps than columns)
                                 dA = __half2float(__ldg(d6A + b0 + bl));
                                 dB = __half2float(__ldg(d6B + b0 + bl));
                             }
@@ -522,28 +729,29 @@ __global__ void __launch_bounds__((MV_MAX_CONSUMERS + 1) * 32, 1) fused_matvec_k
                 }
                 __syncwarp();  // every lane is done reading the slot
                 if (lane == 0 && !dead) mbar_arrive(empty + slot_i);
-                if (j == 0 && it == 0) MV_TRACE(5);
+                if (++slot_i == (grp + 1) * NSG) {
+                    slot_i = grp * NSG;
+                    full_par ^= 1u;
+                }
             }
-            // this warp's share of the tile: sum over the four lanes of a row group, then across warps
+            // This warp's share of the tile: sum over the four lanes of a row group, then hand it to the finisher
+            // warp through one of MV_RED_BUFS buffers (full/empty mbarriers, like the weight ring).
             accA += __shfl_xor_sync(0xffffffffu, accA, 1);
             accB += __shfl_xor_sync(0xffffffffu, accB, 1);
             accA += __shfl_xor_sync(0xffffffffu, accA, 2);
             accB += __shfl_xor_sync(0xffffffffu, accB, 2);
-            float* rbuf = red + (j & 1) * (MV_MAX_CONSUMERS * 16);
+            if (red_wrap > 0 && !dead && !mbar_wait_bounded(red_empty + rb, (uint32_t)((red_wrap & 1) ^ 1))) dead = true;
+            float* rbuf = red + rb * (MV_MAX_CONSUMERS * 16);
             if (cx.t == 0) {
-                rbuf[warp * 16 + cx.g] = accA;
-                rbuf[warp * 16 + 8 + cx.g] = accB;
+                rbuf[wl * 16 + pj] = accA;
+                rbuf[wl * 16 + 8 + pj] = accB;
             }
-            consumer_sync(W * 32);
-            // one warp finishes the tile (a different one each time, so the others run ahead into the next tile)
-            if (warp == j % W && lane < MV_TILE_PAIRS && !dead) {
-                float vA = 0.f, vB = 0.f;
-                for (int w = 0; w < W; ++w) {  // fixed order: results do not depend on timing
-                    vA += rbuf[w * 16 + lane];
-                    vB += rbuf[w * 16 + 8 + lane];
-                }
-                const int t = u.pair0 + lane;
-                if (t < sg.npairs) epilogue_pair(p, sg, t, vA, vB, pos, best);
+            __syncwarp();
+            if (lane == 0 && !dead) mbar_arrive(red_full + rb);
+            rb += CG;  // the buffer of this group's next tile (MV_RED_BUFS is even)
+            if (rb >= MV_RED_BUFS) {
+                rb -= MV_RED_BUFS;
+                ++red_wrap;
             }
         }
         if (dead && lane == 0) atomicExch(p.status, DEV_ERR_TMA_TIMEOUT);
@@ -552,7 +760,7 @@ __global__ void __launch_bounds__((MV_MAX_CONSUMERS + 1) * 32, 1) fused_matvec_k
         // f32 weights: one warp per row pair, weights read straight from global memory (they are L2-sized models)
         for (int j = warp; j < my_units; j += W) {
             const UnitInfo u = find_unit<false>(p, (int)blockIdx.x + j * (int)gridDim.x);
-            const MvSegment& sg = p.seg[u.seg];
+            const MvSegment sg = get_segment(p, u.seg);
             const int t = u.pair0;
             int rowA, rowB;
             pair_rows(p, sg, t, rowA, rowB);
@@ -573,8 +781,9 @@ __global__ void __launch_bounds__((MV_MAX_CONSUMERS + 1) * 32, 1) fused_matvec_k
         }
     }
     MV_TRACE(6);
+    if (p.trace && threadIdx.x == 0) p.trace[blockIdx.x * 16 + 14] = (unsigned long long)my_units;
 
-    if (p.amax_val) {  // EPI_LOGITS: first maximal index over this block's rows
+    if (!KQ && p.amax_val) {  // EPI_LOGITS (f32 weights): first maximal index over this block's rows
         for (int o = 16; o > 0; o >>= 1) {
             const float ov = __shfl_xor_sync(0xffffffffu, best.v, o);
             const int oi = __shfl_xor_sync(0xffffffffu, best.i, o);
