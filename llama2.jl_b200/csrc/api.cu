@@ -369,6 +369,8 @@ struct l2b_session {
     int kernels_per_token = 0;
     cudaEvent_t ev0 = nullptr, ev1 = nullptr;
     float last_ms = 0.f;
+    unsigned long long* trace = nullptr;  // L2B_TRACE_TOKEN=1: per-launch, per-block timeline stamps (debugging aid)
+    int trace_launches = 0;
 };
 
 static size_t kv_layer_elems(const l2b_config& c) { return (size_t)c.n_kv_heads * c.seq_len * (c.dim / c.n_heads); }
@@ -523,6 +525,7 @@ static void session_free(l2b_session* s) {
                     s->rope_cs, s->ctl, s->status, s->prompt, s->out_tokens, s->next_token};
     for (void* b : bufs)
         if (b) cudaFree(b);
+    if (s->trace) cudaFree(s->trace);
     if (s->h_ctl) cudaFreeHost(s->h_ctl);
     if (s->h_small) cudaFreeHost(s->h_small);
     if (s->ev0) cudaEventDestroy(s->ev0);
@@ -545,6 +548,7 @@ static int32_t enqueue_token(l2b_session* s, int* nlaunch) {
     auto mv = [&](MvLaunch& L) -> int32_t {
         L.planes = m->planes;
         L2B_TRY(plan_matvec(L, s->di));
+        if (s->trace) L.p.trace = s->trace + (size_t)(s->trace_launches++) * s->di.sms * 16;
         CU(launch_matvec(L, s->stream, !first));
         last_grid = L.grid;
         first = false;
@@ -731,6 +735,11 @@ extern "C" int32_t l2b_session_create(l2b_model* m, void* stream, l2b_session** 
         CU(cudaMalloc(&s->rope_cs, cs.size() * 4));
         CU(cudaMemcpyAsync(s->rope_cs, cs.data(), cs.size() * 4, cudaMemcpyHostToDevice, s->stream));
         CU(cudaStreamSynchronize(s->stream));
+        if (env_long("L2B_TRACE_TOKEN", 0)) {
+            const size_t n = (size_t)(4 * c.n_layers + 1) * s->di.sms * 16;
+            CU(cudaMalloc(&s->trace, n * 8));
+            CU(cudaMemset(s->trace, 0, n * 8));
+        }
         // capture one token
         cudaGraph_t g = nullptr;
         CU(cudaStreamBeginCapture(s->stream, cudaStreamCaptureModeThreadLocal));
@@ -810,9 +819,34 @@ static int32_t run_one(l2b_session* s, int token, int pos, float temperature, do
     return check_status_word(s);
 }
 
+static void dump_token_trace(l2b_session* s) {
+    const int nl = s->trace_launches, sms = s->di.sms;
+    std::vector<unsigned long long> h((size_t)nl * sms * 16);
+    if (cudaMemcpy(h.data(), s->trace, h.size() * 8, cudaMemcpyDeviceToHost) != cudaSuccess) return;
+    unsigned long long t0 = ~0ull;
+    for (int b = 0; b < sms; ++b)
+        if (h[b * 16]) t0 = std::min(t0, h[b * 16]);
+    fprintf(stderr, "[l2b token trace] per fused launch, us since the first: first-block-start / avg first-copy-issued / avg waited(prev kernel done) / avg activations-built / last-block-end\n");
+    for (int k = 0; k < nl; ++k) {
+        double st = 1e30, en = 0, iss = 0, wt = 0, act = 0;
+        int nb = 0;
+        for (int b = 0; b < sms; ++b) {
+            const unsigned long long* r = &h[((size_t)k * sms + b) * 16];
+            if (!r[0]) continue;
+            ++nb;
+            st = std::min(st, (double)(r[0] - t0));
+            en = std::max(en, (double)(r[6] - t0));
+            iss += (double)(r[1] - t0); wt += (double)(r[2] - t0); act += (double)(r[3] - t0);
+        }
+        if (!nb) continue;
+        if (k < 12 || k >= nl - 3) fprintf(stderr, "  launch %3d: %8.2f %8.2f %8.2f %8.2f %8.2f\n", k, st / 1e3, iss / nb / 1e3, wt / nb / 1e3, act / nb / 1e3, en / 1e3);
+    }
+}
+
 extern "C" int32_t l2b_forward(l2b_session* s, int32_t token, int32_t pos, float* host_logits) {
     if (!s) return fail(L2B_ERR_BAD_ARG, "null session");
     L2B_TRY(run_one(s, token, pos, 0.f, 0.0));
+    if (s->trace) dump_token_trace(s);
     if (host_logits) CU(cudaMemcpy(host_logits, s->logits, (size_t)s->model->cfg.vocab_size * 4, cudaMemcpyDeviceToHost));
     return L2B_OK;
 }
@@ -1201,8 +1235,8 @@ extern "C" int32_t l2b_matrix_matvec(l2b_matrix* m, const float* host_x, int32_t
                 mx[i] = std::max(mx[i], v);
                 av[i] += v / m->di.sms;
             }
-        fprintf(stderr, "[l2b trace] ns since first block start (avg/max): start %.0f/%.0f barriers-ready %.0f issued %.0f/%.0f waited %.0f/%.0f act %.0f/%.0f end %.0f/%.0f | tiles/block %llu\n",
-                av[0], mx[0], av[7], av[1], mx[1], av[2], mx[2], av[3], mx[3], av[6], mx[6], h[14]);
+        fprintf(stderr, "[l2b trace] ns since first block start (avg/max): start %.0f/%.0f barriers-ready %.0f issued %.0f/%.0f waited %.0f/%.0f act %.0f/%.0f end %.0f/%.0f | producer: entered %.0f params-ready %.0f before-expect %.0f after-expect %.0f first-copy-issued %.0f | tiles/block %llu\n",
+                av[0], mx[0], av[7], av[1], mx[1], av[2], mx[2], av[3], mx[3], av[6], mx[6], av[8], av[9], av[10], av[11], av[1], h[14]);
     }
     int hst = 0;
     CU(cudaMemcpy(&hst, m->status, 4, cudaMemcpyDeviceToHost));

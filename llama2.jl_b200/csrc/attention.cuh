@@ -33,7 +33,8 @@ struct AttnParams {
 };
 
 constexpr int ATTN_WARPS = 4;
-constexpr int ATTN_UNROLL = 4;  // positions whose key/value loads a warp keeps in flight
+constexpr int ATTN_UNROLL = 4;      // positions whose key/value loads a warp keeps in flight
+constexpr int ATTN_MIN_CHUNK = 16;  // positions per split below which splitting costs more than it saves
 
 template <int GQ>  // query heads served per block; GQ divides n_heads / n_kv
 __device__ __forceinline__ void attention_split_body(const AttnParams& p) {
@@ -41,10 +42,14 @@ __device__ __forceinline__ void attention_split_body(const AttnParams& p) {
     const int hg = blockIdx.x / p.nsplit, sp = blockIdx.x % p.nsplit;
     const int kvh = (hg * GQ) / (p.n_heads / p.n_kv);
     const int npos = p.npos_override > 0 ? p.npos_override : (__ldcg(p.pos) + 1);
-    const int chunk = (npos + p.nsplit - 1) / p.nsplit;
+    // Short contexts use fewer splits (at least ATTN_MIN_CHUNK positions each): blocks beyond `active` leave at
+    // once, and a single active split writes its result directly, with no partials and no merge.
+    const int active = min(p.nsplit, (npos + ATTN_MIN_CHUNK - 1) / ATTN_MIN_CHUNK);
+    if (sp >= active) return;
+    const int chunk = (npos + active - 1) / active;
     const int t0 = sp * chunk, t1 = min(npos, t0 + chunk);
     const int hs = p.hs;
-    const bool active = 4 * lane < hs;  // lane owns elements 4*lane .. 4*lane+3 of the head
+    const bool lane_active = 4 * lane < hs;  // lane owns elements 4*lane .. 4*lane+3 of the head
     const float div = sqrtf((float)hs);
     const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
 
@@ -53,7 +58,7 @@ __device__ __forceinline__ void attention_split_body(const AttnParams& p) {
 #pragma unroll
     for (int g = 0; g < GQ; ++g) {
         const int h = hg * GQ + g;
-        qv[g] = active ? __ldcg(reinterpret_cast<const float4*>(p.q + (size_t)h * hs) + lane) : zero4;
+        qv[g] = lane_active ? __ldcg(reinterpret_cast<const float4*>(p.q + (size_t)h * hs) + lane) : zero4;
         acc[g] = zero4;
         m[g] = -INFINITY;
         l[g] = 0.f;
@@ -65,7 +70,7 @@ __device__ __forceinline__ void attention_split_body(const AttnParams& p) {
 #pragma unroll
         for (int u = 0; u < ATTN_UNROLL; ++u) {
             kk[u] = vv[u] = zero4;
-            if (active && tb + u < t1) {
+            if (lane_active && tb + u < t1) {
                 kk[u] = __ldcg(reinterpret_cast<const float4*>(kbase + (size_t)(tb + u) * hs) + lane);
                 vv[u] = __ldcg(reinterpret_cast<const float4*>(vbase + (size_t)(tb + u) * hs) + lane);
             }
@@ -124,8 +129,8 @@ __device__ __forceinline__ void attention_split_body(const AttnParams& p) {
             a.w = fmaf(b.w, wgt, a.w);
         }
         const int h = hg * GQ + g;
-        if (p.nsplit == 1) {  // nothing to merge across blocks
-            if (active) {
+        if (active == 1) {  // nothing to merge across blocks
+            if (lane_active) {
                 a.x /= Ls; a.y /= Ls; a.z /= Ls; a.w /= Ls;
                 reinterpret_cast<float4*>(p.out + (size_t)h * hs)[lane] = a;
             }
@@ -134,16 +139,16 @@ __device__ __forceinline__ void attention_split_body(const AttnParams& p) {
                 p.part_m[(size_t)h * p.nsplit + sp] = M;
                 p.part_l[(size_t)h * p.nsplit + sp] = Ls;
             }
-            if (active) reinterpret_cast<float4*>(p.part_acc + ((size_t)h * p.nsplit + sp) * hs)[lane] = a;
+            if (lane_active) reinterpret_cast<float4*>(p.part_acc + ((size_t)h * p.nsplit + sp) * hs)[lane] = a;
         }
     }
-    if (p.nsplit == 1) return;
+    if (active == 1) return;
     // the last block of this head group merges the splits
     __threadfence();
     __syncthreads();
     if (threadIdx.x == 0) {
         const int ticket = atomicAdd(p.tickets + hg, 1);
-        s_last = (ticket == p.nsplit - 1);
+        s_last = (ticket == active - 1);
         if (s_last) p.tickets[hg] = 0;  // ready for the next launch
     }
     __syncthreads();
@@ -154,23 +159,23 @@ __device__ __forceinline__ void attention_split_body(const AttnParams& p) {
         const float* pm = p.part_m + (size_t)h * p.nsplit;
         const float* pl = p.part_l + (size_t)h * p.nsplit;
         // lane s holds split s (nsplit <= 32)
-        const float ms = lane < p.nsplit ? __ldcg(pm + lane) : -INFINITY;
-        const float ls = lane < p.nsplit ? __ldcg(pl + lane) : 0.f;
+        const float ms = lane < active ? __ldcg(pm + lane) : -INFINITY;
+        const float ls = lane < active ? __ldcg(pl + lane) : 0.f;
         const float M = warp_max(ms);
         const float wgt = (ms == -INFINITY) ? 0.f : expf(ms - M);
         const float Ls = warp_sum(ls * wgt);
         float4 a = zero4;
-        for (int s0 = 0; s0 < p.nsplit; s0 += 4) {
+        for (int s0 = 0; s0 < active; s0 += 4) {
             float4 b[4];
 #pragma unroll
             for (int u = 0; u < 4; ++u) {
                 b[u] = zero4;
-                if (active && s0 + u < p.nsplit) b[u] = __ldcg(reinterpret_cast<const float4*>(p.part_acc + ((size_t)h * p.nsplit + s0 + u) * hs) + lane);
+                if (lane_active && s0 + u < active) b[u] = __ldcg(reinterpret_cast<const float4*>(p.part_acc + ((size_t)h * p.nsplit + s0 + u) * hs) + lane);
             }
 #pragma unroll
             for (int u = 0; u < 4; ++u) {
                 const float wu = __shfl_sync(0xffffffffu, wgt, (s0 + u) & 31);
-                if (s0 + u < p.nsplit) {
+                if (s0 + u < active) {
                     a.x = fmaf(b[u].x, wu, a.x);
                     a.y = fmaf(b[u].y, wu, a.y);
                     a.z = fmaf(b[u].z, wu, a.z);
@@ -178,7 +183,7 @@ __device__ __forceinline__ void attention_split_body(const AttnParams& p) {
                 }
             }
         }
-        if (active) {
+        if (lane_active) {
             a.x /= Ls; a.y /= Ls; a.z /= Ls; a.w /= Ls;
             reinterpret_cast<float4*>(p.out + (size_t)h * hs)[lane] = a;
         }

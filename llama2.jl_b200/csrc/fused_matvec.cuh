@@ -44,6 +44,7 @@ constexpr int MV_MAX_SLOTS = 8;
 constexpr int MV_TILE_PAIRS = 8;
 constexpr int MV_TILE_BLOCKS = 16;  // super-blocks per row and stage
 constexpr int MV_RED_BUFS = 8;      // partial-sum buffers between the consumer warps and the finisher warp
+constexpr int MV_GAIN_BLOCKS = 2;   // of those, the blocks whose rmsnorm gains are loaded together with x
 constexpr int MV_REG_BLOCKS = 4;    // 256-value blocks a warp keeps in registers across the rmsnorm reduction
 
 struct MvSegment {
@@ -255,9 +256,19 @@ __device__ __forceinline__ void build_activation(const MvParams& p, uint8_t* sme
     } else {
         // pass 1: sum of squares; the first MV_REG_BLOCKS turns stay in registers for pass 2
         float4 ka[MV_REG_BLOCKS], kb[MV_REG_BLOCKS];
+        float4 ga[MV_GAIN_BLOCKS], gb[MV_GAIN_BLOCKS];  // gains of the register-held turns, loaded with x, not after the sum
         float ss = 0.f;
 #pragma unroll
         for (int u = 0; u < MV_REG_BLOCKS; ++u) fetch(u, ka[u], kb[u]);
+#pragma unroll
+        for (int u = 0; u < MV_GAIN_BLOCKS; ++u) {
+            const int g = group_of(u);
+            ga[u] = gb[u] = zero4;
+            if (g < n8) {
+                ga[u] = __ldg(reinterpret_cast<const float4*>(p.gain + 8 * g));
+                gb[u] = __ldg(reinterpret_cast<const float4*>(p.gain + 8 * g + 4));
+            }
+        }
 #pragma unroll
         for (int u = 0; u < MV_REG_BLOCKS; ++u) ss = sumsq(ka[u], kb[u], ss);
         for (int turn = MV_REG_BLOCKS; turn < turns; ++turn) {
@@ -269,18 +280,22 @@ __device__ __forceinline__ void build_activation(const MvParams& p, uint8_t* sme
         tot /= (float)n;
         tot += 1e-5f;
         const float scale = 1.0f / sqrtf(tot);
-        auto normalise = [&](int turn, float4& a, float4& b) {  // weight .* (ss .* x)
+        auto apply = [&](const float4& ga, const float4& gb, float4& a, float4& b) {  // weight .* (ss .* x)
+            a.x = ga.x * (scale * a.x); a.y = ga.y * (scale * a.y); a.z = ga.z * (scale * a.z); a.w = ga.w * (scale * a.w);
+            b.x = gb.x * (scale * b.x); b.y = gb.y * (scale * b.y); b.z = gb.z * (scale * b.z); b.w = gb.w * (scale * b.w);
+        };
+        auto normalise = [&](int turn, float4& a, float4& b) {
             const int g = group_of(turn);
             if (g < n8) {
                 const float4 ga = __ldg(reinterpret_cast<const float4*>(p.gain + 8 * g));
                 const float4 gb = __ldg(reinterpret_cast<const float4*>(p.gain + 8 * g + 4));
-                a.x = ga.x * (scale * a.x); a.y = ga.y * (scale * a.y); a.z = ga.z * (scale * a.z); a.w = ga.w * (scale * a.w);
-                b.x = gb.x * (scale * b.x); b.y = gb.y * (scale * b.y); b.z = gb.z * (scale * b.z); b.w = gb.w * (scale * b.w);
+                apply(ga, gb, a, b);
             }
         };
 #pragma unroll
         for (int u = 0; u < MV_REG_BLOCKS; ++u) {
-            normalise(u, ka[u], kb[u]);
+            if (u < MV_GAIN_BLOCKS) apply(ga[u], gb[u], ka[u], kb[u]);  // lanes beyond n have x = 0 and gain = 0
+            else normalise(u, ka[u], kb[u]);
             emit(u, ka[u], kb[u]);
         }
         for (int turn = MV_REG_BLOCKS; turn < turns; ++turn) {
@@ -458,19 +473,27 @@ __global__ void __launch_bounds__((MV_MAX_CONSUMERS + 2) * 32, 1) fused_matvec_k
     uint8_t* ring = smem + L.off_ring;
 
     if (KQ) {
-        if (threadIdx.x < NS) {
-            mbar_init(full + threadIdx.x, 1);
-            mbar_init(empty + threadIdx.x, W / p.cgroups);
+        // The producer warp initialises the barriers it touches itself (full, empty) and only ARRIVES at the
+        // block-wide barrier, so its first copies do not wait for the other warps; everyone else initialises
+        // the reduction barriers and waits.
+        const int nthreads = (W + 2) * 32;
+        if (warp == W) {
+            if (lane < NS) {
+                mbar_init(full + lane, 1);
+                mbar_init(empty + lane, W / p.cgroups);
+                fence_barrier_init();
+                fence_proxy_async();
+            }
+            __syncwarp();
+            asm volatile("bar.arrive 2, %0;" ::"r"(nthreads) : "memory");
+        } else {
+            if (threadIdx.x < MV_RED_BUFS) {
+                mbar_init(red_full + threadIdx.x, W / p.cgroups);
+                mbar_init(red_empty + threadIdx.x, 1);
+                fence_barrier_init();
+            }
+            asm volatile("bar.sync 2, %0;" ::"r"(nthreads) : "memory");
         }
-        if (threadIdx.x >= 32 && threadIdx.x < 32 + MV_RED_BUFS) {
-            mbar_init(red_full + (threadIdx.x - 32), W / p.cgroups);
-            mbar_init(red_empty + (threadIdx.x - 32), 1);
-        }
-        if (threadIdx.x < 32 + MV_RED_BUFS) {
-            fence_barrier_init();
-            fence_proxy_async();
-        }
-        __syncthreads();
     }
     MV_TRACE(7);
 
@@ -481,6 +504,7 @@ __global__ void __launch_bounds__((MV_MAX_CONSUMERS + 2) * 32, 1) fused_matvec_k
     if (KQ && warp == W) {
         pdl_launch_dependents();
         if (lane >= 16) return;
+        if (p.trace && lane == 0) p.trace[blockIdx.x * 16 + 8] = global_ns();
         const uint64_t policy = policy_evict_first();
         const int c = lane;
         struct TileSrc {
@@ -527,6 +551,7 @@ __global__ void __launch_bounds__((MV_MAX_CONSUMERS + 2) * 32, 1) fused_matvec_k
         const int CG = p.cgroups, NSG = NS / CG;
         int slot_g[2] = {0, NSG}, ph_g[2] = {0, 0};
         TileSrc ts = tile_src(0);
+        if (p.trace && lane == 0) p.trace[blockIdx.x * 16 + 9] = global_ns();
         // Fast path for the common case (one segment, adjacent or dual rows, full tiles): the next tile's source
         // is the current one plus a constant.
         const bool linear = (p.nseg == 1) && (p.seg[0].pair_mode != PAIR_NEOX);
@@ -553,8 +578,10 @@ __global__ void __launch_bounds__((MV_MAX_CONSUMERS + 2) * 32, 1) fused_matvec_k
                     tx = (uint32_t)(ts.nvalid * nblk * ts.bb);
                 }
                 if (p.debug & 2) bytes = tx = 0;
+                if (first && p.trace && lane == 0) p.trace[blockIdx.x * 16 + 10] = global_ns();
                 if (c == 0) mbar_arrive_expect_tx(full + slot_i, tx);
                 __syncwarp(0x0000ffffu);
+                if (first && p.trace && lane == 0) p.trace[blockIdx.x * 16 + 11] = global_ns();
                 if (bytes)
                     bulk_g2s(ring + (size_t)slot_i * L.slot_bytes + (size_t)c * ts.gs, ts.src + (size_t)it * (MV_TILE_BLOCKS * ts.bb), bytes, full + slot_i, policy);
                 if (first && p.trace && lane == 0) p.trace[blockIdx.x * 16 + 1] = global_ns();
