@@ -158,6 +158,21 @@ int32_t l2b_rope(float* host_x, int32_t head_size, int32_t n_heads, int32_t pos,
  * q [n_heads][hs]; k, v [n_pos][n_kv_heads][hs] (position-major); out [n_heads][hs]. */
 int32_t l2b_attention(float* host_out, const float* host_q, const float* host_k, const float* host_v, int32_t n_pos,
                       int32_t n_heads, int32_t n_kv_heads, int32_t head_size);
+/* The same attention on DEVICE pointers, making no allocation of any kind.  This entry point has no counterpart in
+ * the reference (which has no device memory to manage); it exists for callers that must not allocate, e.g. inside a
+ * region where the CUDA allocator may not be entered.
+ *   dev_q [n_heads][hs], dev_out [n_heads][hs]; dev_kcache, dev_vcache [n_kv_heads][seq_len][hs] f32, of which
+ *   positions 0..n_pos-1 are attended.  The launch is asynchronous on `stream` (cudaStream_t; NULL = default).
+ * Scratch for the partial results lives in one fixed device array inside the library (about 1 MiB per device), so:
+ *   - limits: n_heads <= 128, head_size <= 128 (a multiple of 8), at most 16 splits; larger shapes are rejected with
+ *     L2B_ERR_BAD_ARG;
+ *   - the first call on each device resolves the array's address and must be made outside any stream capture;
+ *   - the array is shared by all calls on a device and keeps the previous call's contents (the words that must be
+ *     zero are cleared on `stream` before each launch); calls whose execution overlaps race on it, so callers
+ *     serialise their calls per device. */
+int32_t l2b_attention_device_noalloc(float* dev_out, const float* dev_q, const float* dev_kcache, const float* dev_vcache,
+                                     int32_t n_pos, int32_t seq_len, int32_t n_heads, int32_t n_kv_heads, int32_t head_size,
+                                     void* stream);
 /* hb = silu(hb) .* hb2 (src/inference.jl:295-299); written to host_hb. */
 int32_t l2b_swiglu(float* host_hb, const float* host_hb2, int64_t n);
 /* argmax(logits) (src/inference.jl:360), first maximal index, 0-based. */

@@ -1256,3 +1256,89 @@ extern "C" int32_t l2b_matvec(int32_t type, const void* host_W, int64_t in_dim, 
     l2b_matrix_destroy(m);
     return st;
 }
+
+// ---------------------------------------------------------------------------------------------
+// Attention on device pointers that allocates nothing
+// ---------------------------------------------------------------------------------------------
+// The split-KV attention kernel needs scratch memory for the per-split partial results and the tickets that
+// elect the merging block.  l2b_attention allocates that scratch per call; this entry point keeps it in one
+// file-scope device array of fixed size instead, so the call makes no device, pinned or managed allocation and
+// frees nothing.  Consequences, all of them the caller's to respect:
+//   * the first call on each device looks the array's address up (cudaGetSymbolAddress) and must therefore be
+//     made outside any stream capture; later calls on that device reuse the address;
+//   * the array is shared by every call on the device and keeps what the last call left in it; the tickets,
+//     which must be zero when the kernel starts, are cleared on the caller's stream before every launch;
+//   * two calls whose execution overlaps (different streams, or two host threads) race on the array: callers
+//     serialise their calls per device;
+//   * shapes whose scratch exceeds the array are rejected with L2B_ERR_BAD_ARG.
+namespace {
+
+constexpr int NA_MAX_HEADS = 128;   // query heads
+constexpr int NA_MAX_HS = 128;      // head size
+constexpr int NA_MAX_SPLITS = 16;   // splits of the position range
+constexpr int NA_MAX_DEVICES = 64;
+constexpr size_t NA_ACC_FLOATS = (size_t)NA_MAX_HEADS * NA_MAX_SPLITS * NA_MAX_HS;  // 262144 floats = 1 MiB
+constexpr size_t NA_ML_FLOATS = (size_t)NA_MAX_HEADS * NA_MAX_SPLITS;               // 2048 floats each for max and sum
+constexpr size_t NA_SCRATCH_FLOATS = NA_ACC_FLOATS + 2 * NA_ML_FLOATS + NA_MAX_HEADS;  // + tickets (int32)
+
+// 1 MiB + 16.5 KiB of scratch per device, inside the module's global memory (no allocation at run time).
+static __device__ __align__(256) float g_attn_static_scratch[NA_SCRATCH_FLOATS];
+
+std::mutex g_na_mutex;
+float* g_na_scratch_addr[NA_MAX_DEVICES] = {nullptr};
+
+template <int GQ>
+__global__ void __launch_bounds__(ATTN_WARPS * 32) attention_static_scratch_kernel(const __grid_constant__ AttnParams p) {
+    attention_split_body<GQ>(p);
+}
+
+}  // namespace
+
+extern "C" int32_t l2b_attention_device_noalloc(float* dev_out, const float* dev_q, const float* dev_kcache, const float* dev_vcache,
+                                                int32_t n_pos, int32_t seq_len, int32_t n_heads, int32_t n_kv, int32_t hs,
+                                                void* stream) {
+    if (!dev_out || !dev_q || !dev_kcache || !dev_vcache) return fail(L2B_ERR_BAD_ARG, "null argument");
+    if (n_pos <= 0 || seq_len < n_pos || n_heads <= 0 || n_kv <= 0 || n_heads % n_kv != 0 || hs % 8 != 0 || hs <= 0)
+        return fail(L2B_ERR_BAD_ARG, "bad attention shape");
+    if (n_heads > NA_MAX_HEADS || hs > NA_MAX_HS)
+        return fail(L2B_ERR_BAD_ARG, "l2b_attention_device_noalloc: at most 128 heads of at most 128 values fit the static scratch array");
+    L2B_TRY(require_device());
+    int dev = 0;
+    CU(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= NA_MAX_DEVICES) return fail(L2B_ERR_BAD_ARG, "l2b_attention_device_noalloc: device ordinal beyond 63");
+    float* scratch = nullptr;
+    {
+        std::lock_guard<std::mutex> lock(g_na_mutex);
+        if (!g_na_scratch_addr[dev]) {
+            float* ptr = nullptr;
+            CU(cudaGetSymbolAddress((void**)&ptr, g_attn_static_scratch));
+            g_na_scratch_addr[dev] = ptr;
+        }
+        scratch = g_na_scratch_addr[dev];
+    }
+    const int gq = choose_gq(n_heads, n_kv);
+    // the same split rule as l2b_attention, so that both entry points add in the same order
+    const int nsplit = std::max(1, std::min(NA_MAX_SPLITS, std::min((n_pos + 7) / 8, (int)env_long("L2B_ATTN_SPLITS", 16))));
+    if ((size_t)n_heads * nsplit * hs > NA_ACC_FLOATS || (size_t)n_heads * nsplit > NA_ML_FLOATS)
+        return fail(L2B_ERR_BAD_ARG, "l2b_attention_device_noalloc: shape exceeds the static scratch array");
+    cudaStream_t st = (cudaStream_t)stream;
+    AttnParams a;
+    memset(&a, 0, sizeof(a));
+    a.q = dev_q; a.kc = dev_kcache; a.vc = dev_vcache; a.out = dev_out;
+    a.part_acc = scratch;
+    a.part_m = scratch + NA_ACC_FLOATS;
+    a.part_l = scratch + NA_ACC_FLOATS + NA_ML_FLOATS;
+    a.tickets = reinterpret_cast<int*>(scratch + NA_ACC_FLOATS + 2 * NA_ML_FLOATS);
+    a.n_heads = n_heads; a.n_kv = n_kv; a.hs = hs; a.seq_len = seq_len; a.nsplit = nsplit; a.npos_override = n_pos;
+    // the array keeps the last call's contents: the tickets must be zero when the kernel starts
+    CU(cudaMemsetAsync(a.tickets, 0, (size_t)NA_MAX_HEADS * sizeof(int), st));
+    const dim3 grid((n_heads / gq) * nsplit), block(ATTN_WARPS * 32);
+    switch (gq) {
+        case 8: attention_static_scratch_kernel<8><<<grid, block, 0, st>>>(a); break;
+        case 4: attention_static_scratch_kernel<4><<<grid, block, 0, st>>>(a); break;
+        case 2: attention_static_scratch_kernel<2><<<grid, block, 0, st>>>(a); break;
+        default: attention_static_scratch_kernel<1><<<grid, block, 0, st>>>(a); break;
+    }
+    CU(cudaGetLastError());
+    return L2B_OK;
+}
