@@ -108,6 +108,19 @@ int32_t l2b_model_weight_bytes(const l2b_model* model, int64_t* bytes_per_token)
  * `stream` is a cudaStream_t passed as a pointer (NULL = the library creates its own). */
 int32_t l2b_session_create(l2b_model* model, void* stream, l2b_session** session);
 int32_t l2b_session_reset(l2b_session* session); /* zero the KV cache, as a fresh RunState */
+/* ---- tensor parallelism (no counterpart in the reference, which runs on one CPU) ------
+ * One process per GPU; every rank creates its model with the same l2b_config except tp_rank, uploads the FULL tensors
+ * (the library keeps its shard: whole kv groups of wq/wk/wv, hidden units of w1/w3, super-block columns of wo/w2; needs
+ * n_kv_heads, dim/256 and hidden_dim/256 divisible by tp_size and k-quant wo/w2), and creates a session.  Then:
+ *   l2b_session_tp_handle  writes a 64-byte handle of this rank's exchange memory;
+ *   the host moves the handles between the processes (any transport) ...
+ *   l2b_session_tp_connect takes all tp_size handles ordered by rank, maps the peers' memory and captures the token graph.
+ * After that l2b_forward / l2b_decode_next / l2b_generate must be called by ALL ranks with the same arguments; every rank
+ * returns the same logits and tokens.  A rank whose peers do not deliver within L2B_TP_TIMEOUT_MS (default 10000) gets
+ * L2B_ERR_TIMEOUT.  All ranks must have finished their calls before any of them destroys its session. */
+int32_t l2b_session_tp_handle(l2b_session* session, void* handle64);
+int32_t l2b_session_tp_connect(l2b_session* session, const void* handles, int32_t count);
+
 int32_t l2b_session_destroy(l2b_session* session);
 
 /* transformer!(token, pos, config, s, weights) (src/inference.jl:222-315): one token

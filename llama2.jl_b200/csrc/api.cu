@@ -254,6 +254,9 @@ static void set_kernel_attrs() {
         set((const void*)fused_matvec_kernel<true, 2>);
         set((const void*)fused_matvec_kernel<true, 3>);
         set((const void*)fused_matvec_kernel<false, 1>);
+        set((const void*)fused_matvec_kernel<true, 1, true>);
+        set((const void*)fused_matvec_kernel<true, 2, true>);
+        set((const void*)fused_matvec_kernel<true, 3, true>);
         set((const void*)export_activation_kernel<true, 1>);
         set((const void*)export_activation_kernel<true, 2>);
         set((const void*)export_activation_kernel<true, 3>);
@@ -270,6 +273,12 @@ static int32_t check_kernel_attrs() {
 static cudaError_t launch_matvec(const MvLaunch& L, cudaStream_t st, bool pdl) {
     const dim3 grid(L.grid), block(L.warps * 32);
     if (!L.kq) return launch_kernel(fused_matvec_kernel<false, 1>, grid, block, L.smem, st, pdl, L.p);
+    if (L.p.tp_push || L.p.part_src)  // the variants that carry the tensor-parallel exchange
+        switch (L.planes) {
+            case 1: return launch_kernel(fused_matvec_kernel<true, 1, true>, grid, block, L.smem, st, pdl, L.p);
+            case 2: return launch_kernel(fused_matvec_kernel<true, 2, true>, grid, block, L.smem, st, pdl, L.p);
+            default: return launch_kernel(fused_matvec_kernel<true, 3, true>, grid, block, L.smem, st, pdl, L.p);
+        }
     switch (L.planes) {
         case 1: return launch_kernel(fused_matvec_kernel<true, 1>, grid, block, L.smem, st, pdl, L.p);
         case 2: return launch_kernel(fused_matvec_kernel<true, 2>, grid, block, L.smem, st, pdl, L.p);
@@ -341,6 +350,12 @@ struct l2b_model {
     std::vector<LayerW> layers;
     bool finalized = false;
     int planes = 3;
+    // tensor parallelism: this process holds rank `rank` of `tp` shards.  Heads are split by kv group, the ffn by
+    // hidden units; wo and w2 are split along their INPUT (block columns), so their outputs are partial sums.
+    int tp = 1, rank = 0;
+    int l_heads = 0, l_kv = 0, l_hidden = 0;  // this rank's query heads, kv heads and hidden units
+    int l_qdim() const { return l_heads * (cfg.dim / cfg.n_heads); }
+    int l_kvdim() const { return l_kv * (cfg.dim / cfg.n_heads); }
 };
 
 struct l2b_session {
@@ -371,9 +386,17 @@ struct l2b_session {
     float last_ms = 0.f;
     unsigned long long* trace = nullptr;  // L2B_TRACE_TOKEN=1: per-launch, per-block timeline stamps (debugging aid)
     int trace_launches = 0;
+    // tensor parallelism.  tp_mem = [n_exch][tp][dim] f32 partial vectors, then [n_exch][tp] u32 arrival counters;
+    // n_exch = 2 * n_layers (one exchange after wo, one after w2).  Peers write into it through IPC mappings.
+    float* x2 = nullptr;          // second buffer of the residual stream (the summing prologue reads one, writes the other)
+    uint8_t* tp_mem = nullptr;
+    size_t tp_flag_off = 0, tp_bytes = 0;
+    unsigned* tp_epoch = nullptr;  // tokens completed (device word)
+    uint8_t* peer_mem[MV_MAX_TP] = {nullptr};  // [r]: rank r's tp_mem as seen from this process ([rank] = own)
+    bool tp_connected = false;
 };
 
-static size_t kv_layer_elems(const l2b_config& c) { return (size_t)c.n_kv_heads * c.seq_len * (c.dim / c.n_heads); }
+static size_t kv_layer_elems(const l2b_model* m) { return (size_t)m->l_kv * m->cfg.seq_len * (m->cfg.dim / m->cfg.n_heads); }
 
 extern "C" int32_t l2b_version(void) { return 100; }
 extern "C" const char* l2b_last_error_string(void) { return g_last_error.c_str(); }
@@ -412,10 +435,22 @@ extern "C" int32_t l2b_model_create(const l2b_config* c, l2b_model** out) {
     if (hs % 8 != 0 || hs > 128) return fail(L2B_ERR_BAD_ARG, "head size must be a multiple of 8 and at most 128");
     if (c->dim % 8 != 0 || c->hidden_dim % 8 != 0 || c->vocab_size % 2 != 0) return fail(L2B_ERR_BAD_ARG, "dim, hidden_dim must be multiples of 8 and vocab_size even");
     if (c->act_planes < 0 || c->act_planes > 3) return fail(L2B_ERR_BAD_ARG, "act_planes must be 0..3");
-    if (c->tp_size > 1) return fail(L2B_ERR_BAD_ARG, "tensor parallelism is not available in this build");
+    const int tp = c->tp_size <= 1 ? 1 : c->tp_size;
+    if (tp > 1) {
+        if (tp > MV_MAX_TP) return fail(L2B_ERR_BAD_ARG, "tp_size is at most 8");
+        if (c->tp_rank < 0 || c->tp_rank >= tp) return fail(L2B_ERR_BAD_ARG, "tp_rank must lie in [0, tp_size)");
+        if (c->n_kv_heads % tp != 0) return fail(L2B_ERR_BAD_ARG, "n_kv_heads must be a multiple of tp_size (heads are split by kv group)");
+        if ((c->dim / tp) % QK_K != 0 || (c->hidden_dim / tp) % QK_K != 0 || c->hidden_dim % tp != 0)
+            return fail(L2B_ERR_BAD_ARG, "dim / tp_size and hidden_dim / tp_size must be multiples of 256 (wo and w2 are split by super-block columns)");
+    }
     L2B_TRY(require_device());
     l2b_model* m = new l2b_model();
     m->cfg = *c;
+    m->tp = tp;
+    m->rank = tp > 1 ? c->tp_rank : 0;
+    m->l_heads = c->n_heads / tp;
+    m->l_kv = c->n_kv_heads / tp;
+    m->l_hidden = c->hidden_dim / tp;
     m->planes = c->act_planes == 0 ? 3 : c->act_planes;
     if (c->device >= 0) {
         cudaError_t e = cudaSetDevice(c->device);
@@ -457,6 +492,39 @@ extern "C" int32_t l2b_model_upload_tensor(l2b_model* m, int32_t role, int32_t l
         return upload_vector(dst, host, c.dim);
     };
     LayerW* lw = per_layer ? &m->layers[layer] : nullptr;
+    if (m->tp > 1) {
+        // The caller passes the FULL tensor on every rank; this rank keeps its shard.
+        //   rows (outputs) of wq / wk / wv / w1 / w3: a contiguous range, i.e. an offset pointer;
+        //   block columns (inputs) of wo / w2: the range [rank*nb/tp, (rank+1)*nb/tp) of every row, gathered on the host.
+        const int64_t r = m->rank, g = m->tp;
+        auto rows = [&](DevMatrix& dst, int64_t in, int64_t out) -> int32_t {
+            L2B_TRY(want(in, out));
+            if (!type_supported(type)) return fail(L2B_ERR_UNSUPPORTED_TYPE, "tensor type " + std::to_string(type) + " not implemented");
+            const int64_t row_bytes = type == T_F32 ? in * 4 : (in / QK_K) * file_block_bytes(type);
+            const int64_t lo = out / g;
+            return upload_matrix(dst, type, (const uint8_t*)host + r * lo * row_bytes, in, lo, 0);
+        };
+        auto cols = [&](DevMatrix& dst, int64_t in, int64_t out) -> int32_t {
+            L2B_TRY(want(in, out));
+            if (type != T_Q4_K && type != T_Q5_K && type != T_Q6_K)
+                return fail(L2B_ERR_UNSUPPORTED_TYPE, "tensor parallelism needs k-quant wo and w2 matrices");
+            const int64_t bb = file_block_bytes(type), nb = in / QK_K, nbl = nb / g;
+            std::vector<uint8_t> tmp((size_t)(out * nbl * bb));
+            for (int64_t o = 0; o < out; ++o)
+                memcpy(tmp.data() + (size_t)(o * nbl * bb), (const uint8_t*)host + (size_t)((o * nb + r * nbl) * bb), (size_t)(nbl * bb));
+            return upload_matrix(dst, type, tmp.data(), in / g, out, 0);
+        };
+        switch (role) {
+            case L2B_ROLE_WQ: return rows(lw->wq, c.dim, c.dim);
+            case L2B_ROLE_WK: return rows(lw->wk, c.dim, kv_dim);
+            case L2B_ROLE_WV: return rows(lw->wv, c.dim, kv_dim);
+            case L2B_ROLE_W1: return rows(lw->w1, c.dim, c.hidden_dim);
+            case L2B_ROLE_W3: return rows(lw->w3, c.dim, c.hidden_dim);
+            case L2B_ROLE_WO: return cols(lw->wo, c.dim, c.dim);
+            case L2B_ROLE_W2: return cols(lw->w2, c.hidden_dim, c.dim);
+            default: break;  // embedding, norms and the classifier are replicated
+        }
+    }
     switch (role) {
         case L2B_ROLE_TOKEN_EMBEDDING: L2B_TRY(want(c.dim, c.vocab_size)); return upload_matrix(m->tok_emb, type, host, in_dim, out_dim, 0);
         case L2B_ROLE_OUTPUT: L2B_TRY(want(c.dim, c.vocab_size)); return upload_matrix(m->output, type, host, in_dim, out_dim, 0);
@@ -483,7 +551,10 @@ extern "C" int32_t l2b_model_finalize(l2b_model* m) {
             !w.w2.present() || !w.w3.present())
             return fail(L2B_ERR_STATE, "missing blk." + std::to_string(l) + " weights");
         if (w.w1.type != w.w3.type) return fail(L2B_ERR_UNSUPPORTED_TYPE, "ffn gate and up matrices must have the same tensor type");
+        if (m->tp > 1 && (w.wq.type == T_F32 || w.wk.type == T_F32 || w.wv.type == T_F32 || w.w1.type == T_F32))
+            return fail(L2B_ERR_UNSUPPORTED_TYPE, "tensor parallelism needs k-quant layer matrices");
     }
+    if (m->tp > 1 && m->output.type == T_F32) return fail(L2B_ERR_UNSUPPORTED_TYPE, "tensor parallelism needs a k-quant output matrix");
     m->finalized = true;
     return L2B_OK;
 }
@@ -526,6 +597,12 @@ static void session_free(l2b_session* s) {
     for (void* b : bufs)
         if (b) cudaFree(b);
     if (s->trace) cudaFree(s->trace);
+    if (s->model)
+        for (int r = 0; r < s->model->tp; ++r)
+            if (s->peer_mem[r] && r != s->model->rank) cudaIpcCloseMemHandle(s->peer_mem[r]);
+    if (s->x2) cudaFree(s->x2);
+    if (s->tp_mem) cudaFree(s->tp_mem);
+    if (s->tp_epoch) cudaFree(s->tp_epoch);
     if (s->h_ctl) cudaFreeHost(s->h_ctl);
     if (s->h_small) cudaFreeHost(s->h_small);
     if (s->ev0) cudaEventDestroy(s->ev0);
@@ -542,7 +619,7 @@ static int32_t enqueue_token(l2b_session* s, int* nlaunch) {
     const l2b_model* m = s->model;
     const l2b_config& c = m->cfg;
     const int hs = c.dim / c.n_heads;
-    const size_t kvl = kv_layer_elems(c);
+    const size_t kvl = kv_layer_elems(m);
     int count = 0, last_grid = 0;
     bool first = true;
     auto mv = [&](MvLaunch& L) -> int32_t {
@@ -562,6 +639,46 @@ static int32_t enqueue_token(l2b_session* s, int* nlaunch) {
         L.p.rope_cs = s->rope_cs;
         L.p.seq_len = c.seq_len;
         L.p.status = s->status;
+        L.p.tp_size = m->tp;
+    };
+    // Tensor parallelism: the residual stream alternates between two buffers; `pending` is the exchange whose
+    // partial vectors the next rmsnorm prologue has to add (-1: none).
+    const int tp = m->tp;
+    float* xbuf[2] = {s->x, tp > 1 ? s->x2 : s->x};
+    int cur = 0, pending = -1, push_grid = 0;
+    auto xchg_vec = [&](uint8_t* base, int e, int r) { return reinterpret_cast<float*>(base) + ((size_t)e * tp + r) * c.dim; };
+    auto xchg_flag = [&](uint8_t* base, int e, int r) { return reinterpret_cast<unsigned*>(base + s->tp_flag_off) + (size_t)e * tp + r; };
+    // rmsnorm prologue over the residual stream; with an exchange pending it first forms x + sum of the partial vectors
+    auto norm_input = [&](MvLaunch& L, const float* gain) {
+        L.p.pro = PRO_RMSNORM;
+        L.p.gain = gain;
+        L.p.x_in = xbuf[cur];
+        if (pending >= 0) {
+            L.p.part_src = xchg_vec(s->tp_mem, pending, 0);
+            L.p.part_flag = xchg_flag(s->tp_mem, pending, 0);
+            L.p.tp_epoch = s->tp_epoch;
+            L.p.part_blocks = (unsigned)push_grid;
+            L.p.tp_timeout_ms = (unsigned)env_long("L2B_TP_TIMEOUT_MS", 10000);
+            L.p.x_out = xbuf[cur ^ 1];
+        }
+    };
+    auto norm_done = [&]() {  // after the launch(es) that consumed the pending exchange
+        if (pending >= 0) cur ^= 1;
+        pending = -1;
+    };
+    // output of a row-split matrix: residual add on one GPU, push of the partial vector with several
+    auto partial_output = [&](MvLaunch& L, const DevMatrix& w, int e) {
+        if (tp == 1) {
+            L.p.seg[L.p.nseg++] = make_segment(w, PAIR_ADJACENT, EPI_RESIDUAL, s->x, hs);
+            L.p.resid = s->x;
+            return;
+        }
+        L.p.seg[L.p.nseg++] = make_segment(w, PAIR_ADJACENT, EPI_PUSH, nullptr, hs);
+        L.p.tp_push = 1;
+        for (int r = 0; r < tp; ++r) {
+            L.p.push_dst[r] = xchg_vec(s->peer_mem[r], e, m->rank);
+            L.p.push_flag[r] = xchg_flag(s->peer_mem[r], e, m->rank);
+        }
     };
     const int rope_mode = c.rope_is_neox ? PAIR_NEOX : PAIR_ADJACENT;
     // --- token embedding row -> residual stream (inference.jl:236)
@@ -586,11 +703,10 @@ static int32_t enqueue_token(l2b_session* s, int* nlaunch) {
                 for (int i = 0; i < 3; ++i)
                     if ((segs[i].type == T_F32) == (cls == 0)) L.p.seg[L.p.nseg++] = segs[i];
                 if (L.p.nseg == 0) continue;
-                L.p.pro = PRO_RMSNORM;
-                L.p.x_in = s->x;
-                L.p.gain = w.rms_att;
+                norm_input(L, w.rms_att);
                 L2B_TRY(mv(L));
             }
+            norm_done();
         }
         // --- attention over the cache (inference.jl:263-278)
         {
@@ -599,19 +715,19 @@ static int32_t enqueue_token(l2b_session* s, int* nlaunch) {
             a.q = s->q; a.kc = kcl; a.vc = vcl; a.out = s->att; a.tickets = s->tickets;
             a.part_m = s->part_m; a.part_l = s->part_l; a.part_acc = s->part_acc;
             a.pos = &s->ctl->pos;
-            a.n_heads = c.n_heads; a.n_kv = c.n_kv_heads; a.hs = hs; a.seq_len = c.seq_len; a.nsplit = s->nsplit;
+            a.n_heads = m->l_heads; a.n_kv = m->l_kv; a.hs = hs; a.seq_len = c.seq_len; a.nsplit = s->nsplit;
             CU(launch_attention(a, s->gq, s->stream, true));
             ++count;
         }
         // --- output projection + residual (inference.jl:281-284)
         {
             MvLaunch L;
-            base_params(L, c.dim);
-            L.p.seg[L.p.nseg++] = make_segment(w.wo, PAIR_ADJACENT, EPI_RESIDUAL, s->x, hs);
+            base_params(L, m->l_qdim());
+            partial_output(L, w.wo, 2 * l);
             L.p.pro = PRO_COPY;
             L.p.x_in = s->att;
-            L.p.resid = s->x;
             L2B_TRY(mv(L));
+            if (tp > 1) pending = 2 * l, push_grid = last_grid;
         }
         // --- ffn rmsnorm + gate/up + SwiGLU (inference.jl:287-299)
         {
@@ -622,20 +738,19 @@ static int32_t enqueue_token(l2b_session* s, int* nlaunch) {
             g.w2 = w.w3.data;
             g.d6_2 = w.w3.d6;
             L.p.seg[L.p.nseg++] = g;
-            L.p.pro = PRO_RMSNORM;
-            L.p.x_in = s->x;
-            L.p.gain = w.rms_ffn;
+            norm_input(L, w.rms_ffn);
             L2B_TRY(mv(L));
+            norm_done();
         }
         // --- down projection + residual (inference.jl:302-305)
         {
             MvLaunch L;
-            base_params(L, c.hidden_dim);
-            L.p.seg[L.p.nseg++] = make_segment(w.w2, PAIR_ADJACENT, EPI_RESIDUAL, s->x, hs);
+            base_params(L, m->l_hidden);
+            partial_output(L, w.w2, 2 * l + 1);
             L.p.pro = PRO_COPY;
             L.p.x_in = s->hb;
-            L.p.resid = s->x;
             L2B_TRY(mv(L));
+            if (tp > 1) pending = 2 * l + 1, push_grid = last_grid;
         }
     }
     // --- final rmsnorm + classifier + per-block argmax (inference.jl:309-312)
@@ -643,12 +758,11 @@ static int32_t enqueue_token(l2b_session* s, int* nlaunch) {
         MvLaunch L;
         base_params(L, c.dim);
         L.p.seg[L.p.nseg++] = make_segment(m->output, PAIR_ADJACENT, EPI_LOGITS, s->logits, hs);
-        L.p.pro = PRO_RMSNORM;
-        L.p.x_in = s->x;
-        L.p.gain = m->rms_final;
+        norm_input(L, m->rms_final);
         L.p.amax_val = s->amax_val;
         L.p.amax_idx = s->amax_idx;
         L2B_TRY(mv(L));
+        norm_done();
     }
     // --- next token (inference.jl:354-368) and advance
     {
@@ -657,6 +771,7 @@ static int32_t enqueue_token(l2b_session* s, int* nlaunch) {
         f.logits = s->logits; f.vocab = c.vocab_size;
         f.amax_val = s->amax_val; f.amax_idx = s->amax_idx; f.nparts = last_grid;
         f.ctl = s->ctl; f.prompt = s->prompt; f.out_tokens = s->out_tokens; f.advance = 1; f.next_token = s->next_token;
+        f.tp_epoch = s->tp_epoch;
         CU(launch_kernel(finalize_token_kernel, dim3(1), dim3(FIN_THREADS), 0, s->stream, true, f));
         ++count;
     }
@@ -672,6 +787,22 @@ static cudaError_t cudaLaunchKernelEx_embed(const l2b_model* m, l2b_session* s, 
     cfg.stream = s->stream;
     return cudaLaunchKernelEx(&cfg, embed_row_kernel, m->tok_emb.type, (const uint8_t*)m->tok_emb.data, (const __half*)m->tok_emb.d6,
                               (const int*)&s->ctl->token, (int)m->cfg.dim, s->x);
+}
+
+static int32_t capture_token_graph(l2b_session* s) {
+    cudaGraph_t g = nullptr;
+    CU(cudaStreamBeginCapture(s->stream, cudaStreamCaptureModeThreadLocal));
+    int32_t es = enqueue_token(s, &s->kernels_per_token);
+    cudaError_t ce = cudaStreamEndCapture(s->stream, &g);
+    if (es != L2B_OK) {
+        if (g) cudaGraphDestroy(g);
+        return es;
+    }
+    CU(ce);
+    cudaError_t ie = cudaGraphInstantiate(&s->graph, g, 0);
+    cudaGraphDestroy(g);
+    CU(ie);
+    return L2B_OK;
 }
 
 extern "C" int32_t l2b_session_create(l2b_model* m, void* stream, l2b_session** out) {
@@ -696,23 +827,24 @@ extern "C" int32_t l2b_session_create(l2b_model* m, void* stream, l2b_session** 
             CU(cudaStreamCreateWithFlags(&s->stream, cudaStreamNonBlocking));
             s->own_stream = true;
         }
-        s->gq = choose_gq(c.n_heads, c.n_kv_heads);
-        const int groups = c.n_heads / s->gq;
+        s->gq = choose_gq(m->l_heads, m->l_kv);
+        const int groups = m->l_heads / s->gq;
         int ns = (s->di.sms + groups - 1) / groups;
         ns = std::max(1, std::min(ns, std::min(32, (c.seq_len + 7) / 8)));
         s->nsplit = (int)env_long("L2B_ATTN_SPLITS", ns);
-        const size_t kvl = kv_layer_elems(c);
+        const size_t kvl = kv_layer_elems(m);
+        // q, att, hb and the caches hold this rank's heads / hidden units only (everything, on one GPU)
         CU(cudaMalloc(&s->x, (size_t)c.dim * 4));
-        CU(cudaMalloc(&s->q, (size_t)c.dim * 4));
-        CU(cudaMalloc(&s->att, (size_t)c.dim * 4));
+        CU(cudaMalloc(&s->q, (size_t)m->l_qdim() * 4));
+        CU(cudaMalloc(&s->att, (size_t)m->l_qdim() * 4));
         CU(cudaMalloc(&s->tickets, (size_t)c.n_heads * 4));
-        CU(cudaMalloc(&s->hb, (size_t)c.hidden_dim * 4));
+        CU(cudaMalloc(&s->hb, (size_t)m->l_hidden * 4));
         CU(cudaMalloc(&s->logits, (size_t)c.vocab_size * 4));
         CU(cudaMalloc(&s->kc, kvl * c.n_layers * 4));
         CU(cudaMalloc(&s->vc, kvl * c.n_layers * 4));
-        CU(cudaMalloc(&s->part_m, (size_t)c.n_heads * s->nsplit * 4));
-        CU(cudaMalloc(&s->part_l, (size_t)c.n_heads * s->nsplit * 4));
-        CU(cudaMalloc(&s->part_acc, (size_t)c.n_heads * s->nsplit * hs * 4));
+        CU(cudaMalloc(&s->part_m, (size_t)m->l_heads * s->nsplit * 4));
+        CU(cudaMalloc(&s->part_l, (size_t)m->l_heads * s->nsplit * 4));
+        CU(cudaMalloc(&s->part_acc, (size_t)m->l_heads * s->nsplit * hs * 4));
         CU(cudaMalloc(&s->amax_val, (size_t)s->di.sms * 4));
         CU(cudaMalloc(&s->amax_idx, (size_t)s->di.sms * 4));
         CU(cudaMalloc(&s->ctl, sizeof(Control)));
@@ -740,20 +872,20 @@ extern "C" int32_t l2b_session_create(l2b_model* m, void* stream, l2b_session** 
             CU(cudaMalloc(&s->trace, n * 8));
             CU(cudaMemset(s->trace, 0, n * 8));
         }
-        // capture one token
-        cudaGraph_t g = nullptr;
-        CU(cudaStreamBeginCapture(s->stream, cudaStreamCaptureModeThreadLocal));
-        int32_t es = enqueue_token(s, &s->kernels_per_token);
-        cudaError_t ce = cudaStreamEndCapture(s->stream, &g);
-        if (es != L2B_OK) {
-            if (g) cudaGraphDestroy(g);
-            return es;
+        if (m->tp > 1) {
+            // exchange memory; the token graph is captured by l2b_session_tp_connect, once the peers' mappings exist
+            const size_t n_exch = 2 * (size_t)c.n_layers;
+            s->tp_flag_off = n_exch * m->tp * c.dim * 4;
+            s->tp_bytes = s->tp_flag_off + n_exch * m->tp * 4;
+            CU(cudaMalloc(&s->tp_mem, s->tp_bytes));
+            CU(cudaMemset(s->tp_mem, 0, s->tp_bytes));
+            CU(cudaMalloc(&s->x2, (size_t)c.dim * 4));
+            CU(cudaMalloc(&s->tp_epoch, 4));
+            CU(cudaMemset(s->tp_epoch, 0, 4));
+            s->peer_mem[m->rank] = s->tp_mem;
+            return L2B_OK;
         }
-        CU(ce);
-        cudaError_t ie = cudaGraphInstantiate(&s->graph, g, 0);
-        cudaGraphDestroy(g);
-        CU(ie);
-        return L2B_OK;
+        return capture_token_graph(s);
     };
     guard(run());
     if (st != L2B_OK) {
@@ -767,7 +899,7 @@ extern "C" int32_t l2b_session_create(l2b_model* m, void* stream, l2b_session** 
 extern "C" int32_t l2b_session_reset(l2b_session* s) {
     if (!s) return fail(L2B_ERR_BAD_ARG, "null session");
     CU(cudaSetDevice(s->model->device));
-    const size_t bytes = kv_layer_elems(s->model->cfg) * s->model->cfg.n_layers * 4;
+    const size_t bytes = kv_layer_elems(s->model) * s->model->cfg.n_layers * 4;
     CU(cudaMemsetAsync(s->kc, 0, bytes, s->stream));
     CU(cudaMemsetAsync(s->vc, 0, bytes, s->stream));
     CU(cudaStreamSynchronize(s->stream));
@@ -782,10 +914,48 @@ extern "C" int32_t l2b_session_destroy(l2b_session* s) {
     return L2B_OK;
 }
 
+// ---- tensor-parallel wiring --------------------------------------------------------------------
+// One process per GPU.  Each rank exports an IPC handle of its exchange memory; the host moves the handles between
+// the processes (any transport: torch.distributed, MPI, a file) and hands every rank the full list.
+extern "C" int32_t l2b_session_tp_handle(l2b_session* s, void* handle64) {
+    if (!s || !handle64) return fail(L2B_ERR_BAD_ARG, "null argument");
+    if (s->model->tp <= 1) return fail(L2B_ERR_STATE, "the model was created with tp_size <= 1");
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+    CU(cudaSetDevice(s->model->device));
+    cudaIpcMemHandle_t h;
+    CU(cudaIpcGetMemHandle(&h, s->tp_mem));
+    memcpy(handle64, &h, 64);
+    return L2B_OK;
+}
+
+extern "C" int32_t l2b_session_tp_connect(l2b_session* s, const void* handles, int32_t count) {
+    if (!s || !handles) return fail(L2B_ERR_BAD_ARG, "null argument");
+    const l2b_model* m = s->model;
+    if (m->tp <= 1) return fail(L2B_ERR_STATE, "the model was created with tp_size <= 1");
+    if (count != m->tp) return fail(L2B_ERR_BAD_ARG, "one handle per rank is needed, ordered by rank");
+    if (s->tp_connected) return fail(L2B_ERR_STATE, "the session is connected already");
+    CU(cudaSetDevice(m->device));
+    for (int r = 0; r < m->tp; ++r) {
+        if (r == m->rank) continue;
+        cudaIpcMemHandle_t h;
+        memcpy(&h, (const uint8_t*)handles + (size_t)r * 64, 64);
+        void* ptr = nullptr;
+        CU(cudaIpcOpenMemHandle(&ptr, h, cudaIpcMemLazyEnablePeerAccess));
+        s->peer_mem[r] = (uint8_t*)ptr;
+    }
+    L2B_TRY(capture_token_graph(s));
+    s->tp_connected = true;
+    return L2B_OK;
+}
+
 static int32_t check_status_word(l2b_session* s) {
     if (s->h_small[1] == DEV_ERR_TMA_TIMEOUT) {
         cudaMemsetAsync(s->status, 0, 4, s->stream);
         return fail(L2B_ERR_TIMEOUT, "a bounded wait on a weight copy ran out inside a kernel");
+    }
+    if (s->h_small[1] == DEV_ERR_PEER_TIMEOUT) {
+        cudaMemsetAsync(s->status, 0, 4, s->stream);
+        return fail(L2B_ERR_TIMEOUT, "the partial results of another tensor-parallel rank did not arrive in time");
     }
     if (s->h_small[1] != DEV_OK) {
         cudaMemsetAsync(s->status, 0, 4, s->stream);
@@ -800,6 +970,7 @@ static int32_t run_one(l2b_session* s, int token, int pos, float temperature, do
     if (token < 0 || token >= c.vocab_size) return fail(L2B_ERR_BAD_ARG, "token id out of range");
     if (pos < 0 || pos >= c.seq_len) return fail(L2B_ERR_BAD_ARG, "position out of range (seq_len)");
     if (temperature < 0.f) return fail(L2B_ERR_BAD_ARG, "temperature must be >= 0");
+    if (!s->graph) return fail(L2B_ERR_STATE, "tensor-parallel session: call l2b_session_tp_connect first");
     CU(cudaSetDevice(s->model->device));
     Control& h = *s->h_ctl;
     memset(&h, 0, sizeof(h));
@@ -868,6 +1039,7 @@ extern "C" int32_t l2b_generate(l2b_session* s, const int32_t* prompt, int32_t n
     if (temperature < 0.f) return fail(L2B_ERR_BAD_ARG, "temperature must be >= 0");
     for (int i = 0; i < n_prompt; ++i)
         if (prompt[i] < 0 || prompt[i] >= c.vocab_size) return fail(L2B_ERR_BAD_ARG, "prompt token id out of range");
+    if (!s->graph) return fail(L2B_ERR_STATE, "tensor-parallel session: call l2b_session_tp_connect first");
     CU(cudaSetDevice(s->model->device));
     Control& h = *s->h_ctl;
     memset(&h, 0, sizeof(h));

@@ -23,7 +23,7 @@ __host__ __device__ constexpr int file_block_bytes(int type) {
 }
 
 // Error codes written to a session's device status word by kernels (0 = fine).
-enum : int { DEV_OK = 0, DEV_ERR_TMA_TIMEOUT = 1, DEV_ERR_BAD_INDEX = 2 };
+enum : int { DEV_OK = 0, DEV_ERR_TMA_TIMEOUT = 1, DEV_ERR_BAD_INDEX = 2, DEV_ERR_PEER_TIMEOUT = 3 };
 
 // Upper bound on polls of an mbarrier before a kernel gives up.  A poll is a test plus a short sleep
 // (tens of nanoseconds), so this is a few tenths of a second: far beyond any legitimate wait

@@ -31,7 +31,13 @@
 namespace l2b {
 
 enum : int { PRO_COPY = 0, PRO_RMSNORM = 1 };
-enum : int { EPI_STORE = 0, EPI_RESIDUAL = 1, EPI_SWIGLU = 2, EPI_ROPE_Q = 3, EPI_ROPE_K = 4, EPI_STORE_V = 5, EPI_LOGITS = 6 };
+enum : int { EPI_STORE = 0, EPI_RESIDUAL = 1, EPI_SWIGLU = 2, EPI_ROPE_Q = 3, EPI_ROPE_K = 4, EPI_STORE_V = 5, EPI_LOGITS = 6, EPI_PUSH = 7 };
+// Tensor parallelism (no counterpart in the reference): a row-split matrix (wo, w2) yields a PARTIAL output vector
+// per GPU.  EPI_PUSH writes this GPU's partial vector into every GPU's exchange buffer with plain stores over
+// NVLink and, when a block has written all its rows, bumps an arrival counter on every GPU.  The next kernel's
+// rmsnorm prologue waits (bounded) until every GPU's counter has reached this token's value and then forms
+// x_new = x + sum_r partial_r in rank order, so that all GPUs hold bit-identical residual streams.
+constexpr int MV_MAX_TP = 8;
 // How the 8 row pairs (A, B) of a tile map to matrix rows.  Pair j of a tile occupies tile rows j and j+8.
 //   ADJACENT: rows (2t, 2t+1)            -- plain outputs and interleaved RoPE pairs
 //   NEOX    : rows (i, i + head_size/2)  -- NeoX RoPE pairs
@@ -92,6 +98,17 @@ struct MvParams {
     int seq_len;
     float* amax_val;        // EPI_LOGITS: per-block best value   [gridDim.x]
     int* amax_idx;          // EPI_LOGITS: per-block best index   [gridDim.x]
+    // tensor parallelism (tp_size <= 1: unused)
+    int tp_size;
+    int tp_push;                          // this launch ends in EPI_PUSH
+    float* push_dst[MV_MAX_TP];           // [r]: where this GPU's partial vector lives in GPU r's exchange buffer
+    unsigned* push_flag[MV_MAX_TP];       // [r]: this GPU's arrival counter in GPU r's memory
+    const float* part_src;                // prologue: partial vectors [tp_size][n_in] in this GPU's exchange buffer, or null
+    const unsigned* part_flag;            // prologue: arrival counters [tp_size] in this GPU's memory
+    const unsigned* tp_epoch;             // tokens completed so far (device word, advanced once per token)
+    unsigned part_blocks;                 // blocks of the pushing launch (arrivals per GPU and token)
+    unsigned tp_timeout_ms;               // bound on the wait for the other GPUs
+    float* x_out;                         // prologue: block 0 writes x_new here (the residual stream is double-buffered)
     int* status;            // device status word
     int debug;              // measurement aid: bit 0 = consumers skip the arithmetic, bit 1 = the producer skips the copies (results are wrong)
     unsigned long long* trace;  // optional timeline: 16 globaltimer stamps per block (debugging aid), or null
@@ -208,7 +225,7 @@ __device__ __noinline__ void quantise_block(float4 va, float4 vb, int lane, uint
 
 // Build the activation vector in shared memory.  KQ: int8 planes + sums; else f32 copy.
 // A warp takes 32 consecutive groups of 8 values (= one 256-value block) per turn.
-template <bool KQ, int P>
+template <bool KQ, int P, bool TP = false>
 __device__ __forceinline__ void build_activation(const MvParams& p, uint8_t* smem, const MvSmem& L, int warp, int lane, int nwarps) {
     const int n = p.n_in;
     float* red = reinterpret_cast<float*>(smem + L.off_red);
@@ -221,12 +238,48 @@ __device__ __forceinline__ void build_activation(const MvParams& p, uint8_t* sme
     const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
 
     auto group_of = [&](int turn) { return 32 * (warp + nwarps * turn) + lane; };
-    auto fetch = [&](int turn, float4& a, float4& b) {
+    const bool tp_sum = TP && p.part_src != nullptr;  // TP = false compiles the exchange out of single-GPU kernels
+    if (tp_sum) {
+        // one lane per GPU waits until that GPU's partial vector of this token has arrived in full
+        if (warp == 0 && lane < p.tp_size && __ldcg(p.status) == DEV_OK) {
+            const unsigned want = (__ldcg(p.tp_epoch) + 1u) * p.part_blocks;
+            const unsigned long long t0 = global_ns(), limit = (unsigned long long)p.tp_timeout_ms * 1000000ull;
+            bool ok = false;
+            for (;;) {
+                unsigned have;
+                asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(have) : "l"(p.part_flag + lane) : "memory");
+                if ((int)(have - want) >= 0) {
+                    ok = true;
+                    break;
+                }
+                if (global_ns() - t0 > limit) break;
+                __nanosleep(200);
+            }
+            if (!ok) atomicExch(p.status, DEV_ERR_PEER_TIMEOUT);
+        }
+        consumer_sync(nwarps * 32);
+    }
+    // write_back: block 0 stores the summed residual stream (first pass over the vector only)
+    auto fetch = [&](int turn, float4& a, float4& b, bool write_back = false) {
         const int g = group_of(turn);
         a = b = zero4;
         if (g < n8) {
             a = __ldcg(reinterpret_cast<const float4*>(p.x_in + 8 * g));
             b = __ldcg(reinterpret_cast<const float4*>(p.x_in + 8 * g + 4));
+            if (tp_sum) {
+#pragma unroll 1
+                for (int r = 0; r < p.tp_size; ++r) {  // rank order on every GPU: identical sums everywhere
+                    const float* src = p.part_src + (size_t)r * n + 8 * g;
+                    const float4 pa = __ldcg(reinterpret_cast<const float4*>(src));
+                    const float4 pb = __ldcg(reinterpret_cast<const float4*>(src + 4));
+                    a.x += pa.x; a.y += pa.y; a.z += pa.z; a.w += pa.w;
+                    b.x += pb.x; b.y += pb.y; b.z += pb.z; b.w += pb.w;
+                }
+                if (write_back && blockIdx.x == 0) {
+                    *reinterpret_cast<float4*>(p.x_out + 8 * g) = a;
+                    *reinterpret_cast<float4*>(p.x_out + 8 * g + 4) = b;
+                }
+            }
         }
     };
     auto emit = [&](int turn, float4 a, float4 b) {
@@ -259,7 +312,7 @@ __device__ __forceinline__ void build_activation(const MvParams& p, uint8_t* sme
         float4 ga[MV_GAIN_BLOCKS], gb[MV_GAIN_BLOCKS];  // gains of the register-held turns, loaded with x, not after the sum
         float ss = 0.f;
 #pragma unroll
-        for (int u = 0; u < MV_REG_BLOCKS; ++u) fetch(u, ka[u], kb[u]);
+        for (int u = 0; u < MV_REG_BLOCKS; ++u) fetch(u, ka[u], kb[u], true);
 #pragma unroll
         for (int u = 0; u < MV_GAIN_BLOCKS; ++u) {
             const int g = group_of(u);
@@ -273,7 +326,7 @@ __device__ __forceinline__ void build_activation(const MvParams& p, uint8_t* sme
         for (int u = 0; u < MV_REG_BLOCKS; ++u) ss = sumsq(ka[u], kb[u], ss);
         for (int turn = MV_REG_BLOCKS; turn < turns; ++turn) {
             float4 a, b;
-            fetch(turn, a, b);
+            fetch(turn, a, b, true);
             ss = sumsq(a, b, ss);
         }
         float tot = block_sum(ss, red, warp, lane, nwarps);
@@ -400,6 +453,7 @@ __device__ __forceinline__ void arg_update(ArgBest& b, float v, int i) {
     }
 }
 
+template <bool TP = false>
 __device__ __forceinline__ void epilogue_pair(const MvParams& p, const MvSegment& sg, int t, float vA, float vB, int pos, ArgBest& best) {
     int rowA, rowB;
     pair_rows(p, sg, t, rowA, rowB);
@@ -449,11 +503,21 @@ __device__ __forceinline__ void epilogue_pair(const MvParams& p, const MvSegment
             arg_update(best, vA, rowA);
             arg_update(best, vB, rowB);
             break;
+        case EPI_PUSH:
+            if (TP) {
+#pragma unroll
+                for (int r = 0; r < MV_MAX_TP; ++r)
+                    if (r < p.tp_size) {
+                        p.push_dst[r][rowA] = vA;
+                        p.push_dst[r][rowB] = vB;
+                    }
+            }
+            break;
     }
 }
 
 // ---- the kernel --------------------------------------------------------------------------------
-template <bool KQ, int P>
+template <bool KQ, int P, bool TP = false>
 __global__ void __launch_bounds__((MV_MAX_CONSUMERS + 2) * 32, 1) fused_matvec_kernel(const __grid_constant__ MvParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -648,13 +712,22 @@ __global__ void __launch_bounds__((MV_MAX_CONSUMERS + 2) * 32, 1) fused_matvec_k
             v += __shfl_xor_sync(0xffffffffu, v, 16);     // (even warps) + (odd warps)
             const float vB = __shfl_sync(0xffffffffu, v, (lane & 7) + 8);
             const int t = (unit - seg_first) * MV_TILE_PAIRS + lane;
-            if (lane < MV_TILE_PAIRS && t < sg.npairs) epilogue_pair(p, sg, t, v, vB, pos, best);
+            if (lane < MV_TILE_PAIRS && t < sg.npairs) epilogue_pair<TP>(p, sg, t, v, vB, pos, best);
             if (++rb == MV_RED_BUFS) {
                 rb = 0;
                 par ^= 1u;
             }
         }
         if (dead && lane == 0) atomicExch(p.status, DEV_ERR_TMA_TIMEOUT);
+        if (TP && p.tp_push) {  // every row of this block is on its way: tell each GPU (blocks without rows report too)
+            __threadfence_system();
+            __syncwarp();
+            unsigned* flag = nullptr;
+#pragma unroll
+            for (int r = 0; r < MV_MAX_TP; ++r)
+                if (lane == r && r < p.tp_size) flag = p.push_flag[r];
+            if (flag) atomicAdd_system(flag, 1u);
+        }
         if (p.amax_val) {  // EPI_LOGITS: first maximal index over this block's rows
             for (int o = 16; o > 0; o >>= 1) {
                 const float ov = __shfl_xor_sync(0xffffffffu, best.v, o);
@@ -675,7 +748,7 @@ __global__ void __launch_bounds__((MV_MAX_CONSUMERS + 2) * 32, 1) fused_matvec_k
     pdl_wait();
     MV_TRACE(2);
 
-    build_activation<KQ, P>(p, smem, L, warp, lane, W);
+    build_activation<KQ, P, TP>(p, smem, L, warp, lane, W);
     MV_TRACE(3);
 
     const int pos = p.pos ? __ldcg(p.pos) : 0;

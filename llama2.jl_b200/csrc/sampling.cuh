@@ -36,6 +36,7 @@ struct FinalizeParams {
     int* out_tokens;    // out_tokens[pos] = token chosen after position pos (may be null)
     int advance;        // 1: ctl->token = next, ctl->pos += 1
     int* next_token;    // single-slot result for one-step calls
+    unsigned* tp_epoch; // tensor parallelism: count of completed tokens, advanced here (null on one GPU)
 };
 
 constexpr int FIN_THREADS = 1024;
@@ -140,6 +141,7 @@ __global__ void __launch_bounds__(FIN_THREADS) finalize_token_kernel(const __gri
             p.ctl->token = next;
             p.ctl->pos = pos + 1;
         }
+        if (p.tp_epoch) *p.tp_epoch += 1u;
     }
 }
 

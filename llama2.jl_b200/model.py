@@ -98,12 +98,12 @@ class TransformerWeights:
 class _DeviceModel:
     """Owns an l2b_model and one l2b_session (RunState)."""
 
-    def __init__(self, config: ModelConfig, weights: TransformerWeights, act_planes=0, device=-1, stream=None):
+    def __init__(self, config: ModelConfig, weights: TransformerWeights, act_planes=0, device=-1, stream=None, tp_size=1, tp_rank=0):
         lib = L.lib()
         cfg = L.Config(dim=config.dim, hidden_dim=config.hidden_dim, n_layers=config.n_layers, n_heads=config.n_heads,
                        n_kv_heads=config.n_kv_heads, vocab_size=config.vocab_size, seq_len=config.seq_len,
                        rope_freq_base=float(config.rope_freq_base), rope_is_neox=int(bool(config.rope_is_neox)),
-                       act_planes=act_planes, device=device, tp_size=1, tp_rank=0)
+                       act_planes=act_planes, device=device, tp_size=tp_size, tp_rank=tp_rank)
         self.model = C.c_void_p()
         self.session = C.c_void_p()
         L.check(lib.l2b_model_create(C.byref(cfg), C.byref(self.model)))
@@ -153,14 +153,16 @@ class LanguageModel:
     k-quant integer dot products; the device copy of the weights is made on first use.
     """
 
-    def __init__(self, config: ModelConfig, tokenizer, weights: TransformerWeights, act_planes: int = 0, device: int = -1, stream=None):
+    def __init__(self, config: ModelConfig, tokenizer, weights: TransformerWeights, act_planes: int = 0, device: int = -1, stream=None,
+                 tp_size: int = 1, tp_rank: int = 0):
         self.config, self.tokenizer, self.weights = config, tokenizer, weights
         self.act_planes, self.device, self.stream = act_planes, device, stream
+        self.tp_size, self.tp_rank = tp_size, tp_rank  # tensor parallelism: see tp.py (one process per GPU)
         self._dev: Optional[_DeviceModel] = None
 
     def device_model(self) -> _DeviceModel:
         if self._dev is None:
-            self._dev = _DeviceModel(self.config, self.weights, self.act_planes, self.device, self.stream)
+            self._dev = _DeviceModel(self.config, self.weights, self.act_planes, self.device, self.stream, self.tp_size, self.tp_rank)
         return self._dev
 
     def close(self):
