@@ -74,12 +74,14 @@ def workload_spec(synth, name):
         return synth.TINY_F32, "llama2.c f32 dim 288 x 6 layers, 16 prompt ids + 240 greedy tokens"
     if name == "phi3":
         return synth.PHI3_MINI_Q5_K_M, "phi3-mini-shape Q5_K_M, 2048 prompt ids + 512 greedy tokens, seq_len 4096"
+    if name == "70b-tp":
+        return synth.LLAMA2_70B_Q4_K, "llama2-70b-shape q4_K (q6_K output), tensor parallel, 512 prompt ids + 256 greedy tokens, batch 1, seq_len 4096"
     raise SystemExit(f"unknown workload {name}")
 
 
-def kv_bytes_per_run(cfg, n_positions):
+def kv_bytes_per_run(cfg, n_positions, tp=1):
     hs = cfg.dim // cfg.n_heads
-    per_pos = 2 * hs * cfg.n_kv_heads * 4 * cfg.n_layers  # f32 keys + values of one position, all layers
+    per_pos = 2 * hs * (cfg.n_kv_heads // tp) * 4 * cfg.n_layers  # f32 keys + values of one position, all layers (this GPU's heads)
     return per_pos * sum(p + 1 for p in range(n_positions))
 
 
@@ -121,7 +123,7 @@ def run_matvec(args):
     peak, kind = measured_peak()
     line = {"metric": "k-quant dequant-matvec, batch 1", "value": round(us, 3), "unit": "us per matvec", "n_gpus": 1, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": round(ms / args.steps, 4), "higher_is_better": False, "vs_baseline": None,
-            "dtype": f"int8 x k-quant integer dot products (dp4a), f32 accumulate; {planes} int8 activation plane(s)",
+            "dtype": f"int8 activation planes x k-quant integers on int8 tensor-core MMAs, f32 accumulate; {planes} int8 activation plane(s)",
             "data": "synthetic", "config": {"workload": f"{args.workload} W {n_out}x{n_in}, {copies} rotating copies, {launches} launches per step"},
             "gpu_launches": args.steps * launches,
             "roofline": {"bound": "hbm", "achieved": round(nbytes / us / 1e3, 1), "peak": peak, "unit": "GB/s",
@@ -147,13 +149,26 @@ def run_ours(args):
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     spec, wl_name = workload_spec(synth, args.workload)
+    tp_mode = args.workload == "70b-tp"  # all GPUs work on ONE token stream (strong scaling); otherwise N replicas
+    if tp_mode and world < 2:
+        raise SystemExit("--workload 70b-tp needs --gpus 2, 4 or 8 (one rank per GPU under torch.distributed.run)")
+    if args.layers > 0:
+        spec = synth.scaled(spec, n_layers=args.layers)
+        wl_name += f" [reduced to {args.layers} layers]"
     cfg = spec["config"]
     n_pos = spec["n_prompt"] + spec["n_decode"]
     if args.positions > 0:  # shortened run (profiling captures); not the benchmark configuration
         n_pos = args.positions
         wl_name += f" [shortened to {n_pos} positions]"
-    weights = synth.model_weights(cfg, spec["types"], seed=2024, tied_output=spec["tied"])
-    model = pkg.LanguageModel(cfg, None, weights, act_planes=args.act_planes, device=local)
+    if tp_mode:
+        from llama2_jl_b200 import tp
+        # four distinct layers, reused in turn: the full host copy (38.7 GB per rank) would not fit beside the other ranks'
+        weights = synth.model_weights(cfg, spec["types"], seed=2024, tied_output=spec["tied"], distinct_layers=4)
+        model = pkg.LanguageModel(cfg, None, weights, act_planes=args.act_planes, device=local, tp_size=world, tp_rank=rank)
+        tp.connect(model)
+    else:
+        weights = synth.model_weights(cfg, spec["types"], seed=2024, tied_output=spec["tied"])
+        model = pkg.LanguageModel(cfg, None, weights, act_planes=args.act_planes, device=local)
     prompt = synth.prompt_tokens(spec, 2024)[:n_pos]
     wbytes = model.weight_bytes_per_token()
     kpt = model.kernels_per_token()
@@ -207,25 +222,28 @@ def run_ours(args):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     dev_ms, e2e_s = float(t[0]), float(t[1])
     ms_per_step = dev_ms / args.steps
-    value = world * n_pos * args.steps / (dev_ms / 1e3)
-    e2e_value = world * n_pos * e2e_steps / e2e_s
+    streams = 1 if tp_mode else world
+    value = streams * n_pos * args.steps / (dev_ms / 1e3)
+    e2e_value = streams * n_pos * e2e_steps / e2e_s
     peak, peak_kind = measured_peak()
-    algo_bytes = wbytes * n_pos + kv_bytes_per_run(cfg, n_pos)  # per step (one run)
+    algo_bytes = wbytes * n_pos + kv_bytes_per_run(cfg, n_pos, world if tp_mode else 1)  # per step (one run) and GPU
     achieved = algo_bytes / (ms_per_step / 1e3) / 1e9
     line = {
-        "metric": METRIC, "value": round(value, 2), "unit": "tok/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": round(ms_per_step, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": "int8 x k-quant integer dot products (dp4a), f32 accumulate; %d int8 activation plane(s)" % (args.act_planes or 3),
+        "metric": METRIC if not tp_mode else "decode tok/s @Llama-2-70B-shape q4_K, batch 1, tensor parallel; % of HBM roofline",
+        "value": round(value, 2), "unit": "tok/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": round(ms_per_step, 4), "higher_is_better": True, "scaling": "strong" if tp_mode else "weak", "vs_baseline": None,
+        "dtype": "int8 activation planes x k-quant integers on int8 tensor-core MMAs, f32 accumulate; %d int8 activation plane(s)" % (args.act_planes or 3),
         "data": "synthetic (seeded random weights and token ids)",
         "config": {"workload": wl_name, "positions_per_step": n_pos, "act_planes": args.act_planes or 3,
                    "l2": "inputs larger than L2 (%.2f GB of weights streamed per position)" % (wbytes / 1e9),
-                   "multi_gpu": "replicas only" if world > 1 else "single GPU"},
+                   "multi_gpu": ("tensor parallel over %d GPUs, partial vectors exchanged by peer stores" % world) if tp_mode
+                   else ("replicas only" if world > 1 else "single GPU")},
         "e2e": {"value": round(e2e_value, 2), "unit": "tok/s", "h2d_bytes_per_step": 48 * n_pos, "d2h_bytes_per_step": 8 * n_pos,
                 "note": "one l2b_decode_next call per position, wall clock"},
         "gpu_launches": kpt * n_pos * args.steps,
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s", "frac": round(achieved / peak, 4),
                      "traffic": None, "peak_kind": peak_kind, "frac_of_nominal_8000": round(achieved / 8000.0, 4),
-                     "scope": "whole token (all kernels): weight + KV bytes per position / device time per position",
+                     "scope": "whole token (all kernels): weight + KV bytes per position (of one GPU) / device time per position",
                      "bytes_per_position": int(algo_bytes / n_pos)},
         "clocks": clocks,
         "us_per_token": round(ms_per_step * 1e3 / n_pos, 2),
@@ -316,7 +334,8 @@ def main():
     ap.add_argument("--steps", type=int, default=3)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="8b", choices=["8b", "tiny", "phi3", "matvec-q4k", "matvec-q5k", "matvec-q6k"])
+    ap.add_argument("--workload", default="8b", choices=["8b", "tiny", "phi3", "70b-tp", "matvec-q4k", "matvec-q5k", "matvec-q6k"])
+    ap.add_argument("--layers", type=int, default=0, help="run the workload's shape with this many layers (0 = all)")
     ap.add_argument("--matvec-in", type=int, default=4096)
     ap.add_argument("--matvec-out", type=int, default=14336)
     ap.add_argument("--matvec-copies", type=int, default=8)

@@ -614,58 +614,76 @@ __global__ void __launch_bounds__((MV_MAX_CONSUMERS + 2) * 32, 1) fused_matvec_k
         // hundreds of cycles here.  Group g owns slots g*NSG .. g*NSG+NSG-1 and takes tiles g, g+cgroups, ...
         const int CG = p.cgroups, NSG = NS / CG;
         int slot_g[2] = {0, NSG}, ph_g[2] = {0, 0};
-        TileSrc ts = tile_src(0);
+        TileSrc tsA = tile_src(0);                                 // the tile group 0 works on next
+        TileSrc tsB = tile_src(my_units);                          // the tile group 1 works on next: worked out after A's first copies are out
+        bool needB = (CG == 2);
         if (p.trace && lane == 0) p.trace[blockIdx.x * 16 + 9] = global_ns();
         // Fast path for the common case (one segment, adjacent or dual rows, full tiles): the next tile's source
         // is the current one plus a constant.
         const bool linear = (p.nseg == 1) && (p.seg[0].pair_mode != PAIR_NEOX);
         const size_t tile_step = linear ? (size_t)gridDim.x * (p.seg[0].pair_mode == PAIR_ADJACENT ? 16 : 8) * nb * dev_block_bytes(p.seg[0].type) : 0;
         const int full_tiles = linear ? p.seg[0].npairs / MV_TILE_PAIRS : 0;  // tiles below this index are complete
-        for (int j = 0; j < my_units && !dead; ++j) {
-            const int grp = (CG == 2) ? (j & 1) : 0;
-            int slot_i = grp ? slot_g[1] : slot_g[0], ph = grp ? ph_g[1] : ph_g[0];
+        // One stage of one tile into the next slot of group `grp` (a literal at every call, so the counters stay in
+        // registers).  Returns false when the wait for a free slot ran out.
+        auto issue = [&](const TileSrc& ts, const int grp, int it) -> bool {
+            int slot_i = slot_g[grp], ph = ph_g[grp];
+            // wait until every consumer warp of the group has released what this slot held before
+            if (ph > 0) {
+                int ok = 1;
+                if (c == 0) ok = mbar_wait_bounded(empty + slot_i, (uint32_t)((ph & 1) ^ 1)) ? 1 : 0;
+                ok = __shfl_sync(0x0000ffffu, ok, 0);
+                if (!ok) return false;
+            }
+            uint32_t bytes = ts.bytes0, tx = ts.tx0;
+            if (nit > 1) {  // a stage is a 16-block slice of every row (one row per copy)
+                const int nblk = min(MV_TILE_BLOCKS, nb - it * MV_TILE_BLOCKS);
+                bytes = ts.nrows ? (uint32_t)(nblk * ts.bb) : 0u;
+                tx = (uint32_t)(ts.nvalid * nblk * ts.bb);
+            }
+            if (p.debug & 2) bytes = tx = 0;
+            if (first && p.trace && lane == 0) p.trace[blockIdx.x * 16 + 10] = global_ns();
+            if (c == 0) mbar_arrive_expect_tx(full + slot_i, tx);
+            __syncwarp(0x0000ffffu);
+            if (first && p.trace && lane == 0) p.trace[blockIdx.x * 16 + 11] = global_ns();
+            if (bytes)
+                bulk_g2s(ring + (size_t)slot_i * L.slot_bytes + (size_t)c * ts.gs, ts.src + (size_t)it * (MV_TILE_BLOCKS * ts.bb), bytes, full + slot_i, policy);
+            if (first && p.trace && lane == 0) p.trace[blockIdx.x * 16 + 1] = global_ns();
+            first = false;
+            if (++slot_i == (grp + 1) * NSG) {
+                slot_i = grp * NSG;
+                ++ph;
+            }
+            slot_g[grp] = slot_i;
+            ph_g[grp] = ph;
+            return true;
+        };
+        // The stages of the two groups' tiles are issued alternately (A0 B0 A1 B1 ...): a tile of several stages
+        // would otherwise hold the producer at its own group's slots while the other group's slots sit empty.
+        for (int j = 0; j < my_units && !dead; j += CG) {
+            const bool hasB = (CG == 2) && (j + 1 < my_units);
             for (int it = 0; it < nit; ++it) {
-                // wait until every consumer warp of the group has released what this slot held before
-                if (ph > 0) {
-                    int ok = 1;
-                    if (c == 0) ok = mbar_wait_bounded(empty + slot_i, (uint32_t)((ph & 1) ^ 1)) ? 1 : 0;
-                    ok = __shfl_sync(0x0000ffffu, ok, 0);
-                    if (!ok) {
-                        dead = true;
-                        break;
+                bool ok = issue(tsA, 0, it);
+                if (ok && hasB) {
+                    if (needB) {
+                        tsB = tile_src(j + 1);
+                        needB = false;
                     }
+                    ok = issue(tsB, 1, it);
                 }
-                uint32_t bytes = ts.bytes0, tx = ts.tx0;
-                if (nit > 1) {  // a stage is a 16-block slice of every row (one row per copy)
-                    const int nblk = min(MV_TILE_BLOCKS, nb - it * MV_TILE_BLOCKS);
-                    bytes = ts.nrows ? (uint32_t)(nblk * ts.bb) : 0u;
-                    tx = (uint32_t)(ts.nvalid * nblk * ts.bb);
-                }
-                if (p.debug & 2) bytes = tx = 0;
-                if (first && p.trace && lane == 0) p.trace[blockIdx.x * 16 + 10] = global_ns();
-                if (c == 0) mbar_arrive_expect_tx(full + slot_i, tx);
-                __syncwarp(0x0000ffffu);
-                if (first && p.trace && lane == 0) p.trace[blockIdx.x * 16 + 11] = global_ns();
-                if (bytes)
-                    bulk_g2s(ring + (size_t)slot_i * L.slot_bytes + (size_t)c * ts.gs, ts.src + (size_t)it * (MV_TILE_BLOCKS * ts.bb), bytes, full + slot_i, policy);
-                if (first && p.trace && lane == 0) p.trace[blockIdx.x * 16 + 1] = global_ns();
-                first = false;
-                if (++slot_i == (grp + 1) * NSG) {
-                    slot_i = grp * NSG;
-                    ++ph;
+                if (!ok) {
+                    dead = true;
+                    break;
                 }
             }
-            if (grp) {
-                slot_g[1] = slot_i;
-                ph_g[1] = ph;
+            // parameters of the next tiles (in the shadow of the wait for their slots)
+            const int next_last = (int)blockIdx.x + (j + 2 * CG - 1) * (int)gridDim.x;  // the later of the next tiles
+            if (linear && next_last < full_tiles) {
+                tsA.src += (size_t)CG * tile_step;
+                tsB.src += (size_t)CG * tile_step;
             } else {
-                slot_g[0] = slot_i;
-                ph_g[0] = ph;
+                tsA = tile_src(j + CG);
+                tsB = tile_src(CG == 2 ? j + CG + 1 : my_units);
             }
-            // parameters of the next tile (in the shadow of the wait for its slot)
-            const int next_tile = (int)blockIdx.x + (j + 1) * (int)gridDim.x;
-            if (linear && next_tile < full_tiles) ts.src += tile_step;
-            else ts = tile_src(j + 1);
         }
         if (dead) {
             // a consumer gave up: let copies still in flight land (bounded) before shared memory is released

@@ -37,13 +37,18 @@ def _seed(base, layer, role):
     return (base * 1000003 + layer * 101 + role) & 0xFFFFFFFFFFFF
 
 
-def model_weights(c: ModelConfig, types: dict, seed: int, tied_output=False) -> TransformerWeights:
-    """types maps 'wq','wk','wv','wo','w1','w2','w3','token_embd','output' to a ggml type.  Norm gains are 1."""
+def model_weights(c: ModelConfig, types: dict, seed: int, tied_output=False, distinct_layers: int = 0) -> TransformerWeights:
+    """types maps 'wq','wk','wv','wo','w1','w2','w3','token_embd','output' to a ggml type.  Norm gains are 1.
+    distinct_layers = k > 0: only the first k layers are generated and layer l reuses the host arrays of layer l % k
+    (every layer still gets its own device copy), for shapes whose full host copy would not fit in memory."""
     hs = c.dim // c.n_heads
     kv = hs * c.n_kv_heads
     ones = np.ones(c.dim, dtype=np.float32)
     layers = []
     for l in range(c.n_layers):
+        if distinct_layers and l >= distinct_layers:
+            layers.append(layers[l % distinct_layers])
+            continue
         layers.append(TransformerLayerWeights(
             ones, ones,
             matrix(types["wq"], c.dim, c.dim, _seed(seed, l, 1)), matrix(types["wk"], c.dim, kv, _seed(seed, l, 2)),
