@@ -197,7 +197,8 @@ static int32_t plan_matvec(MvLaunch& L, const DeviceInfo& di) {
         p.nslots = 0;
         p.row_stride = 0;
         L.warps = W;
-        L.smem = mv_smem_layout(p.n_in, 1, false, 0, 0).total;
+        p.lay = mv_smem_layout(p.n_in, 1, false, 0, 0);
+        L.smem = p.lay.total;
         if ((long)L.smem > di.max_smem_optin - 1024) return fail(L2B_ERR_BAD_ARG, "input vector too long for shared memory");
         return L2B_OK;
     }
@@ -232,7 +233,8 @@ static int32_t plan_matvec(MvLaunch& L, const DeviceInfo& di) {
     ns -= ns % groups;  // every group owns the same number of slots
     if (ns < groups) return fail(L2B_ERR_BAD_ARG, "input dimension too large for the activation planes to fit in shared memory");
     p.nslots = (int)ns;
-    L.smem = mv_smem_layout(p.n_in, L.planes, true, p.nslots, p.row_stride).total;
+    p.lay = mv_smem_layout(p.n_in, L.planes, true, p.nslots, p.row_stride);
+    L.smem = p.lay.total;
     return L2B_OK;
 }
 
@@ -1153,7 +1155,8 @@ extern "C" int32_t l2b_dequantize(int32_t type, const void* host_blocks, int64_t
 static int32_t run_export(MvParams& p, bool kq, int planes, int8_t* q_out, float* d_out, float* sums_out, float* f_out) {
     L2B_TRY(check_kernel_attrs());
     const int warps = 8;
-    const size_t smem = mv_smem_layout(p.n_in, planes, kq, 0, 0).total;
+    p.lay = mv_smem_layout(p.n_in, planes, kq, 0, 0);
+    const size_t smem = p.lay.total;
     p.consumers = warps;
     p.turns = (p.n_in / 8 + 32 * warps - 1) / (32 * warps);
     int optin = 0, dev = 0;

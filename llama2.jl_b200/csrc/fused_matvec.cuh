@@ -71,7 +71,14 @@ struct MvSegment {
     int rowb;            // bytes of one row in a full-width stage
 };
 
+// Offsets of the regions of a block's shared memory (mv_smem_layout).
+struct MvSmem {
+    int off_bar, off_red, off_dpl, off_xs, off_act, off_xf, off_ring, total;
+    int plane_stride, slot_bytes;
+};
+
 struct MvParams {
+    MvSmem lay;      // worked out on the host: the kernel's first microsecond is too precious for it
     MvSegment seg[MV_MAX_SEG];
     int nseg;
     int n_in;        // input length
@@ -115,10 +122,6 @@ struct MvParams {
 };
 
 // ---- shared-memory carve-up (host and device agree through this helper) ------------------
-struct MvSmem {
-    int off_bar, off_red, off_dpl, off_xs, off_act, off_xf, off_ring, total;
-    int plane_stride, slot_bytes;
-};
 
 __host__ __device__ inline int mv_row_stride(int blocks_per_stage, int block_bytes) {
     int rs = blocks_per_stage * block_bytes;  // a multiple of 16
@@ -523,7 +526,7 @@ __global__ void __launch_bounds__((MV_MAX_CONSUMERS + 2) * 32, 1) fused_matvec_k
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int W = p.consumers;
     const int NS = p.nslots;
-    const MvSmem L = mv_smem_layout(p.n_in, P, KQ, KQ ? NS : 0, p.row_stride);
+    const MvSmem L = p.lay;
     MV_TRACE(0);
 
     const int nb = p.n_in / QK_K;
