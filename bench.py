@@ -85,51 +85,64 @@ def kv_bytes_per_run(cfg, n_positions, tp=1):
     return per_pos * sum(p + 1 for p in range(n_positions))
 
 
-def run_matvec(args):
-    """Isolated operator: W 14336 x 4096 as k-quant super-blocks, x f32[4096] quantised on the device, batch 1.
-    Eight copies of W (more than the L2) are rotated through, so every launch streams its weights from HBM."""
+# dram__bytes_read.sum + dram__bytes_write.sum of one fused_matvec_kernel launch on the 14336 x 4096 q4_K matrix, from the
+# ncu capture summarised in profiles/ (33 030 144 algorithmic bytes): no re-reads.
+NCU_TRAFFIC_MATVEC_Q4K_14336x4096 = 33140992
+
+
+def time_matvec(ggml_type, n_in, n_out, copies, launches, steps, warmup, planes):
+    """Average device time of one fused_matvec_kernel launch (CUDA events on the launching stream), weights rotated
+    through `copies` copies of the matrix so that every launch streams from HBM."""
     import torch
     import __graft_entry__ as g
-    pkg = g.load_package()
+    g.load_package()
     from llama2_jl_b200 import _lib as L
     from llama2_jl_b200 import synth
-    torch.cuda.set_device(0)
-    t = {"matvec-q4k": 12, "matvec-q5k": 13, "matvec-q6k": 14}[args.workload]
-    n_in, n_out, copies = args.matvec_in, args.matvec_out, args.matvec_copies
-    A = synth.matrix(t, n_in, n_out, seed=77)
+    A = synth.matrix(ggml_type, n_in, n_out, seed=77)
     x = torch.from_numpy(synth.normal_f32(n_in, 78, 1.0)).cuda()
     y = torch.zeros(n_out, dtype=torch.float32, device="cuda")
     h = C.c_void_p()
-    L.check(L.lib().l2b_matrix_create(t, L.ptr(A.data), n_in, n_out, copies, C.byref(h)))
+    L.check(L.lib().l2b_matrix_create(ggml_type, L.ptr(A.data), n_in, n_out, copies, C.byref(h)))
     stream = torch.cuda.current_stream().cuda_stream
-    planes = args.act_planes or 3
-    launches = args.matvec_launches
 
     def run(n):
         for i in range(n):
             L.check(L.lib().l2b_matrix_matvec_device(h, i % copies, x.data_ptr(), y.data_ptr(), planes, stream))
-    run(args.warmup * copies)
+    run(warmup * copies)
     torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     ms = 0.0
-    for _ in range(args.steps):
+    for _ in range(steps):
         e0.record()
         run(launches)
         e1.record()
         torch.cuda.synchronize()
         ms += e0.elapsed_time(e1)
-    us = ms * 1e3 / (args.steps * launches)
-    nbytes = (n_in // 256) * n_out * L.BLOCK_BYTES[t]
+    L.lib().l2b_matrix_destroy(h)
+    nbytes = (n_in // 256) * n_out * L.BLOCK_BYTES[ggml_type]
+    return ms, ms * 1e3 / (steps * launches), nbytes
+
+
+def run_matvec(args):
+    """Isolated operator: W 14336 x 4096 as k-quant super-blocks, x f32[4096] quantised on the device, batch 1.
+    Eight copies of W (more than the L2) are rotated through, so every launch streams its weights from HBM."""
+    import torch
+    torch.cuda.set_device(0)
+    t = {"matvec-q4k": 12, "matvec-q5k": 13, "matvec-q6k": 14}[args.workload]
+    n_in, n_out, copies = args.matvec_in, args.matvec_out, args.matvec_copies
+    planes = args.act_planes or 3
+    launches = args.matvec_launches
+    ms, us, nbytes = time_matvec(t, n_in, n_out, copies, launches, args.steps, args.warmup, planes)
     peak, kind = measured_peak()
+    traffic = NCU_TRAFFIC_MATVEC_Q4K_14336x4096 if (t, n_in, n_out) == (12, 4096, 14336) else None
     line = {"metric": "k-quant dequant-matvec, batch 1", "value": round(us, 3), "unit": "us per matvec", "n_gpus": 1, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": round(ms / args.steps, 4), "higher_is_better": False, "vs_baseline": None,
             "dtype": f"int8 activation planes x k-quant integers on int8 tensor-core MMAs, f32 accumulate; {planes} int8 activation plane(s)",
             "data": "synthetic", "config": {"workload": f"{args.workload} W {n_out}x{n_in}, {copies} rotating copies, {launches} launches per step"},
             "gpu_launches": args.steps * launches,
             "roofline": {"bound": "hbm", "achieved": round(nbytes / us / 1e3, 1), "peak": peak, "unit": "GB/s",
-                         "frac": round(nbytes / us / 1e3 / peak, 4), "traffic": None, "peak_kind": kind, "bytes_per_launch": nbytes}}
+                         "frac": round(nbytes / us / 1e3 / peak, 4), "traffic": traffic, "peak_kind": kind, "bytes_per_launch": nbytes}}
     print(json.dumps(line), flush=True)
-    L.lib().l2b_matrix_destroy(h)
 
 
 def run_ours(args):
@@ -249,6 +262,14 @@ def run_ours(args):
         "us_per_token": round(ms_per_step * 1e3 / n_pos, 2),
         "kernels_per_token": kpt,
     }
+    if not tp_mode:
+        # the dominant kernel on its own: fused_matvec_kernel on the gate/up-sized q4_K matrix (14336 x 4096), timed live
+        _, k_us, k_bytes = time_matvec(12, 4096, 14336, 8, 64, 2, 3, args.act_planes or 3)
+        line["roofline"]["dominant_kernel"] = {
+            "kernel": "fused_matvec_kernel", "workload": "q4_K 14336x4096, batch 1, 8 rotating copies (264 MB > L2), back-to-back launches",
+            "us_per_launch": round(k_us, 3), "bytes_per_launch": k_bytes, "achieved": round(k_bytes / k_us / 1e3, 1), "unit": "GB/s",
+            "frac": round(k_bytes / k_us / 1e3 / peak, 4), "traffic": NCU_TRAFFIC_MATVEC_Q4K_14336x4096,
+            "traffic_source": "dram__bytes_read.sum + dram__bytes_write.sum of one launch, ncu capture summarised under profiles/"}
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         line["cpu_baseline"] = cpu_baseline(pkg, synth, spec, args)
     if rank == 0:
