@@ -197,8 +197,7 @@ static int32_t plan_matvec(MvLaunch& L, const DeviceInfo& di) {
         p.nslots = 0;
         p.row_stride = 0;
         L.warps = W;
-        p.lay = mv_smem_layout(p.n_in, 1, false, 0, 0);
-        L.smem = p.lay.total;
+        L.smem = mv_smem_layout(p.n_in, 1, false, 0, 0).total;
         if ((long)L.smem > di.max_smem_optin - 1024) return fail(L2B_ERR_BAD_ARG, "input vector too long for shared memory");
         return L2B_OK;
     }
@@ -233,8 +232,7 @@ static int32_t plan_matvec(MvLaunch& L, const DeviceInfo& di) {
     ns -= ns % groups;  // every group owns the same number of slots
     if (ns < groups) return fail(L2B_ERR_BAD_ARG, "input dimension too large for the activation planes to fit in shared memory");
     p.nslots = (int)ns;
-    p.lay = mv_smem_layout(p.n_in, L.planes, true, p.nslots, p.row_stride);
-    L.smem = p.lay.total;
+    L.smem = mv_smem_layout(p.n_in, L.planes, true, p.nslots, p.row_stride).total;
     return L2B_OK;
 }
 
@@ -275,7 +273,7 @@ static int32_t check_kernel_attrs() {
 static cudaError_t launch_matvec(const MvLaunch& L, cudaStream_t st, bool pdl) {
     const dim3 grid(L.grid), block(L.warps * 32);
     if (!L.kq) return launch_kernel(fused_matvec_kernel<false, 1>, grid, block, L.smem, st, pdl, L.p);
-    if (L.p.tp_push || L.p.part_src)  // the variants that carry the tensor-parallel exchange
+    if (L.p.tp)  // the variants that carry the tensor-parallel exchange
         switch (L.planes) {
             case 1: return launch_kernel(fused_matvec_kernel<true, 1, true>, grid, block, L.smem, st, pdl, L.p);
             case 2: return launch_kernel(fused_matvec_kernel<true, 2, true>, grid, block, L.smem, st, pdl, L.p);
@@ -396,6 +394,8 @@ struct l2b_session {
     unsigned* tp_epoch = nullptr;  // tokens completed (device word)
     uint8_t* peer_mem[MV_MAX_TP] = {nullptr};  // [r]: rank r's tp_mem as seen from this process ([rank] = own)
     bool tp_connected = false;
+    MvTp* tp_descs = nullptr;          // device array: one descriptor per tensor-parallel launch of the token
+    std::vector<MvTp> tp_descs_host;   // filled while the token graph is captured, uploaded right after
 };
 
 static size_t kv_layer_elems(const l2b_model* m) { return (size_t)m->l_kv * m->cfg.seq_len * (m->cfg.dim / m->cfg.n_heads); }
@@ -605,6 +605,7 @@ static void session_free(l2b_session* s) {
     if (s->x2) cudaFree(s->x2);
     if (s->tp_mem) cudaFree(s->tp_mem);
     if (s->tp_epoch) cudaFree(s->tp_epoch);
+    if (s->tp_descs) cudaFree(s->tp_descs);
     if (s->h_ctl) cudaFreeHost(s->h_ctl);
     if (s->h_small) cudaFreeHost(s->h_small);
     if (s->ev0) cudaEventDestroy(s->ev0);
@@ -641,7 +642,6 @@ static int32_t enqueue_token(l2b_session* s, int* nlaunch) {
         L.p.rope_cs = s->rope_cs;
         L.p.seq_len = c.seq_len;
         L.p.status = s->status;
-        L.p.tp_size = m->tp;
     };
     // Tensor parallelism: the residual stream alternates between two buffers; `pending` is the exchange whose
     // partial vectors the next rmsnorm prologue has to add (-1: none).
@@ -651,17 +651,27 @@ static int32_t enqueue_token(l2b_session* s, int* nlaunch) {
     auto xchg_vec = [&](uint8_t* base, int e, int r) { return reinterpret_cast<float*>(base) + ((size_t)e * tp + r) * c.dim; };
     auto xchg_flag = [&](uint8_t* base, int e, int r) { return reinterpret_cast<unsigned*>(base + s->tp_flag_off) + (size_t)e * tp + r; };
     // rmsnorm prologue over the residual stream; with an exchange pending it first forms x + sum of the partial vectors
+    // descriptors live in device memory; their contents are uploaded after the capture (capture_token_graph)
+    auto new_desc = [&](MvLaunch& L) -> MvTp& {
+        MvTp d;
+        memset(&d, 0, sizeof(d));
+        d.tp_size = tp;
+        s->tp_descs_host.push_back(d);
+        L.p.tp = s->tp_descs + (s->tp_descs_host.size() - 1);
+        return s->tp_descs_host.back();
+    };
     auto norm_input = [&](MvLaunch& L, const float* gain) {
         L.p.pro = PRO_RMSNORM;
         L.p.gain = gain;
         L.p.x_in = xbuf[cur];
         if (pending >= 0) {
-            L.p.part_src = xchg_vec(s->tp_mem, pending, 0);
-            L.p.part_flag = xchg_flag(s->tp_mem, pending, 0);
-            L.p.tp_epoch = s->tp_epoch;
-            L.p.part_blocks = (unsigned)push_grid;
-            L.p.tp_timeout_ms = (unsigned)env_long("L2B_TP_TIMEOUT_MS", 10000);
-            L.p.x_out = xbuf[cur ^ 1];
+            MvTp& d = new_desc(L);
+            d.part_src = xchg_vec(s->tp_mem, pending, 0);
+            d.part_flag = xchg_flag(s->tp_mem, pending, 0);
+            d.tp_epoch = s->tp_epoch;
+            d.part_blocks = (unsigned)push_grid;
+            d.tp_timeout_ms = (unsigned)env_long("L2B_TP_TIMEOUT_MS", 10000);
+            d.x_out = xbuf[cur ^ 1];
         }
     };
     auto norm_done = [&]() {  // after the launch(es) that consumed the pending exchange
@@ -677,9 +687,10 @@ static int32_t enqueue_token(l2b_session* s, int* nlaunch) {
         }
         L.p.seg[L.p.nseg++] = make_segment(w, PAIR_ADJACENT, EPI_PUSH, nullptr, hs);
         L.p.tp_push = 1;
+        MvTp& d = new_desc(L);
         for (int r = 0; r < tp; ++r) {
-            L.p.push_dst[r] = xchg_vec(s->peer_mem[r], e, m->rank);
-            L.p.push_flag[r] = xchg_flag(s->peer_mem[r], e, m->rank);
+            d.push_dst[r] = xchg_vec(s->peer_mem[r], e, m->rank);
+            d.push_flag[r] = xchg_flag(s->peer_mem[r], e, m->rank);
         }
     };
     const int rope_mode = c.rope_is_neox ? PAIR_NEOX : PAIR_ADJACENT;
@@ -793,9 +804,17 @@ static cudaError_t cudaLaunchKernelEx_embed(const l2b_model* m, l2b_session* s, 
 
 static int32_t capture_token_graph(l2b_session* s) {
     cudaGraph_t g = nullptr;
+    const size_t max_descs = 4 * (size_t)s->model->cfg.n_layers + 2;  // <= 2 pushes + 2 summing prologues per layer, + logits
+    if (s->model->tp > 1 && !s->tp_descs) CU(cudaMalloc(&s->tp_descs, max_descs * sizeof(MvTp)));
+    s->tp_descs_host.clear();
+    s->tp_descs_host.reserve(max_descs + 8);
     CU(cudaStreamBeginCapture(s->stream, cudaStreamCaptureModeThreadLocal));
     int32_t es = enqueue_token(s, &s->kernels_per_token);
     cudaError_t ce = cudaStreamEndCapture(s->stream, &g);
+    if (es == L2B_OK && ce == cudaSuccess && !s->tp_descs_host.empty()) {
+        if (s->tp_descs_host.size() > max_descs) es = fail(L2B_ERR_STATE, "more tensor-parallel launches than descriptors");
+        else ce = cudaMemcpy(s->tp_descs, s->tp_descs_host.data(), s->tp_descs_host.size() * sizeof(MvTp), cudaMemcpyHostToDevice);
+    }
     if (es != L2B_OK) {
         if (g) cudaGraphDestroy(g);
         return es;
@@ -1155,8 +1174,7 @@ extern "C" int32_t l2b_dequantize(int32_t type, const void* host_blocks, int64_t
 static int32_t run_export(MvParams& p, bool kq, int planes, int8_t* q_out, float* d_out, float* sums_out, float* f_out) {
     L2B_TRY(check_kernel_attrs());
     const int warps = 8;
-    p.lay = mv_smem_layout(p.n_in, planes, kq, 0, 0);
-    const size_t smem = p.lay.total;
+    const size_t smem = mv_smem_layout(p.n_in, planes, kq, 0, 0).total;
     p.consumers = warps;
     p.turns = (p.n_in / 8 + 32 * warps - 1) / (32 * warps);
     int optin = 0, dev = 0;
@@ -1410,8 +1428,8 @@ extern "C" int32_t l2b_matrix_matvec(l2b_matrix* m, const float* host_x, int32_t
                 mx[i] = std::max(mx[i], v);
                 av[i] += v / m->di.sms;
             }
-        fprintf(stderr, "[l2b trace] ns since first block start (avg/max): start %.0f/%.0f barriers-ready %.0f issued %.0f/%.0f waited %.0f/%.0f act %.0f/%.0f end %.0f/%.0f | producer: entered %.0f params-ready %.0f before-expect %.0f after-expect %.0f first-copy-issued %.0f | tiles/block %llu\n",
-                av[0], mx[0], av[7], av[1], mx[1], av[2], mx[2], av[3], mx[3], av[6], mx[6], av[8], av[9], av[10], av[11], av[1], h[14]);
+        fprintf(stderr, "[l2b trace] ns since first block start (avg/max): start %.0f/%.0f barriers-ready %.0f issued %.0f/%.0f waited %.0f/%.0f act %.0f/%.0f end %.0f/%.0f | tiles/block %llu\n",
+                av[0], mx[0], av[7], av[1], mx[1], av[2], mx[2], av[3], mx[3], av[6], mx[6], h[14]);
     }
     int hst = 0;
     CU(cudaMemcpy(&hst, m->status, 4, cudaMemcpyDeviceToHost));

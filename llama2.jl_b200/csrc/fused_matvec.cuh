@@ -71,6 +71,19 @@ struct MvSegment {
     int rowb;            // bytes of one row in a full-width stage
 };
 
+// What a tensor-parallel launch needs to know about the other GPUs.
+struct MvTp {
+    int tp_size;
+    unsigned part_blocks;                 // blocks of the pushing launch (arrivals per GPU and token)
+    unsigned tp_timeout_ms;               // bound on the wait for the other GPUs
+    float* push_dst[8];                   // [r]: where this GPU's partial vector lives in GPU r's exchange buffer
+    unsigned* push_flag[8];               // [r]: this GPU's arrival counter in GPU r's memory
+    const float* part_src;                // prologue: partial vectors [tp_size][n_in] in this GPU's exchange buffer, or null
+    const unsigned* part_flag;            // prologue: arrival counters [tp_size] in this GPU's memory
+    const unsigned* tp_epoch;             // tokens completed so far (device word, advanced once per token)
+    float* x_out;                         // prologue: block 0 writes x_new here (the residual stream is double-buffered)
+};
+
 // Offsets of the regions of a block's shared memory (mv_smem_layout).
 struct MvSmem {
     int off_bar, off_red, off_dpl, off_xs, off_act, off_xf, off_ring, total;
@@ -78,7 +91,6 @@ struct MvSmem {
 };
 
 struct MvParams {
-    MvSmem lay;      // worked out on the host: the kernel's first microsecond is too precious for it
     MvSegment seg[MV_MAX_SEG];
     int nseg;
     int n_in;        // input length
@@ -105,17 +117,10 @@ struct MvParams {
     int seq_len;
     float* amax_val;        // EPI_LOGITS: per-block best value   [gridDim.x]
     int* amax_idx;          // EPI_LOGITS: per-block best index   [gridDim.x]
-    // tensor parallelism (tp_size <= 1: unused)
-    int tp_size;
-    int tp_push;                          // this launch ends in EPI_PUSH
-    float* push_dst[MV_MAX_TP];           // [r]: where this GPU's partial vector lives in GPU r's exchange buffer
-    unsigned* push_flag[MV_MAX_TP];       // [r]: this GPU's arrival counter in GPU r's memory
-    const float* part_src;                // prologue: partial vectors [tp_size][n_in] in this GPU's exchange buffer, or null
-    const unsigned* part_flag;            // prologue: arrival counters [tp_size] in this GPU's memory
-    const unsigned* tp_epoch;             // tokens completed so far (device word, advanced once per token)
-    unsigned part_blocks;                 // blocks of the pushing launch (arrivals per GPU and token)
-    unsigned tp_timeout_ms;               // bound on the wait for the other GPUs
-    float* x_out;                         // prologue: block 0 writes x_new here (the residual stream is double-buffered)
+    // tensor parallelism: descriptor in device memory (null on one GPU).  Kept out of the parameter block on purpose:
+    // every byte of kernel parameters is paid for at each of the ~160 launches of a token.
+    const MvTp* tp;
+    int tp_push;            // this launch ends in EPI_PUSH
     int* status;            // device status word
     int debug;              // measurement aid: bit 0 = consumers skip the arithmetic, bit 1 = the producer skips the copies (results are wrong)
     unsigned long long* trace;  // optional timeline: 16 globaltimer stamps per block (debugging aid), or null
@@ -241,16 +246,20 @@ __device__ __forceinline__ void build_activation(const MvParams& p, uint8_t* sme
     const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
 
     auto group_of = [&](int turn) { return 32 * (warp + nwarps * turn) + lane; };
-    const bool tp_sum = TP && p.part_src != nullptr;  // TP = false compiles the exchange out of single-GPU kernels
+    const MvTp* T = TP ? p.tp : nullptr;  // TP = false compiles the exchange out of single-GPU kernels
+    const bool tp_sum = TP && T && T->part_src != nullptr;
+    const int tp_n = tp_sum ? T->tp_size : 0;
+    const float* part_src = tp_sum ? T->part_src : nullptr;
+    float* x_out = tp_sum ? T->x_out : nullptr;
     if (tp_sum) {
         // one lane per GPU waits until that GPU's partial vector of this token has arrived in full
-        if (warp == 0 && lane < p.tp_size && __ldcg(p.status) == DEV_OK) {
-            const unsigned want = (__ldcg(p.tp_epoch) + 1u) * p.part_blocks;
-            const unsigned long long t0 = global_ns(), limit = (unsigned long long)p.tp_timeout_ms * 1000000ull;
+        if (warp == 0 && lane < tp_n && __ldcg(p.status) == DEV_OK) {
+            const unsigned want = (__ldcg(T->tp_epoch) + 1u) * T->part_blocks;
+            const unsigned long long t0 = global_ns(), limit = (unsigned long long)T->tp_timeout_ms * 1000000ull;
             bool ok = false;
             for (;;) {
                 unsigned have;
-                asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(have) : "l"(p.part_flag + lane) : "memory");
+                asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(have) : "l"(T->part_flag + lane) : "memory");
                 if ((int)(have - want) >= 0) {
                     ok = true;
                     break;
@@ -271,16 +280,16 @@ __device__ __forceinline__ void build_activation(const MvParams& p, uint8_t* sme
             b = __ldcg(reinterpret_cast<const float4*>(p.x_in + 8 * g + 4));
             if (tp_sum) {
 #pragma unroll 1
-                for (int r = 0; r < p.tp_size; ++r) {  // rank order on every GPU: identical sums everywhere
-                    const float* src = p.part_src + (size_t)r * n + 8 * g;
+                for (int r = 0; r < tp_n; ++r) {  // rank order on every GPU: identical sums everywhere
+                    const float* src = part_src + (size_t)r * n + 8 * g;
                     const float4 pa = __ldcg(reinterpret_cast<const float4*>(src));
                     const float4 pb = __ldcg(reinterpret_cast<const float4*>(src + 4));
                     a.x += pa.x; a.y += pa.y; a.z += pa.z; a.w += pa.w;
                     b.x += pb.x; b.y += pb.y; b.z += pb.z; b.w += pb.w;
                 }
                 if (write_back && blockIdx.x == 0) {
-                    *reinterpret_cast<float4*>(p.x_out + 8 * g) = a;
-                    *reinterpret_cast<float4*>(p.x_out + 8 * g + 4) = b;
+                    *reinterpret_cast<float4*>(x_out + 8 * g) = a;
+                    *reinterpret_cast<float4*>(x_out + 8 * g + 4) = b;
                 }
             }
         }
@@ -508,12 +517,13 @@ __device__ __forceinline__ void epilogue_pair(const MvParams& p, const MvSegment
             break;
         case EPI_PUSH:
             if (TP) {
-#pragma unroll
-                for (int r = 0; r < MV_MAX_TP; ++r)
-                    if (r < p.tp_size) {
-                        p.push_dst[r][rowA] = vA;
-                        p.push_dst[r][rowB] = vB;
-                    }
+                const MvTp* T = p.tp;
+                const int g = T->tp_size;
+                for (int r = 0; r < g; ++r) {
+                    float* dst = T->push_dst[r];
+                    dst[rowA] = vA;
+                    dst[rowB] = vB;
+                }
             }
             break;
     }
@@ -526,7 +536,7 @@ __global__ void __launch_bounds__((MV_MAX_CONSUMERS + 2) * 32, 1) fused_matvec_k
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int W = p.consumers;
     const int NS = p.nslots;
-    const MvSmem L = p.lay;
+    const MvSmem L = mv_smem_layout(p.n_in, P, KQ, KQ ? NS : 0, p.row_stride);
     MV_TRACE(0);
 
     const int nb = p.n_in / QK_K;
@@ -540,27 +550,19 @@ __global__ void __launch_bounds__((MV_MAX_CONSUMERS + 2) * 32, 1) fused_matvec_k
     uint8_t* ring = smem + L.off_ring;
 
     if (KQ) {
-        // The producer warp initialises the barriers it touches itself (full, empty) and only ARRIVES at the
-        // block-wide barrier, so its first copies do not wait for the other warps; everyone else initialises
-        // the reduction barriers and waits.
-        const int nthreads = (W + 2) * 32;
-        if (warp == W) {
-            if (lane < NS) {
-                mbar_init(full + lane, 1);
-                mbar_init(empty + lane, W / p.cgroups);
-                fence_barrier_init();
-                fence_proxy_async();
-            }
-            __syncwarp();
-            asm volatile("bar.arrive 2, %0;" ::"r"(nthreads) : "memory");
-        } else {
-            if (threadIdx.x < MV_RED_BUFS) {
-                mbar_init(red_full + threadIdx.x, W / p.cgroups);
-                mbar_init(red_empty + threadIdx.x, 1);
-                fence_barrier_init();
-            }
-            asm volatile("bar.sync 2, %0;" ::"r"(nthreads) : "memory");
+        if (threadIdx.x < NS) {
+            mbar_init(full + threadIdx.x, 1);
+            mbar_init(empty + threadIdx.x, W / p.cgroups);
         }
+        if (threadIdx.x >= 32 && threadIdx.x < 32 + MV_RED_BUFS) {
+            mbar_init(red_full + (threadIdx.x - 32), W / p.cgroups);
+            mbar_init(red_empty + (threadIdx.x - 32), 1);
+        }
+        if (threadIdx.x < 32 + MV_RED_BUFS) {
+            fence_barrier_init();
+            fence_proxy_async();
+        }
+        __syncthreads();
     }
     MV_TRACE(7);
 
@@ -571,7 +573,6 @@ __global__ void __launch_bounds__((MV_MAX_CONSUMERS + 2) * 32, 1) fused_matvec_k
     if (KQ && warp == W) {
         pdl_launch_dependents();
         if (lane >= 16) return;
-        if (p.trace && lane == 0) p.trace[blockIdx.x * 16 + 8] = global_ns();
         const uint64_t policy = policy_evict_first();
         const int c = lane;
         struct TileSrc {
@@ -617,76 +618,55 @@ __global__ void __launch_bounds__((MV_MAX_CONSUMERS + 2) * 32, 1) fused_matvec_k
         // hundreds of cycles here.  Group g owns slots g*NSG .. g*NSG+NSG-1 and takes tiles g, g+cgroups, ...
         const int CG = p.cgroups, NSG = NS / CG;
         int slot_g[2] = {0, NSG}, ph_g[2] = {0, 0};
-        TileSrc tsA = tile_src(0);                                 // the tile group 0 works on next
-        TileSrc tsB = tile_src(my_units);                          // the tile group 1 works on next: worked out after A's first copies are out
-        bool needB = (CG == 2);
-        if (p.trace && lane == 0) p.trace[blockIdx.x * 16 + 9] = global_ns();
+        TileSrc ts = tile_src(0);
         // Fast path for the common case (one segment, adjacent or dual rows, full tiles): the next tile's source
         // is the current one plus a constant.
         const bool linear = (p.nseg == 1) && (p.seg[0].pair_mode != PAIR_NEOX);
         const size_t tile_step = linear ? (size_t)gridDim.x * (p.seg[0].pair_mode == PAIR_ADJACENT ? 16 : 8) * nb * dev_block_bytes(p.seg[0].type) : 0;
         const int full_tiles = linear ? p.seg[0].npairs / MV_TILE_PAIRS : 0;  // tiles below this index are complete
-        // One stage of one tile into the next slot of group `grp` (a literal at every call, so the counters stay in
-        // registers).  Returns false when the wait for a free slot ran out.
-        auto issue = [&](const TileSrc& ts, const int grp, int it) -> bool {
-            int slot_i = slot_g[grp], ph = ph_g[grp];
-            // wait until every consumer warp of the group has released what this slot held before
-            if (ph > 0) {
-                int ok = 1;
-                if (c == 0) ok = mbar_wait_bounded(empty + slot_i, (uint32_t)((ph & 1) ^ 1)) ? 1 : 0;
-                ok = __shfl_sync(0x0000ffffu, ok, 0);
-                if (!ok) return false;
-            }
-            uint32_t bytes = ts.bytes0, tx = ts.tx0;
-            if (nit > 1) {  // a stage is a 16-block slice of every row (one row per copy)
-                const int nblk = min(MV_TILE_BLOCKS, nb - it * MV_TILE_BLOCKS);
-                bytes = ts.nrows ? (uint32_t)(nblk * ts.bb) : 0u;
-                tx = (uint32_t)(ts.nvalid * nblk * ts.bb);
-            }
-            if (p.debug & 2) bytes = tx = 0;
-            if (first && p.trace && lane == 0) p.trace[blockIdx.x * 16 + 10] = global_ns();
-            if (c == 0) mbar_arrive_expect_tx(full + slot_i, tx);
-            __syncwarp(0x0000ffffu);
-            if (first && p.trace && lane == 0) p.trace[blockIdx.x * 16 + 11] = global_ns();
-            if (bytes)
-                bulk_g2s(ring + (size_t)slot_i * L.slot_bytes + (size_t)c * ts.gs, ts.src + (size_t)it * (MV_TILE_BLOCKS * ts.bb), bytes, full + slot_i, policy);
-            if (first && p.trace && lane == 0) p.trace[blockIdx.x * 16 + 1] = global_ns();
-            first = false;
-            if (++slot_i == (grp + 1) * NSG) {
-                slot_i = grp * NSG;
-                ++ph;
-            }
-            slot_g[grp] = slot_i;
-            ph_g[grp] = ph;
-            return true;
-        };
-        // The stages of the two groups' tiles are issued alternately (A0 B0 A1 B1 ...): a tile of several stages
-        // would otherwise hold the producer at its own group's slots while the other group's slots sit empty.
-        for (int j = 0; j < my_units && !dead; j += CG) {
-            const bool hasB = (CG == 2) && (j + 1 < my_units);
+        for (int j = 0; j < my_units && !dead; ++j) {
+            const int grp = (CG == 2) ? (j & 1) : 0;
+            int slot_i = grp ? slot_g[1] : slot_g[0], ph = grp ? ph_g[1] : ph_g[0];
             for (int it = 0; it < nit; ++it) {
-                bool ok = issue(tsA, 0, it);
-                if (ok && hasB) {
-                    if (needB) {
-                        tsB = tile_src(j + 1);
-                        needB = false;
+                // wait until every consumer warp of the group has released what this slot held before
+                if (ph > 0) {
+                    int ok = 1;
+                    if (c == 0) ok = mbar_wait_bounded(empty + slot_i, (uint32_t)((ph & 1) ^ 1)) ? 1 : 0;
+                    ok = __shfl_sync(0x0000ffffu, ok, 0);
+                    if (!ok) {
+                        dead = true;
+                        break;
                     }
-                    ok = issue(tsB, 1, it);
                 }
-                if (!ok) {
-                    dead = true;
-                    break;
+                uint32_t bytes = ts.bytes0, tx = ts.tx0;
+                if (nit > 1) {  // a stage is a 16-block slice of every row (one row per copy)
+                    const int nblk = min(MV_TILE_BLOCKS, nb - it * MV_TILE_BLOCKS);
+                    bytes = ts.nrows ? (uint32_t)(nblk * ts.bb) : 0u;
+                    tx = (uint32_t)(ts.nvalid * nblk * ts.bb);
+                }
+                if (p.debug & 2) bytes = tx = 0;
+                if (c == 0) mbar_arrive_expect_tx(full + slot_i, tx);
+                __syncwarp(0x0000ffffu);
+                if (bytes)
+                    bulk_g2s(ring + (size_t)slot_i * L.slot_bytes + (size_t)c * ts.gs, ts.src + (size_t)it * (MV_TILE_BLOCKS * ts.bb), bytes, full + slot_i, policy);
+                if (first && p.trace && lane == 0) p.trace[blockIdx.x * 16 + 1] = global_ns();
+                first = false;
+                if (++slot_i == (grp + 1) * NSG) {
+                    slot_i = grp * NSG;
+                    ++ph;
                 }
             }
-            // parameters of the next tiles (in the shadow of the wait for their slots)
-            const int next_last = (int)blockIdx.x + (j + 2 * CG - 1) * (int)gridDim.x;  // the later of the next tiles
-            if (linear && next_last < full_tiles) {
-                tsA.src += (size_t)CG * tile_step;
-                tsB.src += (size_t)CG * tile_step;
+            if (grp) {
+                slot_g[1] = slot_i;
+                ph_g[1] = ph;
             } else {
-                tsA = tile_src(j + CG);
-                tsB = tile_src(CG == 2 ? j + CG + 1 : my_units);
+                slot_g[0] = slot_i;
+                ph_g[0] = ph;
             }
+            // parameters of the next tile (in the shadow of the wait for its slot)
+            const int next_tile = (int)blockIdx.x + (j + 1) * (int)gridDim.x;
+            if (linear && next_tile < full_tiles) ts.src += tile_step;
+            else ts = tile_src(j + 1);
         }
         if (dead) {
             // a consumer gave up: let copies still in flight land (bounded) before shared memory is released
@@ -743,11 +723,7 @@ __global__ void __launch_bounds__((MV_MAX_CONSUMERS + 2) * 32, 1) fused_matvec_k
         if (TP && p.tp_push) {  // every row of this block is on its way: tell each GPU (blocks without rows report too)
             __threadfence_system();
             __syncwarp();
-            unsigned* flag = nullptr;
-#pragma unroll
-            for (int r = 0; r < MV_MAX_TP; ++r)
-                if (lane == r && r < p.tp_size) flag = p.push_flag[r];
-            if (flag) atomicAdd_system(flag, 1u);
+            if (lane < p.tp->tp_size) atomicAdd_system(p.tp->push_flag[lane], 1u);
         }
         if (p.amax_val) {  // EPI_LOGITS: first maximal index over this block's rows
             for (int o = 16; o > 0; o >>= 1) {

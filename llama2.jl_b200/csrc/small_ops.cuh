@@ -61,7 +61,7 @@ __global__ void __launch_bounds__(256) export_activation_kernel(const __grid_con
                                                                  float* f_out) {
     extern __shared__ __align__(128) uint8_t smem[];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
-    const MvSmem L = p.lay;
+    const MvSmem L = mv_smem_layout(p.n_in, P, KQ, 0, 0);
     build_activation<KQ, P>(p, smem, L, warp, lane, nwarps);
     const int n = p.n_in, nb = n / QK_K;
     if (KQ) {
