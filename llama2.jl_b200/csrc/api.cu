@@ -254,6 +254,10 @@ static void set_kernel_attrs() {
         set((const void*)fused_matvec_kernel<true, 2>);
         set((const void*)fused_matvec_kernel<true, 3>);
         set((const void*)fused_matvec_kernel<false, 1>);
+        set((const void*)fused_matvec_kernel<true, 1, false, true>);
+        set((const void*)fused_matvec_kernel<true, 2, false, true>);
+        set((const void*)fused_matvec_kernel<true, 3, false, true>);
+        set((const void*)fused_matvec_kernel<false, 1, false, true>);
         set((const void*)fused_matvec_kernel<true, 1, true>);
         set((const void*)fused_matvec_kernel<true, 2, true>);
         set((const void*)fused_matvec_kernel<true, 3, true>);
@@ -272,6 +276,15 @@ static int32_t check_kernel_attrs() {
 
 static cudaError_t launch_matvec(const MvLaunch& L, cudaStream_t st, bool pdl) {
     const dim3 grid(L.grid), block(L.warps * 32);
+    if (L.p.debug || L.p.trace) {  // measurement aids: the instantiations that carry them
+        if (L.p.tp) return cudaErrorNotSupported;
+        if (!L.kq) return launch_kernel(fused_matvec_kernel<false, 1, false, true>, grid, block, L.smem, st, pdl, L.p);
+        switch (L.planes) {
+            case 1: return launch_kernel(fused_matvec_kernel<true, 1, false, true>, grid, block, L.smem, st, pdl, L.p);
+            case 2: return launch_kernel(fused_matvec_kernel<true, 2, false, true>, grid, block, L.smem, st, pdl, L.p);
+            default: return launch_kernel(fused_matvec_kernel<true, 3, false, true>, grid, block, L.smem, st, pdl, L.p);
+        }
+    }
     if (!L.kq) return launch_kernel(fused_matvec_kernel<false, 1>, grid, block, L.smem, st, pdl, L.p);
     if (L.p.tp)  // the variants that carry the tensor-parallel exchange
         switch (L.planes) {

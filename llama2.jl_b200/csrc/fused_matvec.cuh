@@ -172,7 +172,7 @@ __device__ __forceinline__ unsigned long long global_ns() {
 }
 #define MV_TRACE(i)                                                                      \
     do {                                                                                 \
-        if (p.trace && threadIdx.x == 0) p.trace[blockIdx.x * 16 + (i)] = global_ns();  \
+        if (DBG && p.trace && threadIdx.x == 0) p.trace[blockIdx.x * 16 + (i)] = global_ns();  \
     } while (0)
 
 // Barrier over the first `nthreads` threads of the block (the consumer warps); the producer warp never joins it.
@@ -530,7 +530,9 @@ __device__ __forceinline__ void epilogue_pair(const MvParams& p, const MvSegment
 }
 
 // ---- the kernel --------------------------------------------------------------------------------
-template <bool KQ, int P, bool TP = false>
+// DBG = true compiles in the measurement aids (timeline stamps, skip-arithmetic / skip-copies switches); the production
+// instantiations carry none of them: even a predicated-off stamp in the producer's loop cost 2 % of a token.
+template <bool KQ, int P, bool TP = false, bool DBG = false>
 __global__ void __launch_bounds__((MV_MAX_CONSUMERS + 2) * 32, 1) fused_matvec_kernel(const __grid_constant__ MvParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -644,12 +646,12 @@ __global__ void __launch_bounds__((MV_MAX_CONSUMERS + 2) * 32, 1) fused_matvec_k
                     bytes = ts.nrows ? (uint32_t)(nblk * ts.bb) : 0u;
                     tx = (uint32_t)(ts.nvalid * nblk * ts.bb);
                 }
-                if (p.debug & 2) bytes = tx = 0;
+                if (DBG && (p.debug & 2)) bytes = tx = 0;
                 if (c == 0) mbar_arrive_expect_tx(full + slot_i, tx);
                 __syncwarp(0x0000ffffu);
                 if (bytes)
                     bulk_g2s(ring + (size_t)slot_i * L.slot_bytes + (size_t)c * ts.gs, ts.src + (size_t)it * (MV_TILE_BLOCKS * ts.bb), bytes, full + slot_i, policy);
-                if (first && p.trace && lane == 0) p.trace[blockIdx.x * 16 + 1] = global_ns();
+                if (DBG && first && p.trace && lane == 0) p.trace[blockIdx.x * 16 + 1] = global_ns();
                 first = false;
                 if (++slot_i == (grp + 1) * NSG) {
                     slot_i = grp * NSG;
@@ -808,7 +810,7 @@ __global__ void __launch_bounds__((MV_MAX_CONSUMERS + 2) * 32, 1) fused_matvec_k
                     dB = __half2float(__ldg(d6B + b0 + wl));
                 }
                 if (!dead && !mbar_wait_bounded(full + slot_i, full_par)) dead = true;  // uniform across the warp
-                if (!dead && !(p.debug & 1)) {
+                if (!dead && !(DBG && (p.debug & 1))) {
                     const uint8_t* slot = ring + (size_t)slot_i * L.slot_bytes;
                     for (int bl = wl; bl < nblk; bl += WG) {
                         const uint8_t* rA = slot + offA + bl * bb;
@@ -878,7 +880,7 @@ __global__ void __launch_bounds__((MV_MAX_CONSUMERS + 2) * 32, 1) fused_matvec_k
         }
     }
     MV_TRACE(6);
-    if (p.trace && threadIdx.x == 0) p.trace[blockIdx.x * 16 + 14] = (unsigned long long)my_units;
+    if (DBG && p.trace && threadIdx.x == 0) p.trace[blockIdx.x * 16 + 14] = (unsigned long long)my_units;
 
     if (!KQ && p.amax_val) {  // EPI_LOGITS (f32 weights): first maximal index over this block's rows
         for (int o = 16; o > 0; o >>= 1) {
