@@ -108,6 +108,18 @@ int32_t l2b_model_weight_bytes(const l2b_model* model, int64_t* bytes_per_token)
  * `stream` is a cudaStream_t passed as a pointer (NULL = the library creates its own). */
 int32_t l2b_session_create(l2b_model* model, void* stream, l2b_session** session);
 int32_t l2b_session_reset(l2b_session* session); /* zero the KV cache, as a fresh RunState */
+/* ---- GGUF files --------------------------------------------------------------------- */
+/* The file walk of load_gguf_model (src/load_gguf.jl:317-336: header, metadata, tensor directory, alignment) and the model
+ * construction of build_llama / build_phi3 (:211-315) inside the library: the file is memory-mapped and every tensor is
+ * uploaded straight from the map.  Every metadata value type of the format is read (the reference reads six, :59-77); a
+ * missing output.weight means a classifier tied to the embedding.  The tokenizer metadata stays with the host.
+ *   seq_len > 0: as given; 0: the file's <arch>.context_length; < 0: the 512 the reference hard-codes (:237, :299). */
+int32_t l2b_model_load_gguf(const char* path, int32_t seq_len, int32_t act_planes, int32_t device, int32_t tp_size, int32_t tp_rank,
+                            l2b_config* config_out, l2b_model** model);
+/* The same parse without a device: ModelConfig fields (seq_len = context_length), architecture (0 llama, 1 phi3),
+ * number of tensors, context length.  Fails with L2B_ERR_BAD_ARG ("Not a GGUF file", :89) on anything else. */
+int32_t l2b_gguf_inspect(const char* path, l2b_config* config_out, int32_t* arch_out, int64_t* n_tensors, int64_t* context_length);
+
 /* ---- tensor parallelism (no counterpart in the reference, which runs on one CPU) ------
  * One process per GPU; every rank creates its model with the same l2b_config except tp_rank, uploads the FULL tensors
  * (the library keeps its shard: whole kv groups of wq/wk/wv, hidden units of w1/w3, super-block columns of wo/w2; needs

@@ -3,9 +3,9 @@ import os
 import subprocess
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-SOURCES = ["csrc/api.cu", "csrc/synth.cpp"]
+SOURCES = ["csrc/api.cu", "csrc/synth.cpp", "csrc/gguf_reader.cpp"]
 HEADERS = ["csrc/common.cuh", "csrc/kquants.cuh", "csrc/fused_matvec.cuh", "csrc/attention.cuh", "csrc/sampling.cuh",
-           "csrc/small_ops.cuh", "../include/llama2_b200.h"]
+           "csrc/small_ops.cuh", "csrc/gguf_reader.h", "../include/llama2_b200.h"]
 OUTPUT = os.path.join(_HERE, "libllama2_b200.so")
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC", "-shared"]
 

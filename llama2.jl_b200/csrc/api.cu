@@ -10,6 +10,7 @@
 #include <string>
 #include <vector>
 
+#include "gguf_reader.h"
 #include "attention.cuh"
 #include "fused_matvec.cuh"
 #include "sampling.cuh"
@@ -598,6 +599,141 @@ extern "C" int32_t l2b_model_weight_bytes(const l2b_model* m, int64_t* bytes) {
         b += w.wq.file_bytes + w.wk.file_bytes + w.wv.file_bytes + w.wo.file_bytes + w.w1.file_bytes + w.w2.file_bytes + w.w3.file_bytes +
              2 * (int64_t)m->cfg.dim * 4;
     *bytes = b;
+    return L2B_OK;
+}
+
+// ---------------------------------------------------------------------------------------------
+// GGUF files: load_gguf_model's weight path (src/load_gguf.jl:211-336) inside the library
+// ---------------------------------------------------------------------------------------------
+namespace {
+
+struct GgufModelInfo {
+    l2b_config cfg;
+    int arch = 0;  // 0 llama, 1 phi3
+    int64_t context_length = 0;
+};
+
+int32_t gguf_describe(const GgufFile& f, GgufModelInfo& info) {
+    memset(&info.cfg, 0, sizeof(info.cfg));
+    const GgufValue* a = f.find("general.architecture");
+    if (!a || a->type != 8) return fail(L2B_ERR_BAD_ARG, "general.architecture is missing");
+    const std::string arch = a->str;
+    if (arch == "llama") info.arch = 0;
+    else if (arch == "phi3") info.arch = 1;
+    else return fail(L2B_ERR_BAD_ARG, "unsupported model architecture: " + arch);  // src/load_gguf.jl:385-386
+    auto num = [&](const char* key, double dflt, bool required, double& out) -> int32_t {
+        const GgufValue* v = f.find(arch + "." + key);
+        if (!v || v->type == 8 || v->type == 9) {
+            if (required) return fail(L2B_ERR_BAD_ARG, "metadata key " + arch + "." + key + " is missing");
+            out = dflt;
+            return L2B_OK;
+        }
+        out = v->num;
+        return L2B_OK;
+    };
+    double dim, hidden, layers, heads, kv_heads, base, ctx;
+    L2B_TRY(num("embedding_length", 0, true, dim));
+    L2B_TRY(num("feed_forward_length", 0, true, hidden));
+    L2B_TRY(num("block_count", 0, true, layers));
+    L2B_TRY(num("attention.head_count", 0, true, heads));
+    L2B_TRY(num("attention.head_count_kv", heads, false, kv_heads));
+    L2B_TRY(num("rope.freq_base", 10000.0, false, base));  // src/load_gguf.jl:238, 300
+    L2B_TRY(num("context_length", 0, false, ctx));
+    l2b_config& c = info.cfg;
+    c.dim = (int32_t)dim; c.hidden_dim = (int32_t)hidden; c.n_layers = (int32_t)layers;
+    c.n_heads = (int32_t)heads; c.n_kv_heads = (int32_t)kv_heads;
+    c.rope_freq_base = (float)base;
+    c.rope_is_neox = info.arch == 1;  // src/load_gguf.jl:239, 301
+    info.context_length = (int64_t)ctx;
+    // vocabulary = number of tokenizer tokens (src/load_gguf.jl:382), else the rows of the embedding table
+    const GgufValue* toks = f.find("tokenizer.ggml.tokens");
+    if (toks && toks->type == 9) c.vocab_size = (int32_t)toks->count;
+    else if (const GgufTensor* e = f.tensor("token_embd.weight")) c.vocab_size = (int32_t)e->rows();
+    else return fail(L2B_ERR_BAD_ARG, "neither tokenizer.ggml.tokens nor token_embd.weight is present");
+    return L2B_OK;
+}
+
+}  // namespace
+
+extern "C" int32_t l2b_gguf_inspect(const char* path, l2b_config* config_out, int32_t* arch_out, int64_t* n_tensors, int64_t* context_length) {
+    if (!path || !config_out) return fail(L2B_ERR_BAD_ARG, "null argument");
+    GgufFile f;
+    if (!f.open(path)) return fail(L2B_ERR_BAD_ARG, f.error());
+    GgufModelInfo info;
+    L2B_TRY(gguf_describe(f, info));
+    info.cfg.seq_len = (int32_t)std::min<int64_t>(info.context_length, 0x7fffffff);
+    *config_out = info.cfg;
+    if (arch_out) *arch_out = info.arch;
+    if (n_tensors) *n_tensors = (int64_t)f.tensors().size();
+    if (context_length) *context_length = info.context_length;
+    return L2B_OK;
+}
+
+extern "C" int32_t l2b_model_load_gguf(const char* path, int32_t seq_len, int32_t act_planes, int32_t device, int32_t tp_size, int32_t tp_rank,
+                                       l2b_config* config_out, l2b_model** out) {
+    if (!path || !out) return fail(L2B_ERR_BAD_ARG, "null argument");
+    *out = nullptr;
+    GgufFile f;
+    if (!f.open(path)) return fail(L2B_ERR_BAD_ARG, f.error());
+    GgufModelInfo info;
+    L2B_TRY(gguf_describe(f, info));
+    l2b_config c = info.cfg;
+    // seq_len > 0: as given; 0: the file's context_length; < 0: the 512 the reference hard-codes (src/load_gguf.jl:237, 299)
+    c.seq_len = seq_len > 0 ? seq_len : (seq_len == 0 ? (int32_t)info.context_length : 512);
+    c.act_planes = act_planes;
+    c.device = device;
+    c.tp_size = tp_size;
+    c.tp_rank = tp_rank;
+    l2b_model* m = nullptr;
+    L2B_TRY(l2b_model_create(&c, &m));
+    const int64_t hs = c.dim / c.n_heads, kv_dim = hs * c.n_kv_heads;
+    auto fail_free = [&](int32_t st) {
+        l2b_model_destroy(m);
+        return st;
+    };
+    // one tensor (or a row range of it) -> one role.  Rows are contiguous, so a range is an offset pointer.
+    auto up = [&](const std::string& name, int32_t role, int32_t layer, int64_t in, int64_t row0, int64_t rows, bool vector) -> int32_t {
+        const GgufTensor* t = f.tensor(name);
+        if (!t) return fail(L2B_ERR_STATE, "tensor " + name + " is missing");
+        if (!t->data) return fail(L2B_ERR_UNSUPPORTED_TYPE, "tensor type " + std::to_string(t->type) + " not implemented (" + name + ")");  // :153
+        const int64_t t_in = (int64_t)t->dims[0], t_rows = (int64_t)t->rows();
+        if (vector) {
+            if (t->type != T_F32 || t_in * t_rows != in) return fail(L2B_ERR_BAD_ARG, "norm tensor " + name + " must be f32 of length dim");
+            return l2b_model_upload_tensor(m, role, layer, T_F32, t->data, in, 1);
+        }
+        if (t_in != in || row0 + rows > t_rows) return fail(L2B_ERR_BAD_ARG, "tensor " + name + " has an unexpected shape");
+        const int64_t row_bytes = t->type == T_F32 ? in * 4 : in / QK_K * file_block_bytes((int)t->type);
+        return l2b_model_upload_tensor(m, role, layer, (int32_t)t->type, t->data + row0 * row_bytes, in, rows);
+    };
+    int32_t st = up("token_embd.weight", L2B_ROLE_TOKEN_EMBEDDING, 0, c.dim, 0, c.vocab_size, false);
+    // models that tie the classifier to the embedding ship no output.weight
+    if (st == L2B_OK) st = up(f.tensor("output.weight") ? "output.weight" : "token_embd.weight", L2B_ROLE_OUTPUT, 0, c.dim, 0, c.vocab_size, false);
+    if (st == L2B_OK) st = up("output_norm.weight", L2B_ROLE_RMS_FINAL, 0, c.dim, 0, 1, true);
+    for (int l = 0; l < c.n_layers && st == L2B_OK; ++l) {
+        const std::string b = "blk." + std::to_string(l) + ".";
+        st = up(b + "attn_norm.weight", L2B_ROLE_RMS_ATT, l, c.dim, 0, 1, true);
+        if (st == L2B_OK) st = up(b + "ffn_norm.weight", L2B_ROLE_RMS_FFN, l, c.dim, 0, 1, true);
+        if (st != L2B_OK) break;
+        if (info.arch == 0) {  // src/load_gguf.jl:211-253
+            st = up(b + "attn_q.weight", L2B_ROLE_WQ, l, c.dim, 0, c.dim, false);
+            if (st == L2B_OK) st = up(b + "attn_k.weight", L2B_ROLE_WK, l, c.dim, 0, kv_dim, false);
+            if (st == L2B_OK) st = up(b + "attn_v.weight", L2B_ROLE_WV, l, c.dim, 0, kv_dim, false);
+            if (st == L2B_OK) st = up(b + "ffn_gate.weight", L2B_ROLE_W1, l, c.dim, 0, c.hidden_dim, false);
+            if (st == L2B_OK) st = up(b + "ffn_up.weight", L2B_ROLE_W3, l, c.dim, 0, c.hidden_dim, false);
+        } else {  // phi3 (src/load_gguf.jl:255-315): q, k, v are row ranges of attn_qkv; gate and up are the halves of ffn_up
+            st = up(b + "attn_qkv.weight", L2B_ROLE_WQ, l, c.dim, 0, c.dim, false);
+            if (st == L2B_OK) st = up(b + "attn_qkv.weight", L2B_ROLE_WK, l, c.dim, c.dim, kv_dim, false);
+            if (st == L2B_OK) st = up(b + "attn_qkv.weight", L2B_ROLE_WV, l, c.dim, c.dim + kv_dim, kv_dim, false);
+            if (st == L2B_OK) st = up(b + "ffn_up.weight", L2B_ROLE_W1, l, c.dim, 0, c.hidden_dim, false);
+            if (st == L2B_OK) st = up(b + "ffn_up.weight", L2B_ROLE_W3, l, c.dim, c.hidden_dim, c.hidden_dim, false);
+        }
+        if (st == L2B_OK) st = up(b + "attn_output.weight", L2B_ROLE_WO, l, c.dim, 0, c.dim, false);
+        if (st == L2B_OK) st = up(b + "ffn_down.weight", L2B_ROLE_W2, l, c.hidden_dim, 0, c.dim, false);
+    }
+    if (st == L2B_OK) st = l2b_model_finalize(m);
+    if (st != L2B_OK) return fail_free(st);
+    if (config_out) *config_out = c;
+    *out = m;
     return L2B_OK;
 }
 

@@ -152,18 +152,19 @@ def build_phi3(kv, t, vocab_size, seq_len):
     return c, TransformerWeights(t["token_embd.weight"], layers, t["output_norm.weight"], t["output.weight"])
 
 
-def load_gguf_model(filename: str, mmap: bool = True, seq_len: int = 512, **kw) -> LanguageModel:
+def load_gguf_model(filename: str, mmap: bool = True, seq_len: int = 512, native: bool = False, **kw) -> LanguageModel:
     """load_gguf_model(filename; mmap=true) (src/load_gguf.jl:317-394).
 
     seq_len defaults to the 512 the reference hard-codes (:237, :299); pass 0 to take `<arch>.context_length`
-    from the file instead."""
+    from the file instead.  native=True lets the library read the tensors itself (l2b_model_load_gguf: its own
+    parser, memory map and upload; `model.weights` is then None); the tokenizer is built here either way."""
     buf = np.memmap(filename, dtype=np.uint8, mode="r") if mmap else np.fromfile(filename, dtype=np.uint8)
     r = _Reader(buf)
     tensor_count, kv = read_gguf_header(r)
     infos = [read_gguf_tensor_info(r) for _ in range(tensor_count)]
     alignment = int(kv.get("general.alignment", 32))
     pad_offset = align_offset(r.pos, alignment)
-    tensors = {name: _tensor(buf, pad_offset + off, dims, typ) for name, dims, typ, off in infos}
+    tensors = {} if native else {name: _tensor(buf, pad_offset + off, dims, typ) for name, dims, typ, off in infos}
 
     id_to_token = [bytes(s) for s in kv["tokenizer.ggml.tokens"]]
     token_types = kv["tokenizer.ggml.token_type"]
@@ -187,6 +188,13 @@ def load_gguf_model(filename: str, mmap: bool = True, seq_len: int = 512, **kw) 
     tokenizer = BPETokenizer(id_to_token, token_to_id, scores, int(kv["tokenizer.ggml.bos_token_id"]), int(kv["tokenizer.ggml.eos_token_id"]))
 
     arch = kv["general.architecture"].decode()
+    if native:
+        from .model import _DeviceModel
+        dev, config = _DeviceModel.from_gguf(filename, seq_len, kw.get("act_planes", 0), kw.get("device", -1), kw.get("stream"),
+                                             kw.get("tp_size", 1), kw.get("tp_rank", 0))
+        model = LanguageModel(config, tokenizer, None, **kw)
+        model._dev = dev
+        return model
     if seq_len == 0:
         seq_len = int(kv[f"{arch}.context_length"])
     if arch == "llama":

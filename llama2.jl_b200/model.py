@@ -130,6 +130,23 @@ class _DeviceModel:
             self.close()
             raise
 
+    @classmethod
+    def from_gguf(cls, path: str, seq_len: int, act_planes=0, device=-1, stream=None, tp_size=1, tp_rank=0):
+        """Weights loaded by the library's own GGUF reader (l2b_model_load_gguf); returns (device model, ModelConfig)."""
+        lib = L.lib()
+        self = cls.__new__(cls)
+        self.model, self.session = C.c_void_p(), C.c_void_p()
+        cfg = L.Config()
+        L.check(lib.l2b_model_load_gguf(path.encode(), int(seq_len), act_planes, device, tp_size, tp_rank, C.byref(cfg), C.byref(self.model)))
+        try:
+            L.check(lib.l2b_session_create(self.model, stream, C.byref(self.session)))
+        except Exception:
+            self.close()
+            raise
+        config = ModelConfig(cfg.dim, cfg.hidden_dim, cfg.n_layers, cfg.n_heads, cfg.n_kv_heads, cfg.vocab_size, cfg.seq_len,
+                             float(cfg.rope_freq_base), bool(cfg.rope_is_neox))
+        return self, config
+
     def close(self):
         lib = L.lib()
         if self.session:

@@ -122,3 +122,30 @@ def test_decode_next_session_semantics(pkg, synth):
     assert model.kernels_per_token() == 5 * 1 + 3
     assert model.weight_bytes_per_token() > 0
     model.close()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("arch", ["llama", "phi3"])
+def test_native_gguf_loader_matches_python_loader(pkg, synth, tmp_path, arch):
+    """l2b_model_load_gguf (the library's own parser, map and upload) gives the same greedy stream and logits as the
+    model built from the arrays of the Python loader."""
+    from test_host_logic import _write_gguf
+    neox = arch == "phi3"
+    cfg = pkg.ModelConfig(256, 512, 2, 4, 4 if neox else 2, 64, 512, 500000.0, neox)
+    types = dict(synth.ALL(13), output=14) if neox else dict(synth.ALL(12), wv=13, w2=13, output=14)
+    w = synth.model_weights(cfg, types, seed=8)
+    path = str(tmp_path / f"{arch}.gguf")
+    _write_gguf(path, arch, cfg, w, synth, fused=neox)
+    a = pkg.load_gguf_model(path, seq_len=64)
+    b = pkg.load_gguf_model(path, seq_len=64, native=True)
+    assert b.weights is None and b.config == a.config
+    prompt = synth.tokens(6, 5, 3, cfg.vocab_size)
+    ta, _ = pkg.generate(a, prompt, 32)
+    tb, _ = pkg.generate(b, prompt, 32)
+    assert np.array_equal(ta, tb)
+    sa, sb = pkg.RunState(a), pkg.RunState(b)
+    pkg.transformer_(7, 0, a.config, sa)
+    pkg.transformer_(7, 0, b.config, sb)
+    assert np.array_equal(sa.logits.view(np.uint32), sb.logits.view(np.uint32))
+    a.close()
+    b.close()

@@ -187,6 +187,40 @@ def test_gguf_loader(pkg, synth, tmp_path, arch):
     assert np.array_equal(m.weights.layers[0].rms_att_weight, np.ones(256, np.float32))
 
 
+@pytest.mark.parametrize("arch", ["llama", "phi3"])
+def test_native_gguf_inspect(pkg, synth, tmp_path, arch):
+    """The library's own GGUF parser (no device needed): config, architecture, tensor count, context length."""
+    import ctypes as C
+    from llama2_jl_b200 import _lib as L
+    neox = arch == "phi3"
+    cfg = pkg.ModelConfig(256, 512, 2, 4, 4 if neox else 2, 40, 512, 500000.0, neox)
+    w = synth.model_weights(cfg, dict(synth.ALL(13), output=14) if neox else dict(synth.ALL(12), wv=13, w2=13, output=14), seed=8)
+    path = str(tmp_path / f"{arch}.gguf")
+    _write_gguf(path, arch, cfg, w, synth, fused=neox)
+    out, a, n, ctx = L.Config(), C.c_int32(), C.c_int64(), C.c_int64()
+    L.check(L.lib().l2b_gguf_inspect(path.encode(), C.byref(out), C.byref(a), C.byref(n), C.byref(ctx)))
+    assert (out.dim, out.hidden_dim, out.n_layers, out.n_heads, out.n_kv_heads, out.vocab_size) == (256, 512, 2, 4, cfg.n_kv_heads, 40)
+    assert abs(out.rope_freq_base - 500000.0) < 1e-3 and bool(out.rope_is_neox) == neox
+    assert a.value == (1 if neox else 0) and ctx.value == 2048 and out.seq_len == 2048
+    assert n.value == 3 + 2 * (6 if neox else 9)
+
+
+def test_native_gguf_rejects_other_files(pkg, tmp_path):
+    import ctypes as C
+    from llama2_jl_b200 import _lib as L
+    lib = L.lib()
+    out = L.Config()
+    cases = {"magic": b"GGML" + b"\0" * 64, "short": b"GGUF\x03", "truncated": b"GGUF" + (3).to_bytes(4, "little") + (5).to_bytes(8, "little") + (9).to_bytes(8, "little"),
+             "huge_count": b"GGUF" + (3).to_bytes(4, "little") + (1 << 40).to_bytes(8, "little") + (0).to_bytes(8, "little") + b"\0" * 32}
+    for name, blob in cases.items():
+        p = tmp_path / f"{name}.gguf"
+        p.write_bytes(blob)
+        assert lib.l2b_gguf_inspect(str(p).encode(), C.byref(out), None, None, None) == L.ERR_BAD_ARG, name
+        if name == "magic":
+            assert b"Not a GGUF file" in lib.l2b_last_error_string()  # the reference's message (src/load_gguf.jl:89)
+    assert lib.l2b_gguf_inspect(str(tmp_path / "missing.gguf").encode(), C.byref(out), None, None, None) == L.ERR_BAD_ARG
+
+
 def test_gguf_rejects_other_files(pkg, tmp_path):
     p = tmp_path / "x.gguf"
     p.write_bytes(b"GGML" + b"\0" * 64)
