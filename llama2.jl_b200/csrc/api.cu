@@ -63,6 +63,7 @@ struct DevMatrix {
     uint8_t* data = nullptr;  // f32 rows, or block records
     __half* d6 = nullptr;     // q6_K super-block scales
     int64_t file_bytes = 0;   // bytes in the stored (file) format
+    bool panels = false;      // k-quant rows longer than 16 blocks, stored as column panels
     bool present() const { return data != nullptr; }
 };
 
@@ -75,7 +76,29 @@ static void free_matrix(DevMatrix& m) {
 }
 
 // Copy one matrix to the device (repacking q6_K).  `rows` x `in` weights.
-static int32_t upload_matrix(DevMatrix& m, int type, const void* host, int64_t in, int64_t out, cudaStream_t st) {
+// Rows longer than one stage (in > 4096) are re-ordered into column panels on the device (panelize_kernel) unless
+// `panels` is false (matrices that are read row by row: the embedding table, plain dequantisation).
+static int32_t panelize(DevMatrix& m, cudaStream_t st) {
+    const int64_t nb = m.in / QK_K;
+    if (m.type == T_F32 || nb <= MV_TILE_BLOCKS || m.out < 2) return L2B_OK;
+    const int bb = dev_block_bytes(m.type);
+    const size_t bytes = (size_t)nb * m.out * bb;
+    uint8_t* dst = nullptr;
+    CU(cudaMalloc(&dst, bytes));
+    panelize_kernel<<<1184, 256, 0, st>>>(m.data, dst, (int)nb, m.out, bb);
+    cudaError_t e = cudaGetLastError();
+    if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+    if (e != cudaSuccess) {
+        cudaFree(dst);
+        CU(e);
+    }
+    cudaFree(m.data);
+    m.data = dst;
+    m.panels = true;
+    return L2B_OK;
+}
+
+static int32_t upload_matrix(DevMatrix& m, int type, const void* host, int64_t in, int64_t out, cudaStream_t st, bool panels = true) {
     if (!type_supported(type)) return fail(L2B_ERR_UNSUPPORTED_TYPE, "tensor type " + std::to_string(type) + " not implemented");
     if (!host || in <= 0 || out <= 0) return fail(L2B_ERR_BAD_ARG, "upload: null pointer or empty shape");
     if (type != T_F32 && in % QK_K != 0) return fail(L2B_ERR_BAD_ARG, "k-quant tensors need in_dim % 256 == 0");
@@ -97,7 +120,7 @@ static int32_t upload_matrix(DevMatrix& m, int type, const void* host, int64_t i
         CU(cudaMalloc(&m.data, (size_t)m.file_bytes));
         CU(cudaMemcpyAsync(m.data, host, (size_t)m.file_bytes, cudaMemcpyHostToDevice, st));
         CU(cudaStreamSynchronize(st));
-        return L2B_OK;
+        return panels ? panelize(m, st) : L2B_OK;
     }
     uint8_t* raw = nullptr;
     CU(cudaMalloc(&raw, (size_t)m.file_bytes));
@@ -111,7 +134,7 @@ static int32_t upload_matrix(DevMatrix& m, int type, const void* host, int64_t i
     if (e == cudaSuccess) e = cudaStreamSynchronize(st);
     cudaFree(raw);
     CU(e);
-    return L2B_OK;
+    return panels ? panelize(m, st) : L2B_OK;
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -542,7 +565,7 @@ extern "C" int32_t l2b_model_upload_tensor(l2b_model* m, int32_t role, int32_t l
         }
     }
     switch (role) {
-        case L2B_ROLE_TOKEN_EMBEDDING: L2B_TRY(want(c.dim, c.vocab_size)); return upload_matrix(m->tok_emb, type, host, in_dim, out_dim, 0);
+        case L2B_ROLE_TOKEN_EMBEDDING: L2B_TRY(want(c.dim, c.vocab_size)); return upload_matrix(m->tok_emb, type, host, in_dim, out_dim, 0, false);
         case L2B_ROLE_OUTPUT: L2B_TRY(want(c.dim, c.vocab_size)); return upload_matrix(m->output, type, host, in_dim, out_dim, 0);
         case L2B_ROLE_RMS_FINAL: return norm(m->rms_final);
         case L2B_ROLE_RMS_ATT: return norm(lw->rms_att);
@@ -1304,7 +1327,7 @@ extern "C" int32_t l2b_dequantize(int32_t type, const void* host_blocks, int64_t
     }
     if (n % QK_K != 0) return fail(L2B_ERR_BAD_ARG, "element count must be a multiple of 256");
     DevMatrix m;
-    int32_t st = upload_matrix(m, type, host_blocks, n, 1, 0);
+    int32_t st = upload_matrix(m, type, host_blocks, n, 1, 0, false);
     if (st != L2B_OK) return st;
     DevBuf out;
     st = dev_alloc(out, (size_t)n * 4);

@@ -430,9 +430,8 @@ __host__ __device__ inline int pad_32_mod_128(int v) {
 // Host side: decide the copy grouping of a segment.  kb = super-blocks per row and stage, nit = stages per row.
 __host__ inline void mv_fill_geometry(MvSegment& sg, int kb, int nit) {
     sg.rowb = kb * dev_block_bytes(sg.type);
-    if (nit > 1) {
-        sg.ngroups = 16; sg.rpg = 1;
-    } else if (sg.pair_mode == PAIR_ADJACENT) {
+    (void)nit;  // rows longer than a stage are stored as column panels (panelize_kernel): every stage looks like a short row
+    if (sg.pair_mode == PAIR_ADJACENT) {
         sg.ngroups = 4; sg.rpg = 4;
     } else {
         sg.ngroups = 8; sg.rpg = 2;
@@ -440,15 +439,13 @@ __host__ inline void mv_fill_geometry(MvSegment& sg, int kb, int nit) {
     sg.gs = pad_32_mod_128(sg.rpg * sg.rowb);
 }
 // Byte offsets of the two rows (A, B) of pair j inside a slot.
-__device__ __forceinline__ void pair_offsets(const MvSegment& t, int j, int& offA, int& offB) {
-    if (t.rpg == 1) {
-        offA = j * t.gs;
-        offB = (j + 8) * t.gs;
-    } else if (t.rpg == 4) {
-        offA = (j >> 1) * t.gs + 2 * (j & 1) * t.rowb;
-        offB = offA + t.rowb;
+// rowb = bytes of one row in THIS stage (the last panel of a long row may be narrower than 16 blocks).
+__device__ __forceinline__ void pair_offsets(const MvSegment& t, int rowb, int j, int& offA, int& offB) {
+    if (t.rpg == 4) {
+        offA = (j >> 1) * t.gs + 2 * (j & 1) * rowb;
+        offB = offA + rowb;
     } else {
-        offA = (j >> 1) * t.gs + (j & 1) * t.rowb;
+        offA = (j >> 1) * t.gs + (j & 1) * rowb;
         offB = offA + 4 * t.gs;
     }
 }
@@ -582,12 +579,15 @@ __global__ void __launch_bounds__((MV_MAX_CONSUMERS + 2) * 32, 1) fused_matvec_k
             uint32_t bytes0;     // bytes of this lane's copy in a full-width stage (0: nothing to copy)
             uint32_t tx0;        // bytes of the whole stage (all lanes) in a full-width stage
             int bb, nrows, nvalid, gs;
+            int row;             // matrix row of this lane's copy (panel addressing of long rows)
+            size_t ps;           // bytes of one full column panel of the matrix (rows * 16 blocks)
         };
         auto tile_src = [&](int j) {
             TileSrc ts;
             ts.src = nullptr;
             ts.bytes0 = ts.tx0 = 0;
-            ts.bb = ts.nrows = ts.nvalid = ts.gs = 0;
+            ts.bb = ts.nrows = ts.nvalid = ts.gs = ts.row = 0;
+            ts.ps = 0;
             if (j >= my_units) return ts;
             const UnitInfo u = find_unit<true>(p, (int)blockIdx.x + j * (int)gridDim.x);
             const MvSegment sg = get_segment(p, u.seg);
@@ -598,7 +598,8 @@ __global__ void __launch_bounds__((MV_MAX_CONSUMERS + 2) * 32, 1) fused_matvec_k
             if (c < sg.ngroups) {
                 if (sg.rpg == 4) {  // adjacent rows 16*tile + 4c ..
                     ts.nrows = max(0, min(4, 2 * pairs_left - 4 * c));
-                    ts.src = sg.w + (size_t)(2 * u.pair0 + 4 * c) * nb * ts.bb;
+                    ts.row = 2 * u.pair0 + 4 * c;
+                    ts.src = sg.w + (size_t)ts.row * sg.rowb;
                 } else {
                     const int half = (sg.rpg == 2) ? (c >> 2) : (c >> 3);      // A or B rows
                     const int jp = (sg.rpg == 2) ? 2 * (c & 3) : (c & 7);      // pair of the copy's first row
@@ -607,12 +608,14 @@ __global__ void __launch_bounds__((MV_MAX_CONSUMERS + 2) * 32, 1) fused_matvec_k
                         int rowA, rowB;
                         pair_rows(p, sg, u.pair0 + jp, rowA, rowB);
                         const uint8_t* base = (sg.pair_mode == PAIR_DUAL && half) ? sg.w2 : sg.w;
-                        ts.src = base + (size_t)(half ? rowB : rowA) * nb * ts.bb;
+                        ts.row = half ? rowB : rowA;
+                        ts.src = base + (size_t)ts.row * sg.rowb;
                     }
                 }
             }
             ts.bytes0 = (uint32_t)(ts.nrows * sg.rowb);
             ts.tx0 = (uint32_t)(ts.nvalid * sg.rowb);
+            ts.ps = (size_t)(sg.pair_mode == PAIR_DUAL ? sg.npairs : 2 * sg.npairs) * sg.rowb;
             return ts;
         };
         bool dead = false, first = true;
@@ -624,7 +627,8 @@ __global__ void __launch_bounds__((MV_MAX_CONSUMERS + 2) * 32, 1) fused_matvec_k
         // Fast path for the common case (one segment, adjacent or dual rows, full tiles): the next tile's source
         // is the current one plus a constant.
         const bool linear = (p.nseg == 1) && (p.seg[0].pair_mode != PAIR_NEOX);
-        const size_t tile_step = linear ? (size_t)gridDim.x * (p.seg[0].pair_mode == PAIR_ADJACENT ? 16 : 8) * nb * dev_block_bytes(p.seg[0].type) : 0;
+        const int row_step = (int)gridDim.x * (p.seg[0].pair_mode == PAIR_ADJACENT ? 16 : 8);  // rows between a block's consecutive tiles
+        const size_t tile_step = linear ? (size_t)row_step * p.seg[0].rowb : 0;
         const int full_tiles = linear ? p.seg[0].npairs / MV_TILE_PAIRS : 0;  // tiles below this index are complete
         for (int j = 0; j < my_units && !dead; ++j) {
             const int grp = (CG == 2) ? (j & 1) : 0;
@@ -641,16 +645,18 @@ __global__ void __launch_bounds__((MV_MAX_CONSUMERS + 2) * 32, 1) fused_matvec_k
                     }
                 }
                 uint32_t bytes = ts.bytes0, tx = ts.tx0;
-                if (nit > 1) {  // a stage is a 16-block slice of every row (one row per copy)
+                const uint8_t* src = ts.src;
+                if (nit > 1) {  // stage `it` lives in column panel `it`, whose rows are nblk blocks wide
                     const int nblk = min(MV_TILE_BLOCKS, nb - it * MV_TILE_BLOCKS);
-                    bytes = ts.nrows ? (uint32_t)(nblk * ts.bb) : 0u;
+                    bytes = (uint32_t)(ts.nrows * nblk * ts.bb);
                     tx = (uint32_t)(ts.nvalid * nblk * ts.bb);
+                    src += (size_t)it * ts.ps - (size_t)ts.row * ((MV_TILE_BLOCKS - nblk) * ts.bb);
                 }
                 if (DBG && (p.debug & 2)) bytes = tx = 0;
                 if (c == 0) mbar_arrive_expect_tx(full + slot_i, tx);
                 __syncwarp(0x0000ffffu);
                 if (bytes)
-                    bulk_g2s(ring + (size_t)slot_i * L.slot_bytes + (size_t)c * ts.gs, ts.src + (size_t)it * (MV_TILE_BLOCKS * ts.bb), bytes, full + slot_i, policy);
+                    bulk_g2s(ring + (size_t)slot_i * L.slot_bytes + (size_t)c * ts.gs, src, bytes, full + slot_i, policy);
                 if (DBG && first && p.trace && lane == 0) p.trace[blockIdx.x * 16 + 1] = global_ns();
                 first = false;
                 if (++slot_i == (grp + 1) * NSG) {
@@ -667,7 +673,10 @@ __global__ void __launch_bounds__((MV_MAX_CONSUMERS + 2) * 32, 1) fused_matvec_k
             }
             // parameters of the next tile (in the shadow of the wait for its slot)
             const int next_tile = (int)blockIdx.x + (j + 1) * (int)gridDim.x;
-            if (linear && next_tile < full_tiles) ts.src += tile_step;
+            if (linear && next_tile < full_tiles) {
+                ts.src += tile_step;
+                ts.row += row_step;
+            }
             else ts = tile_src(j + 1);
         }
         if (dead) {
@@ -786,7 +795,7 @@ __global__ void __launch_bounds__((MV_MAX_CONSUMERS + 2) * 32, 1) fused_matvec_k
                 seg_first = (seg_i == 0) ? 0 : (seg_i == 1 ? p.seg_start[1] : p.seg_start[2]);
                 seg_end = (seg_i == 0) ? p.seg_start[1] : (seg_i == 1 ? p.seg_start[2] : p.seg_start[3]);
                 bb = dev_block_bytes(sg.type);
-                pair_offsets(sg, pj, offA, offB);
+                pair_offsets(sg, sg.rowb, pj, offA, offB);
             }
             UnitInfo u;
             u.seg = seg_i;
@@ -804,6 +813,8 @@ __global__ void __launch_bounds__((MV_MAX_CONSUMERS + 2) * 32, 1) fused_matvec_k
             float accA = 0.f, accB = 0.f;  // the two rows of pair pj of the tile
             for (int it = 0; it < nit; ++it) {
                 const int b0 = it * MV_TILE_BLOCKS, nblk = min(MV_TILE_BLOCKS, nb - b0);
+                int oA = offA, oB = offB;
+                if (nit > 1 && nblk < MV_TILE_BLOCKS) pair_offsets(sg, nblk * bb, pj, oA, oB);  // narrow last panel
                 float dA = 0.f, dB = 0.f;
                 if (sg.type == T_Q6_K && wl < nblk) {  // fetched before the wait so that the latency overlaps it
                     dA = __half2float(__ldg(d6A + b0 + wl));
@@ -813,8 +824,8 @@ __global__ void __launch_bounds__((MV_MAX_CONSUMERS + 2) * 32, 1) fused_matvec_k
                 if (!dead && !(DBG && (p.debug & 1))) {
                     const uint8_t* slot = ring + (size_t)slot_i * L.slot_bytes;
                     for (int bl = wl; bl < nblk; bl += WG) {
-                        const uint8_t* rA = slot + offA + bl * bb;
-                        const uint8_t* rB = slot + offB + bl * bb;
+                        const uint8_t* rA = slot + oA + bl * bb;
+                        const uint8_t* rB = slot + oB + bl * bb;
                         if (sg.type == T_Q4_K) tile_q4k(rA, rB, b0 + bl, cx, accA, accB);
                         else if (sg.type == T_Q5_K) tile_q5k(rA, rB, b0 + bl, cx, accA, accB);
                         else {

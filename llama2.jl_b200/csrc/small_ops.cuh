@@ -18,6 +18,24 @@ __global__ void repack_q6k_kernel(const uint8_t* __restrict__ src, uint8_t* __re
     }
 }
 
+// Matrices whose rows are longer than one stage (more than 16 super-blocks) are stored as column panels: panel k holds
+// blocks 16k .. 16k+15 of EVERY row, rows back to back.  A tile's stage is then 16 adjacent rows of one panel, which a
+// few large bulk copies bring in, instead of 16 row slices that lie a whole row apart.  Same bytes, other order.
+//   address(row, block b) = (b / 16) * rows * 16 * bb  +  row * w * bb  +  (b % 16) * bb,   w = width of panel b / 16
+__global__ void panelize_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst, int nb, int64_t rows, int bb) {
+    const int q = bb / 16;  // 16-byte units per block
+    const int64_t total = rows * nb * q;
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t blk = i / q;
+        const int u = (int)(i % q);
+        const int64_t r = blk / nb;
+        const int b = (int)(blk % nb);
+        const int k = b / 16, w = min(16, nb - 16 * k);
+        const int64_t o = (int64_t)k * rows * 16 + r * w + (b % 16);
+        reinterpret_cast<uint4*>(dst)[o * q + u] = reinterpret_cast<const uint4*>(src)[i];
+    }
+}
+
 // dequantize! of n values from device-layout blocks.
 __global__ void dequantize_kernel(int type, const uint8_t* __restrict__ blocks, const __half* __restrict__ d6, int64_t n, float* __restrict__ out) {
     for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
