@@ -162,6 +162,10 @@ int32_t l2b_session_logits(l2b_session* session, float* host_logits);
 int32_t l2b_session_read(l2b_session* session, int32_t which, float* host_out, int64_t capacity, int64_t* n);
 /* Device time (ms, CUDA events on the session stream) of the most recent forward/decode/generate call. */
 int32_t l2b_session_last_device_ms(l2b_session* session, float* ms);
+/* 1 when l2b_generate feeds prompts two positions per pass (k-quant model, three activation planes, one GPU, everything fits in
+ * shared memory; switch off with L2B_PREFILL_PAIRS=0): positions p, p+1 that are both followed by a prompt token share one pass
+ * over the weights, and no logits are computed for them.  The reference feeds prompts token by token (src/inference.jl:349-356). */
+int32_t l2b_session_prefill_pairs(l2b_session* session, int32_t* enabled);
 /* Number of kernel launches the captured token graph contains. */
 int32_t l2b_session_kernels_per_token(l2b_session* session, int32_t* n);
 

@@ -179,6 +179,7 @@ struct MvLaunch {
     MvParams p;
     bool kq = true;
     int planes = 3;
+    int nb = 1;  // activation vectors per launch (2: two prompt positions per pass)
     int grid = 0, warps = 0;
     size_t smem = 0;
 };
@@ -236,7 +237,7 @@ static int32_t plan_matvec(MvLaunch& L, const DeviceInfo& di) {
     p.row_stride = (int)((slot + 15) / 16);
     p.row_stride += (16 - p.row_stride % 16) % 16;
     slot = 16L * p.row_stride;
-    const long base = mv_smem_layout(p.n_in, L.planes, true, 0, p.row_stride).total;
+    const long base = mv_smem_layout(p.n_in, L.planes, true, 0, p.row_stride, L.nb).total;
     const long cap = std::min<long>(env_long("L2B_MV_SMEM_KB", 208) * 1024, di.max_smem_optin - 1024);
     const long per_block_stages = (long)(p.units_lo + (p.units_rem ? 1 : 0)) * p.nit;
     long ns = std::min<long>(std::min<long>(MV_MAX_SLOTS, std::max<long>(per_block_stages, 2)), (cap - base) / slot);
@@ -256,7 +257,7 @@ static int32_t plan_matvec(MvLaunch& L, const DeviceInfo& di) {
     ns -= ns % groups;  // every group owns the same number of slots
     if (ns < groups) return fail(L2B_ERR_BAD_ARG, "input dimension too large for the activation planes to fit in shared memory");
     p.nslots = (int)ns;
-    L.smem = mv_smem_layout(p.n_in, L.planes, true, p.nslots, p.row_stride).total;
+    L.smem = mv_smem_layout(p.n_in, L.planes, true, p.nslots, p.row_stride, L.nb).total;
     return L2B_OK;
 }
 
@@ -278,6 +279,7 @@ static void set_kernel_attrs() {
         set((const void*)fused_matvec_kernel<true, 2>);
         set((const void*)fused_matvec_kernel<true, 3>);
         set((const void*)fused_matvec_kernel<false, 1>);
+        set((const void*)fused_matvec_kernel<true, 3, false, false, 2>);
         set((const void*)fused_matvec_kernel<true, 1, false, true>);
         set((const void*)fused_matvec_kernel<true, 2, false, true>);
         set((const void*)fused_matvec_kernel<true, 3, false, true>);
@@ -309,6 +311,10 @@ static cudaError_t launch_matvec(const MvLaunch& L, cudaStream_t st, bool pdl) {
             default: return launch_kernel(fused_matvec_kernel<true, 3, false, true>, grid, block, L.smem, st, pdl, L.p);
         }
     }
+    if (L.nb == 2) {  // two prompt positions per pass: k-quant weights, three planes, one GPU only
+        if (!L.kq || L.planes != 3 || L.p.tp) return cudaErrorNotSupported;
+        return launch_kernel(fused_matvec_kernel<true, 3, false, false, 2>, grid, block, L.smem, st, pdl, L.p);
+    }
     if (!L.kq) return launch_kernel(fused_matvec_kernel<false, 1>, grid, block, L.smem, st, pdl, L.p);
     if (L.p.tp)  // the variants that carry the tensor-parallel exchange
         switch (L.planes) {
@@ -338,7 +344,7 @@ static MvSegment make_segment(const DevMatrix& m, int pair_mode, int epi, float*
 }
 
 static cudaError_t launch_attention(const AttnParams& a, int gq, cudaStream_t st, bool pdl) {
-    const dim3 grid((a.n_heads / gq) * a.nsplit), block(ATTN_WARPS * 32);
+    const dim3 grid((a.n_heads / gq) * a.nsplit * (a.nq > 1 ? a.nq : 1)), block(ATTN_WARPS * 32);
     switch (gq) {
         case 8: return launch_kernel(attention_split_kernel<8>, grid, block, 0, st, pdl, a);
         case 4: return launch_kernel(attention_split_kernel<4>, grid, block, 0, st, pdl, a);
@@ -418,6 +424,8 @@ struct l2b_session {
     Control* h_ctl = nullptr;
     int* h_small = nullptr;  // [0] next token, [1] status
     cudaGraphExec_t graph = nullptr;
+    cudaGraphExec_t graph2 = nullptr;  // two prompt positions per pass (null when the model does not qualify)
+    bool all_kquant = true;            // set while the one-position graph is built
     int kernels_per_token = 0;
     cudaEvent_t ev0 = nullptr, ev1 = nullptr;
     float last_ms = 0.f;
@@ -766,6 +774,7 @@ extern "C" int32_t l2b_model_load_gguf(const char* path, int32_t seq_len, int32_
 static void session_free(l2b_session* s) {
     if (!s) return;
     if (s->graph) cudaGraphExecDestroy(s->graph);
+    if (s->graph2) cudaGraphExecDestroy(s->graph2);
     void* bufs[] = {s->x, s->q, s->att, s->tickets, s->hb, s->logits, s->kc, s->vc, s->part_m, s->part_l, s->part_acc, s->amax_val, s->amax_idx,
                     s->rope_cs, s->ctl, s->status, s->prompt, s->out_tokens, s->next_token};
     for (void* b : bufs)
@@ -787,24 +796,40 @@ static void session_free(l2b_session* s) {
 }
 
 struct l2b_session;
-static cudaError_t cudaLaunchKernelEx_embed(const l2b_model* m, l2b_session* s, int blocks, int threads);
+static cudaError_t cudaLaunchKernelEx_embed(const l2b_model* m, l2b_session* s, int blocks, int threads, int second);
 
 // Enqueue every kernel of one token on the session stream (this is what the graph captures).
-static int32_t enqueue_token(l2b_session* s, int* nlaunch) {
+// nb = 2: a pass over TWO consecutive prompt positions (pos, pos + 1), both of which are followed by a prompt token:
+// every matrix is streamed once for both, no logits are computed and nothing is sampled.
+static int32_t enqueue_token(l2b_session* s, int* nlaunch, int nb = 1) {
     const l2b_model* m = s->model;
     const l2b_config& c = m->cfg;
     const int hs = c.dim / c.n_heads;
     const size_t kvl = kv_layer_elems(m);
     int count = 0, last_grid = 0;
     bool first = true;
+    // Debugging aid (L2B_EAGER_CHECK=1, used by l2b_generate outside graph capture): wait after every launch and name
+    // the first one that fails.
+    const bool eager = env_long("L2B_EAGER_CHECK", 0) != 0;
+    auto checked = [&](const char* what) -> int32_t {
+        if (!eager) return L2B_OK;
+        cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
+        if (cudaStreamIsCapturing(s->stream, &cs) != cudaSuccess || cs != cudaStreamCaptureStatusNone) return L2B_OK;
+        cudaError_t e = cudaStreamSynchronize(s->stream);
+        if (e != cudaSuccess) return fail(L2B_ERR_CUDA, std::string("launch ") + std::to_string(count) + " (" + what + ", nb=" + std::to_string(nb) + "): " + cudaGetErrorString(e));
+        return L2B_OK;
+    };
     auto mv = [&](MvLaunch& L) -> int32_t {
         L.planes = m->planes;
+        L.nb = nb;
         L2B_TRY(plan_matvec(L, s->di));
+        if (!L.kq) s->all_kquant = false;
         if (s->trace) L.p.trace = s->trace + (size_t)(s->trace_launches++) * s->di.sms * 16;
         CU(launch_matvec(L, s->stream, !first));
         last_grid = L.grid;
         first = false;
         ++count;
+        L2B_TRY(checked(L.p.seg[0].epi == EPI_ROPE_Q ? "qkv" : L.p.seg[0].epi == EPI_SWIGLU ? "gate/up" : L.p.seg[0].epi == EPI_LOGITS ? "logits" : (L.p.n_in == c.dim / m->tp ? "wo" : "down")));
         return L2B_OK;
     };
     auto base_params = [&](MvLaunch& L, int n_in) {
@@ -854,6 +879,7 @@ static int32_t enqueue_token(l2b_session* s, int* nlaunch) {
     auto partial_output = [&](MvLaunch& L, const DevMatrix& w, int e) {
         if (tp == 1) {
             L.p.seg[L.p.nseg++] = make_segment(w, PAIR_ADJACENT, EPI_RESIDUAL, s->x, hs);
+            L.p.seg[L.p.nseg - 1].out2 = c.dim;
             L.p.resid = s->x;
             return;
         }
@@ -869,9 +895,13 @@ static int32_t enqueue_token(l2b_session* s, int* nlaunch) {
     // --- token embedding row -> residual stream (inference.jl:236)
     {
         const int threads = 256, blocks = std::max(1, std::min(32, c.dim / 256));
-        CU(cudaLaunchKernelEx_embed(m, s, blocks, threads));
+        CU(cudaLaunchKernelEx_embed(m, s, blocks, threads, 0));
         first = false;
         ++count;
+        if (nb == 2) {
+            CU(cudaLaunchKernelEx_embed(m, s, blocks, threads, 1));
+            ++count;
+        }
     }
     for (int l = 0; l < c.n_layers; ++l) {
         const LayerW& w = m->layers[l];
@@ -881,6 +911,7 @@ static int32_t enqueue_token(l2b_session* s, int* nlaunch) {
         {
             MvSegment segs[3] = {make_segment(w.wq, rope_mode, EPI_ROPE_Q, s->q, hs), make_segment(w.wk, rope_mode, EPI_ROPE_K, kcl, hs),
                                  make_segment(w.wv, PAIR_ADJACENT, EPI_STORE_V, vcl, hs)};
+            segs[0].out2 = m->l_qdim();  // the caches take both positions at their own rows: out2 = 0
             // matrices of one storage class (f32 or k-quant) share a launch
             for (int cls = 0; cls < 2; ++cls) {
                 MvLaunch L;
@@ -901,8 +932,10 @@ static int32_t enqueue_token(l2b_session* s, int* nlaunch) {
             a.part_m = s->part_m; a.part_l = s->part_l; a.part_acc = s->part_acc;
             a.pos = &s->ctl->pos;
             a.n_heads = m->l_heads; a.n_kv = m->l_kv; a.hs = hs; a.seq_len = c.seq_len; a.nsplit = s->nsplit;
+            a.nq = nb; a.q_stride = m->l_qdim();
             CU(launch_attention(a, s->gq, s->stream, true));
             ++count;
+            L2B_TRY(checked("attention"));
         }
         // --- output projection + residual (inference.jl:281-284)
         {
@@ -922,6 +955,7 @@ static int32_t enqueue_token(l2b_session* s, int* nlaunch) {
             g.npairs = (int)w.w1.out;
             g.w2 = w.w3.data;
             g.d6_2 = w.w3.d6;
+            g.out2 = m->l_hidden;
             L.p.seg[L.p.nseg++] = g;
             norm_input(L, w.rms_ffn);
             L2B_TRY(mv(L));
@@ -937,6 +971,14 @@ static int32_t enqueue_token(l2b_session* s, int* nlaunch) {
             L2B_TRY(mv(L));
             if (tp > 1) pending = 2 * l + 1, push_grid = last_grid;
         }
+    }
+    if (nb == 2) {  // both positions are followed by prompt tokens: no classifier, no sampling, move on by two
+        AdvanceParams ap;
+        ap.ctl = s->ctl; ap.prompt = s->prompt; ap.out_tokens = s->out_tokens; ap.epoch = s->tp_epoch;
+        CU(launch_kernel(advance_pair_kernel, dim3(1), dim3(32), 0, s->stream, true, ap));
+        ++count;
+        if (nlaunch) *nlaunch = count;
+        return L2B_OK;
     }
     // --- final rmsnorm + classifier + per-block argmax (inference.jl:309-312)
     {
@@ -964,14 +1006,15 @@ static int32_t enqueue_token(l2b_session* s, int* nlaunch) {
     return L2B_OK;
 }
 
-static cudaError_t cudaLaunchKernelEx_embed(const l2b_model* m, l2b_session* s, int blocks, int threads) {
+static cudaError_t cudaLaunchKernelEx_embed(const l2b_model* m, l2b_session* s, int blocks, int threads, int second) {
     cudaLaunchConfig_t cfg;
     memset(&cfg, 0, sizeof(cfg));
     cfg.gridDim = dim3(blocks);
     cfg.blockDim = dim3(threads);
     cfg.stream = s->stream;
     return cudaLaunchKernelEx(&cfg, embed_row_kernel, m->tok_emb.type, (const uint8_t*)m->tok_emb.data, (const __half*)m->tok_emb.d6,
-                              (const int*)&s->ctl->token, (int)m->cfg.dim, s->x);
+                              (const int*)&s->ctl->token, (int)m->cfg.dim, s->x + (second ? m->cfg.dim : 0), (const int*)(second ? s->prompt : nullptr),
+                              (const int*)&s->ctl->pos);
 }
 
 static int32_t capture_token_graph(l2b_session* s) {
@@ -995,6 +1038,25 @@ static int32_t capture_token_graph(l2b_session* s) {
     cudaError_t ie = cudaGraphInstantiate(&s->graph, g, 0);
     cudaGraphDestroy(g);
     CU(ie);
+    // Second graph: two prompt positions per pass.  Needs k-quant matrices throughout, three planes, one GPU.
+    if (s->model->tp == 1 && s->model->planes == 3 && s->all_kquant && !s->trace && env_long("L2B_PREFILL_PAIRS", 1) != 0) {
+        cudaGraph_t g2 = nullptr;
+        int n2 = 0;
+        CU(cudaStreamBeginCapture(s->stream, cudaStreamCaptureModeThreadLocal));
+        es = enqueue_token(s, &n2, 2);
+        ce = cudaStreamEndCapture(s->stream, &g2);
+        if (es != L2B_OK || ce != cudaSuccess) {
+            // e.g. two sets of activation planes of a very long input do not fit in shared memory: prompts then
+            // go through the one-position graph, as they do for f32 models
+            (void)cudaGetLastError();
+            if (g2) cudaGraphDestroy(g2);
+            g_last_error.clear();
+        } else {
+            ie = cudaGraphInstantiate(&s->graph2, g2, 0);
+            cudaGraphDestroy(g2);
+            CU(ie);
+        }
+    }
     return L2B_OK;
 }
 
@@ -1027,17 +1089,18 @@ extern "C" int32_t l2b_session_create(l2b_model* m, void* stream, l2b_session** 
         s->nsplit = (int)env_long("L2B_ATTN_SPLITS", ns);
         const size_t kvl = kv_layer_elems(m);
         // q, att, hb and the caches hold this rank's heads / hidden units only (everything, on one GPU)
-        CU(cudaMalloc(&s->x, (size_t)c.dim * 4));
-        CU(cudaMalloc(&s->q, (size_t)m->l_qdim() * 4));
-        CU(cudaMalloc(&s->att, (size_t)m->l_qdim() * 4));
-        CU(cudaMalloc(&s->tickets, (size_t)c.n_heads * 4));
-        CU(cudaMalloc(&s->hb, (size_t)m->l_hidden * 4));
+        // (two of each vector: the two-position prompt passes keep both positions' activations side by side)
+        CU(cudaMalloc(&s->x, (size_t)c.dim * 4 * 2));
+        CU(cudaMalloc(&s->q, (size_t)m->l_qdim() * 4 * 2));
+        CU(cudaMalloc(&s->att, (size_t)m->l_qdim() * 4 * 2));
+        CU(cudaMalloc(&s->tickets, (size_t)c.n_heads * 4 * 2));
+        CU(cudaMalloc(&s->hb, (size_t)m->l_hidden * 4 * 2));
         CU(cudaMalloc(&s->logits, (size_t)c.vocab_size * 4));
         CU(cudaMalloc(&s->kc, kvl * c.n_layers * 4));
         CU(cudaMalloc(&s->vc, kvl * c.n_layers * 4));
-        CU(cudaMalloc(&s->part_m, (size_t)m->l_heads * s->nsplit * 4));
-        CU(cudaMalloc(&s->part_l, (size_t)m->l_heads * s->nsplit * 4));
-        CU(cudaMalloc(&s->part_acc, (size_t)m->l_heads * s->nsplit * hs * 4));
+        CU(cudaMalloc(&s->part_m, (size_t)m->l_heads * s->nsplit * 4 * 2));
+        CU(cudaMalloc(&s->part_l, (size_t)m->l_heads * s->nsplit * 4 * 2));
+        CU(cudaMalloc(&s->part_acc, (size_t)m->l_heads * s->nsplit * hs * 4 * 2));
         CU(cudaMalloc(&s->amax_val, (size_t)s->di.sms * 4));
         CU(cudaMalloc(&s->amax_idx, (size_t)s->di.sms * 4));
         CU(cudaMalloc(&s->ctl, sizeof(Control)));
@@ -1052,7 +1115,7 @@ extern "C" int32_t l2b_session_create(l2b_model* m, void* stream, l2b_session** 
         CU(cudaMemsetAsync(s->kc, 0, kvl * c.n_layers * 4, s->stream));
         CU(cudaMemsetAsync(s->vc, 0, kvl * c.n_layers * 4, s->stream));
         CU(cudaMemsetAsync(s->status, 0, 4, s->stream));
-        CU(cudaMemsetAsync(s->tickets, 0, (size_t)c.n_heads * 4, s->stream));
+        CU(cudaMemsetAsync(s->tickets, 0, (size_t)c.n_heads * 4 * 2, s->stream));
         CU(cudaMemsetAsync(s->ctl, 0, sizeof(Control), s->stream));
         CU(cudaMemsetAsync(s->prompt, 0, (size_t)c.seq_len * 4, s->stream));
         std::vector<float> cs;
@@ -1223,6 +1286,12 @@ extern "C" int32_t l2b_decode_next(l2b_session* s, int32_t token, int32_t pos, f
     return L2B_OK;
 }
 
+extern "C" int32_t l2b_session_prefill_pairs(l2b_session* s, int32_t* enabled) {
+    if (!s || !enabled) return fail(L2B_ERR_BAD_ARG, "null argument");
+    *enabled = s->graph2 ? 1 : 0;
+    return L2B_OK;
+}
+
 extern "C" int32_t l2b_generate(l2b_session* s, const int32_t* prompt, int32_t n_prompt, int32_t n_positions, float temperature, uint64_t seed,
                                 int32_t* out_tokens, float* device_ms) {
     if (!s || !prompt || !out_tokens) return fail(L2B_ERR_BAD_ARG, "null argument");
@@ -1245,7 +1314,14 @@ extern "C" int32_t l2b_generate(l2b_session* s, const int32_t* prompt, int32_t n
     CU(cudaMemcpyAsync(s->prompt, prompt, (size_t)n_prompt * 4, cudaMemcpyHostToDevice, s->stream));
     CU(cudaMemcpyAsync(s->ctl, s->h_ctl, sizeof(Control), cudaMemcpyHostToDevice, s->stream));
     CU(cudaEventRecord(s->ev0, s->stream));  // the timed region is the token loop itself: inputs are resident
-    for (int i = 0; i < n_positions; ++i) CU(cudaGraphLaunch(s->graph, s->stream));
+    // Positions p and p + 1 go through one two-position pass when both are followed by a prompt token (their next
+    // tokens are forced, so neither needs logits); everything else takes the one-position graph.
+    for (int i = 0; i < n_positions;) {
+        const bool pair = s->graph2 && i + 2 < n_prompt && i + 1 < n_positions;
+        if (env_long("L2B_EAGER_CHECK", 0)) L2B_TRY(enqueue_token(s, nullptr, pair ? 2 : 1));  // debugging aid: no graph, a wait per launch
+        else CU(cudaGraphLaunch(pair ? s->graph2 : s->graph, s->stream));
+        i += pair ? 2 : 1;
+    }
     CU(cudaEventRecord(s->ev1, s->stream));
     CU(cudaMemcpyAsync(out_tokens, s->out_tokens, (size_t)n_positions * 4, cudaMemcpyDeviceToHost, s->stream));
     CU(cudaMemcpyAsync(&s->h_small[1], s->status, 4, cudaMemcpyDeviceToHost, s->stream));

@@ -30,6 +30,8 @@ struct AttnParams {
     const int* pos;   // device scalar, 0-based position of the query; positions 0..pos are attended
     int n_heads, n_kv, hs, seq_len, nsplit;
     int npos_override;  // >0: attend exactly this many positions (isolated-operator entry point)
+    int nq;             // 2: two consecutive query positions (pos, pos + 1) per launch; 0 or 1: one
+    int q_stride;       // elements between the two positions' q (and out) vectors
 };
 
 constexpr int ATTN_WARPS = 4;
@@ -39,9 +41,17 @@ constexpr int ATTN_MIN_CHUNK = 16;  // positions per split below which splitting
 template <int GQ>  // query heads served per block; GQ divides n_heads / n_kv
 __device__ __forceinline__ void attention_split_body(const AttnParams& p) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int hg = blockIdx.x / p.nsplit, sp = blockIdx.x % p.nsplit;
+    // with two query positions the grid holds two copies of the (head group, split) blocks: copy qi serves position pos + qi
+    const int ngroups = p.n_heads / GQ;
+    const int qi = (p.nq > 1) ? (int)blockIdx.x / (ngroups * p.nsplit) : 0;
+    const int bx = (int)blockIdx.x - qi * ngroups * p.nsplit;
+    const int hg = bx / p.nsplit, sp = bx % p.nsplit;
     const int kvh = (hg * GQ) / (p.n_heads / p.n_kv);
-    const int npos = p.npos_override > 0 ? p.npos_override : (__ldcg(p.pos) + 1);
+    const int npos = p.npos_override > 0 ? p.npos_override : (__ldcg(p.pos) + 1 + qi);
+    const float* const qbase = p.q + (size_t)qi * p.q_stride;
+    float* const obase = p.out + (size_t)qi * p.q_stride;
+    const int hq = qi * p.n_heads;   // first row of this position in the partial-result scratch
+    int* const ticket_p = p.tickets + qi * ngroups + hg;
     // Short contexts use fewer splits (at least ATTN_MIN_CHUNK positions each): blocks beyond `active` leave at
     // once, and a single active split writes its result directly, with no partials and no merge.
     const int active = min(p.nsplit, (npos + ATTN_MIN_CHUNK - 1) / ATTN_MIN_CHUNK);
@@ -58,7 +68,7 @@ __device__ __forceinline__ void attention_split_body(const AttnParams& p) {
 #pragma unroll
     for (int g = 0; g < GQ; ++g) {
         const int h = hg * GQ + g;
-        qv[g] = lane_active ? __ldcg(reinterpret_cast<const float4*>(p.q + (size_t)h * hs) + lane) : zero4;
+        qv[g] = lane_active ? __ldcg(reinterpret_cast<const float4*>(qbase + (size_t)h * hs) + lane) : zero4;
         acc[g] = zero4;
         m[g] = -INFINITY;
         l[g] = 0.f;
@@ -132,14 +142,14 @@ __device__ __forceinline__ void attention_split_body(const AttnParams& p) {
         if (active == 1) {  // nothing to merge across blocks
             if (lane_active) {
                 a.x /= Ls; a.y /= Ls; a.z /= Ls; a.w /= Ls;
-                reinterpret_cast<float4*>(p.out + (size_t)h * hs)[lane] = a;
+                reinterpret_cast<float4*>(obase + (size_t)h * hs)[lane] = a;
             }
         } else {
             if (lane == 0) {
-                p.part_m[(size_t)h * p.nsplit + sp] = M;
-                p.part_l[(size_t)h * p.nsplit + sp] = Ls;
+                p.part_m[(size_t)(hq + h) * p.nsplit + sp] = M;
+                p.part_l[(size_t)(hq + h) * p.nsplit + sp] = Ls;
             }
-            if (lane_active) reinterpret_cast<float4*>(p.part_acc + ((size_t)h * p.nsplit + sp) * hs)[lane] = a;
+            if (lane_active) reinterpret_cast<float4*>(p.part_acc + ((size_t)(hq + h) * p.nsplit + sp) * hs)[lane] = a;
         }
     }
     if (active == 1) return;
@@ -147,17 +157,17 @@ __device__ __forceinline__ void attention_split_body(const AttnParams& p) {
     __threadfence();
     __syncthreads();
     if (threadIdx.x == 0) {
-        const int ticket = atomicAdd(p.tickets + hg, 1);
+        const int ticket = atomicAdd(ticket_p, 1);
         s_last = (ticket == active - 1);
-        if (s_last) p.tickets[hg] = 0;  // ready for the next launch
+        if (s_last) *ticket_p = 0;  // ready for the next launch
     }
     __syncthreads();
     if (!s_last) return;
     __threadfence();
     for (int g = warp; g < GQ; g += ATTN_WARPS) {
         const int h = hg * GQ + g;
-        const float* pm = p.part_m + (size_t)h * p.nsplit;
-        const float* pl = p.part_l + (size_t)h * p.nsplit;
+        const float* pm = p.part_m + (size_t)(hq + h) * p.nsplit;
+        const float* pl = p.part_l + (size_t)(hq + h) * p.nsplit;
         // lane s holds split s (nsplit <= 32)
         const float ms = lane < active ? __ldcg(pm + lane) : -INFINITY;
         const float ls = lane < active ? __ldcg(pl + lane) : 0.f;
@@ -170,7 +180,7 @@ __device__ __forceinline__ void attention_split_body(const AttnParams& p) {
 #pragma unroll
             for (int u = 0; u < 4; ++u) {
                 b[u] = zero4;
-                if (lane_active && s0 + u < active) b[u] = __ldcg(reinterpret_cast<const float4*>(p.part_acc + ((size_t)h * p.nsplit + s0 + u) * hs) + lane);
+                if (lane_active && s0 + u < active) b[u] = __ldcg(reinterpret_cast<const float4*>(p.part_acc + ((size_t)(hq + h) * p.nsplit + s0 + u) * hs) + lane);
             }
 #pragma unroll
             for (int u = 0; u < 4; ++u) {
@@ -185,7 +195,7 @@ __device__ __forceinline__ void attention_split_body(const AttnParams& p) {
         }
         if (lane_active) {
             a.x /= Ls; a.y /= Ls; a.z /= Ls; a.w /= Ls;
-            reinterpret_cast<float4*>(p.out + (size_t)h * hs)[lane] = a;
+            reinterpret_cast<float4*>(obase + (size_t)h * hs)[lane] = a;
         }
     }
 }

@@ -69,6 +69,7 @@ struct MvSegment {
     int rpg;             // rows per copy
     int gs;              // bytes between copy groups inside a slot (= 32 mod 128)
     int rowb;            // bytes of one row in a full-width stage
+    int out2;            // two-position launches: element offset of the second position's output vector (0: same base, e.g. caches)
 };
 
 // What a tensor-parallel launch needs to know about the other GPUs.
@@ -134,7 +135,8 @@ __host__ __device__ inline int mv_row_stride(int blocks_per_stage, int block_byt
     return rs;
 }
 
-__host__ __device__ inline MvSmem mv_smem_layout(int n_in, int planes, bool kquant, int nslots, int row_stride) {
+// nbatch = activation vectors per launch (1, or 2 for the two-position prompt passes): planes, sums and reduction buffers double.
+__host__ __device__ inline MvSmem mv_smem_layout(int n_in, int planes, bool kquant, int nslots, int row_stride, int nbatch = 1) {
     MvSmem s;
     const int nb = n_in / QK_K;
     int o = 0;
@@ -142,16 +144,16 @@ __host__ __device__ inline MvSmem mv_smem_layout(int n_in, int planes, bool kqua
     o += (2 * MV_MAX_SLOTS + 2 * MV_RED_BUFS) * 8;
     o = (o + 15) & ~15;
     s.off_red = o;  // [MV_RED_BUFS][MV_MAX_CONSUMERS][16] f32 tile partials (also the block-sum scratch of the prologue)
-    o += MV_RED_BUFS * MV_MAX_CONSUMERS * 16 * 4;
+    o += MV_RED_BUFS * MV_MAX_CONSUMERS * 16 * 4 * nbatch;
     s.off_dpl = o;
     if (kquant) o += nb * 8 * 4;
     s.off_xs = o;
-    if (kquant) o += nb * 16 * 4;
+    if (kquant) o += nb * 16 * 4 * nbatch;
     o = (o + 127) & ~127;
     s.plane_stride = n_in;
     while ((s.plane_stride & 127) != 32) s.plane_stride += 16;  // planes 0..2 of a fragment load fall in distinct banks
     s.off_act = o;
-    if (kquant) o += planes * s.plane_stride;
+    if (kquant) o += planes * nbatch * s.plane_stride;
     o = (o + 15) & ~15;
     s.off_xf = o;
     if (!kquant) o += n_in * 4;
@@ -193,7 +195,7 @@ __device__ __forceinline__ float block_sum(float v, float* red, int warp, int la
 //   plane k: the residual of the planes before it, quantised with d_k = d_{k-1}/254.
 // Rounding to nearest-even uses the 1.5*2^23 trick: the low byte of the float's bits is the int8.
 // Not inlined: it is called from several places in the prologue.
-template <int P>
+template <int P, int ZHI = 8>  // columns P .. ZHI-1 of the block's scale row are zeroed (unused MMA columns)
 __device__ __noinline__ void quantise_block(float4 va, float4 vb, int lane, uint8_t* act, int plane_stride, float* dpl, float* xs16, int b) {
     const float v[8] = {va.x, va.y, va.z, va.w, vb.x, vb.y, vb.z, vb.w};
     float amax = 0.f;
@@ -202,7 +204,10 @@ __device__ __noinline__ void quantise_block(float4 va, float4 vb, int lane, uint
     amax = warp_max(amax);
     const float MAGIC = 12582912.f;
     float d = amax * (1.0f / 127.f);
+    // Inverse scales overflow for blocks whose largest value is below ~1e-32 (id grows by 254 per plane): such a plane is
+    // left empty (id = 0), which drops a residual of relative size 1e-5 or less of a block that is itself negligible.
     float id = amax > 0.f ? __fdividef(127.f, amax) : 0.f;
+    if (!(id < 3.0e38f)) id = 0.f;
     float r[8];
 #pragma unroll
     for (int e = 0; e < 8; ++e) r[e] = v[e];
@@ -221,8 +226,9 @@ __device__ __noinline__ void quantise_block(float4 va, float4 vb, int lane, uint
         if (lane == k) dpl[8 * b + k] = d;
         d *= (1.0f / 254.f);
         id *= 254.f;
+        if (!(id < 3.0e38f)) id = 0.f;
     }
-    if (lane >= P && lane < 8) dpl[8 * b + lane] = 0.f;  // unused MMA columns
+    if (lane >= P && lane < ZHI) dpl[8 * b + lane] = 0.f;  // unused MMA columns
     // sum of the represented values = x - final residual
     float s = 0.f;
 #pragma unroll
@@ -233,13 +239,11 @@ __device__ __noinline__ void quantise_block(float4 va, float4 vb, int lane, uint
 
 // Build the activation vector in shared memory.  KQ: int8 planes + sums; else f32 copy.
 // A warp takes 32 consecutive groups of 8 values (= one 256-value block) per turn.
-template <bool KQ, int P, bool TP = false>
-__device__ __forceinline__ void build_activation(const MvParams& p, uint8_t* smem, const MvSmem& L, int warp, int lane, int nwarps) {
+template <bool KQ, int P, bool TP = false, int ZHI = 8>
+__device__ __forceinline__ void build_activation(const MvParams& p, uint8_t* smem, const MvSmem& L, int warp, int lane, int nwarps, const float* x_in,
+                                                 uint8_t* act, float* dpl, float* xs16) {
     const int n = p.n_in;
     float* red = reinterpret_cast<float*>(smem + L.off_red);
-    uint8_t* act = smem + L.off_act;
-    float* dpl = reinterpret_cast<float*>(smem + L.off_dpl);
-    float* xs16 = reinterpret_cast<float*>(smem + L.off_xs);
     float* xf = reinterpret_cast<float*>(smem + L.off_xf);
     const int n8 = n / 8;
     const int turns = p.turns;
@@ -276,8 +280,8 @@ __device__ __forceinline__ void build_activation(const MvParams& p, uint8_t* sme
         const int g = group_of(turn);
         a = b = zero4;
         if (g < n8) {
-            a = __ldcg(reinterpret_cast<const float4*>(p.x_in + 8 * g));
-            b = __ldcg(reinterpret_cast<const float4*>(p.x_in + 8 * g + 4));
+            a = __ldcg(reinterpret_cast<const float4*>(x_in + 8 * g));
+            b = __ldcg(reinterpret_cast<const float4*>(x_in + 8 * g + 4));
             if (tp_sum) {
 #pragma unroll 1
                 for (int r = 0; r < tp_n; ++r) {  // rank order on every GPU: identical sums everywhere
@@ -297,7 +301,7 @@ __device__ __forceinline__ void build_activation(const MvParams& p, uint8_t* sme
     auto emit = [&](int turn, float4 a, float4 b) {
         const int g0 = 32 * (warp + nwarps * turn), g = g0 + lane;
         if (g0 >= n8) return;
-        if (KQ) quantise_block<P>(a, b, lane, act, L.plane_stride, dpl, xs16, g0 >> 5);
+        if (KQ) quantise_block<P, ZHI>(a, b, lane, act, L.plane_stride, dpl, xs16, g0 >> 5);
         else if (g < n8) {
             *reinterpret_cast<float4*>(xf + 8 * g) = a;
             *reinterpret_cast<float4*>(xf + 8 * g + 4) = b;
@@ -463,21 +467,25 @@ __device__ __forceinline__ void arg_update(ArgBest& b, float v, int i) {
 }
 
 template <bool TP = false>
-__device__ __forceinline__ void epilogue_pair(const MvParams& p, const MvSegment& sg, int t, float vA, float vB, int pos, ArgBest& best) {
+__device__ __forceinline__ void epilogue_pair(const MvParams& p, const MvSegment& sg, int t, float vA, float vB, int pos, ArgBest& best, int seq = 0) {
+    // seq = 1: the second position of a two-position launch (pos is already that position's; vectors sit out2 elements further)
     int rowA, rowB;
     pair_rows(p, sg, t, rowA, rowB);
+    float* const out = sg.out + (size_t)seq * sg.out2;
     switch (sg.epi) {
         case EPI_STORE:
-            sg.out[rowA] = vA;
-            sg.out[rowB] = vB;
+            out[rowA] = vA;
+            out[rowB] = vB;
             break;
-        case EPI_RESIDUAL:
-            sg.out[rowA] = __ldcg(p.resid + rowA) + vA;
-            sg.out[rowB] = __ldcg(p.resid + rowB) + vB;
+        case EPI_RESIDUAL: {
+            const float* resid = p.resid + (size_t)seq * sg.out2;
+            out[rowA] = __ldcg(resid + rowA) + vA;
+            out[rowB] = __ldcg(resid + rowB) + vB;
             break;
+        }
         case EPI_SWIGLU: {
             const float g = vA * (1.0f / (1.0f + expf(-vA)));
-            sg.out[t] = g * vB;
+            out[t] = g * vB;
             break;
         }
         case EPI_ROPE_Q:
@@ -490,10 +498,10 @@ __device__ __forceinline__ void epilogue_pair(const MvParams& p, const MvSegment
             const float oa = __fsub_rn(__fmul_rn(vA, cs.x), __fmul_rn(vB, cs.y));
             const float ob = __fadd_rn(__fmul_rn(vA, cs.y), __fmul_rn(vB, cs.x));
             if (sg.epi == EPI_ROPE_Q) {
-                sg.out[rowA] = oa;
-                sg.out[rowB] = ob;
+                out[rowA] = oa;
+                out[rowB] = ob;
             } else {  // key cache [kv_head][seq_len][hs]
-                float* dst = sg.out + ((size_t)head * p.seq_len + pos) * hs;
+                float* dst = out + ((size_t)head * p.seq_len + pos) * hs;
                 dst[rowA % hs] = oa;
                 dst[rowB % hs] = ob;
             }
@@ -501,14 +509,14 @@ __device__ __forceinline__ void epilogue_pair(const MvParams& p, const MvSegment
         }
         case EPI_STORE_V: {  // value cache [kv_head][seq_len][hs]
             const int hs = sg.head_size;
-            float* dst = sg.out + ((size_t)(rowA / hs) * p.seq_len + pos) * hs;
+            float* dst = out + ((size_t)(rowA / hs) * p.seq_len + pos) * hs;
             dst[rowA % hs] = vA;
             dst[rowB % hs] = vB;
             break;
         }
         case EPI_LOGITS:
-            sg.out[rowA] = vA;
-            sg.out[rowB] = vB;
+            out[rowA] = vA;
+            out[rowB] = vB;
             arg_update(best, vA, rowA);
             arg_update(best, vB, rowB);
             break;
@@ -529,13 +537,15 @@ __device__ __forceinline__ void epilogue_pair(const MvParams& p, const MvSegment
 // ---- the kernel --------------------------------------------------------------------------------
 // DBG = true compiles in the measurement aids (timeline stamps, skip-arithmetic / skip-copies switches); the production
 // instantiations carry none of them: even a predicated-off stamp in the producer's loop cost 2 % of a token.
-template <bool KQ, int P, bool TP = false, bool DBG = false>
+// NB = 2: two activation vectors (two consecutive prompt positions) per launch.  Their int8 planes occupy MMA columns
+// 0..2 and 4..6, so the weights are streamed and unpacked once for both positions at no extra MMA cost.
+template <bool KQ, int P, bool TP = false, bool DBG = false, int NB = 1>
 __global__ void __launch_bounds__((MV_MAX_CONSUMERS + 2) * 32, 1) fused_matvec_kernel(const __grid_constant__ MvParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int W = p.consumers;
     const int NS = p.nslots;
-    const MvSmem L = mv_smem_layout(p.n_in, P, KQ, KQ ? NS : 0, p.row_stride);
+    const MvSmem L = mv_smem_layout(p.n_in, P, KQ, KQ ? NS : 0, p.row_stride, NB);
     MV_TRACE(0);
 
     const int nb = p.n_in / QK_K;
@@ -716,15 +726,27 @@ __global__ void __launch_bounds__((MV_MAX_CONSUMERS + 2) * 32, 1) fused_matvec_k
                 dead = true;
                 break;
             }
-            const float* rbuf = red + rb * (MV_MAX_CONSUMERS * 16);
-            float v = 0.f;
-            for (int w = fq; w < WGf; w += 2) v += rbuf[w * 16 + fidx];
+            const float* rbuf = red + rb * (MV_MAX_CONSUMERS * 16 * NB);
+            float v = 0.f, v1 = 0.f;
+            if (NB == 1) {
+                for (int w = fq; w < WGf; w += 2) v += rbuf[w * 16 + fidx];
+            } else {
+                for (int w = fq; w < WGf; w += 2) {
+                    v += rbuf[(w * 2) * 16 + fidx];
+                    v1 += rbuf[(w * 2 + 1) * 16 + fidx];
+                }
+            }
             __syncwarp();
             if (lane == 0) mbar_arrive(red_empty + rb);  // the buffer may be rewritten
             v += __shfl_xor_sync(0xffffffffu, v, 16);     // (even warps) + (odd warps)
             const float vB = __shfl_sync(0xffffffffu, v, (lane & 7) + 8);
             const int t = (unit - seg_first) * MV_TILE_PAIRS + lane;
             if (lane < MV_TILE_PAIRS && t < sg.npairs) epilogue_pair<TP>(p, sg, t, v, vB, pos, best);
+            if (NB == 2) {  // the second position
+                v1 += __shfl_xor_sync(0xffffffffu, v1, 16);
+                const float v1B = __shfl_sync(0xffffffffu, v1, (lane & 7) + 8);
+                if (lane < MV_TILE_PAIRS && t < sg.npairs) epilogue_pair<TP>(p, sg, t, v1, v1B, pos + 1, best, 1);
+            }
             if (++rb == MV_RED_BUFS) {
                 rb = 0;
                 par ^= 1u;
@@ -756,7 +778,17 @@ __global__ void __launch_bounds__((MV_MAX_CONSUMERS + 2) * 32, 1) fused_matvec_k
     pdl_wait();
     MV_TRACE(2);
 
-    build_activation<KQ, P, TP>(p, smem, L, warp, lane, W);
+    {
+        uint8_t* act = smem + L.off_act;
+        float* dpl = reinterpret_cast<float*>(smem + L.off_dpl);
+        float* xs16 = reinterpret_cast<float*>(smem + L.off_xs);
+        if (NB == 1) {
+            build_activation<KQ, P, TP>(p, smem, L, warp, lane, W, p.x_in, act, dpl, xs16);
+        } else {  // vector s: planes s*P .., scale columns 4s .., its own sums
+            build_activation<KQ, P, TP, 4>(p, smem, L, warp, lane, W, p.x_in, act, dpl, xs16);
+            build_activation<KQ, P, TP, 4>(p, smem, L, warp, lane, W, p.x_in + p.n_in, act + P * L.plane_stride, dpl + 4, xs16 + (p.n_in / QK_K) * 16);
+        }
+    }
     MV_TRACE(3);
 
     const int pos = p.pos ? __ldcg(p.pos) : 0;
@@ -773,6 +805,13 @@ __global__ void __launch_bounds__((MV_MAX_CONSUMERS + 2) * 32, 1) fused_matvec_k
         cx.g = lane >> 2;
         cx.t = lane & 3;
         cx.colv = cx.g < P;
+        if (NB == 2) {
+            // MMA column g carries plane g & 3 of vector g >> 2; lanes t = 0, 1 collect vector 0, lanes t = 2, 3 vector 1
+            const int pl = (cx.g >> 2) * P + (cx.g & 3);
+            cx.colv = (cx.g & 3) < P;
+            cx.act = smem + L.off_act + (pl - cx.g) * L.plane_stride;  // the tile functions add g * plane_stride
+            cx.xs16 = reinterpret_cast<const float*>(smem + L.off_xs) + (cx.t >> 1) * (p.n_in / QK_K) * 16;
+        }
         const int pj = ((cx.g & 3) << 1) | (cx.g >> 2);  // the pair of the tile this lane group works on: (0,2,4,6,1,3,5,7)[g]
         float* red = reinterpret_cast<float*>(smem + L.off_red);
         bool dead = false;
@@ -826,14 +865,14 @@ __global__ void __launch_bounds__((MV_MAX_CONSUMERS + 2) * 32, 1) fused_matvec_k
                     for (int bl = wl; bl < nblk; bl += WG) {
                         const uint8_t* rA = slot + oA + bl * bb;
                         const uint8_t* rB = slot + oB + bl * bb;
-                        if (sg.type == T_Q4_K) tile_q4k(rA, rB, b0 + bl, cx, accA, accB);
-                        else if (sg.type == T_Q5_K) tile_q5k(rA, rB, b0 + bl, cx, accA, accB);
+                        if (sg.type == T_Q4_K) tile_q4k<NB>(rA, rB, b0 + bl, cx, accA, accB);
+                        else if (sg.type == T_Q5_K) tile_q5k<NB>(rA, rB, b0 + bl, cx, accA, accB);
                         else {
                             if (bl != wl) {  // a second column for this warp (fewer warps than columns)
                                 dA = __half2float(__ldg(d6A + b0 + bl));
                                 dB = __half2float(__ldg(d6B + b0 + bl));
                             }
-                            tile_q6k(rA, rB, dA, dB, b0 + bl, cx, accA, accB);
+                            tile_q6k<NB>(rA, rB, dA, dB, b0 + bl, cx, accA, accB);
                         }
                     }
                 }
@@ -848,13 +887,20 @@ __global__ void __launch_bounds__((MV_MAX_CONSUMERS + 2) * 32, 1) fused_matvec_k
             // warp through one of MV_RED_BUFS buffers (full/empty mbarriers, like the weight ring).
             accA += __shfl_xor_sync(0xffffffffu, accA, 1);
             accB += __shfl_xor_sync(0xffffffffu, accB, 1);
-            accA += __shfl_xor_sync(0xffffffffu, accA, 2);
-            accB += __shfl_xor_sync(0xffffffffu, accB, 2);
+            if (NB == 1) {
+                accA += __shfl_xor_sync(0xffffffffu, accA, 2);
+                accB += __shfl_xor_sync(0xffffffffu, accB, 2);
+            }
             if (red_wrap > 0 && !dead && !mbar_wait_bounded(red_empty + rb, (uint32_t)((red_wrap & 1) ^ 1))) dead = true;
-            float* rbuf = red + rb * (MV_MAX_CONSUMERS * 16);
-            if (cx.t == 0) {
-                rbuf[wl * 16 + pj] = accA;
-                rbuf[wl * 16 + 8 + pj] = accB;
+            float* rbuf = red + rb * (MV_MAX_CONSUMERS * 16 * NB);
+            if (NB == 1) {
+                if (cx.t == 0) {
+                    rbuf[wl * 16 + pj] = accA;
+                    rbuf[wl * 16 + 8 + pj] = accB;
+                }
+            } else if ((cx.t & 1) == 0) {  // t = 0 holds vector 0's sums, t = 2 vector 1's
+                rbuf[(wl * 2 + (cx.t >> 1)) * 16 + pj] = accA;
+                rbuf[(wl * 2 + (cx.t >> 1)) * 16 + 8 + pj] = accB;
             }
             __syncwarp();
             if (lane == 0 && !dead) mbar_arrive(red_full + rb);

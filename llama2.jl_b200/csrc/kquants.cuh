@@ -115,7 +115,20 @@ __device__ __forceinline__ float min_term_lane(uint64_t m8, const float* xs16b, 
     return fmaf((float)byte64(m8, 2 * t), v.x + v.y, (float)byte64(m8, 2 * t + 1) * (v.z + v.w));
 }
 
+// Two activation vectors per launch (NB = 2): lanes t = 0, 1 work for the first vector, t = 2, 3 for the second, so a
+// lane covers half of the block's sub-blocks: 4h .. 4h+3 with h = t & 1 (xs16b already points at the lane's vector).
+__device__ __forceinline__ float min_term_half(uint64_t m8, const float* xs16b, int h) {
+    const float4 v0 = *reinterpret_cast<const float4*>(xs16b + 8 * h);
+    const float4 v1 = *reinterpret_cast<const float4*>(xs16b + 8 * h + 4);
+    float r = (float)byte64(m8, 4 * h) * (v0.x + v0.y);
+    r = fmaf((float)byte64(m8, 4 * h + 1), v0.z + v0.w, r);
+    r = fmaf((float)byte64(m8, 4 * h + 2), v1.x + v1.y, r);
+    r = fmaf((float)byte64(m8, 4 * h + 3), v1.z + v1.w, r);
+    return r;
+}
+
 // q4_K: rA, rB = this block of rows g and g+8 (144-byte blocks); b = block index along the row.
+template <int NB = 1>
 __device__ __forceinline__ void tile_q4k(const uint8_t* rA, const uint8_t* rB, int b, const TileCtx& x, float& accA, float& accB) {
     const uint4 hA = *reinterpret_cast<const uint4*>(rA);
     const uint4 hB = *reinterpret_cast<const uint4*>(rB);
@@ -148,11 +161,17 @@ __device__ __forceinline__ void tile_q4k(const uint8_t* rA, const uint8_t* rB, i
     const float fB = fmaf(dp.x, (float)S[2], dp.y * (float)S[3]);
     const float dA = half_bits_to_float(hA.x & 0xFFFFu), dminA = half_bits_to_float(hA.x >> 16);
     const float dB = half_bits_to_float(hB.x & 0xFFFFu), dminB = half_bits_to_float(hB.x >> 16);
-    accA += dA * 0.0625f * fA - dminA * min_term_lane(mA, x.xs16 + 16 * b, x.t);
-    accB += dB * 0.0625f * fB - dminB * min_term_lane(mB, x.xs16 + 16 * b, x.t);
+    if (NB == 1) {
+        accA += dA * 0.0625f * fA - dminA * min_term_lane(mA, x.xs16 + 16 * b, x.t);
+        accB += dB * 0.0625f * fB - dminB * min_term_lane(mB, x.xs16 + 16 * b, x.t);
+    } else {
+        accA += dA * 0.0625f * fA - dminA * min_term_half(mA, x.xs16 + 16 * b, x.t & 1);
+        accB += dB * 0.0625f * fB - dminB * min_term_half(mB, x.xs16 + 16 * b, x.t & 1);
+    }
 }
 
 // q5_K: 176-byte blocks: header 16 | qh 32 | qs 128.
+template <int NB = 1>
 __device__ __forceinline__ void tile_q5k(const uint8_t* rA, const uint8_t* rB, int b, const TileCtx& x, float& accA, float& accB) {
     const uint4 hA = *reinterpret_cast<const uint4*>(rA);
     const uint4 hB = *reinterpret_cast<const uint4*>(rB);
@@ -190,13 +209,19 @@ __device__ __forceinline__ void tile_q5k(const uint8_t* rA, const uint8_t* rB, i
     const float fB = fmaf(dp.x, (float)S[2], dp.y * (float)S[3]);
     const float dA = half_bits_to_float(hA.x & 0xFFFFu), dminA = half_bits_to_float(hA.x >> 16);
     const float dB = half_bits_to_float(hB.x & 0xFFFFu), dminB = half_bits_to_float(hB.x >> 16);
-    accA += dA * fA - dminA * min_term_lane(mA, x.xs16 + 16 * b, x.t);
-    accB += dB * fB - dminB * min_term_lane(mB, x.xs16 + 16 * b, x.t);
+    if (NB == 1) {
+        accA += dA * fA - dminA * min_term_lane(mA, x.xs16 + 16 * b, x.t);
+        accB += dB * fB - dminB * min_term_lane(mB, x.xs16 + 16 * b, x.t);
+    } else {
+        accA += dA * fA - dminA * min_term_half(mA, x.xs16 + 16 * b, x.t & 1);
+        accB += dB * fB - dminB * min_term_half(mB, x.xs16 + 16 * b, x.t & 1);
+    }
 }
 
 // q6_K: 208-byte records (ql[128] qh[64] scales[16]); dA, dB = the blocks' fp16 scales.  Scales cover 16 values,
 // so the products run on m16n8k16.  Quants stay unsigned 0..63; the -32 offset becomes -32 * scale * (sum of
 // the activations of the group).  Lane t takes values l = 16c + 4t .. 16c + 4t + 3 of every group.
+template <int NB = 1>
 __device__ __forceinline__ void tile_q6k(const uint8_t* rA, const uint8_t* rB, float dA, float dB, int b, const TileCtx& x, float& accA, float& accB) {
     const uint4 sA4 = *reinterpret_cast<const uint4*>(rA + 192);
     const uint4 sB4 = *reinterpret_cast<const uint4*>(rB + 192);
@@ -233,16 +258,33 @@ __device__ __forceinline__ void tile_q6k(const uint8_t* rA, const uint8_t* rB, f
     const float2 dp = *reinterpret_cast<const float2*>(x.dpl + 8 * b + 2 * x.t);
     const float fA = fmaf(dp.x, (float)S[0], dp.y * (float)S[1]);
     const float fB = fmaf(dp.x, (float)S[2], dp.y * (float)S[3]);
-    // offset term, this lane's four groups 4t..4t+3 (scale word t, selected without indexing the array dynamically)
-    const float4 v = *reinterpret_cast<const float4*>(x.xs16 + 16 * b + 4 * x.t);
-    const float vv[4] = {v.x, v.y, v.z, v.w};
-    const uint32_t wA = (x.t & 2) ? ((x.t & 1) ? sA4.w : sA4.z) : ((x.t & 1) ? sA4.y : sA4.x);
-    const uint32_t wB = (x.t & 2) ? ((x.t & 1) ? sB4.w : sB4.z) : ((x.t & 1) ? sB4.y : sB4.x);
     float tA = 0.f, tB = 0.f;
+    if (NB == 1) {
+        // offset term, this lane's four groups 4t..4t+3 (scale word t, selected without indexing the array dynamically)
+        const float4 v = *reinterpret_cast<const float4*>(x.xs16 + 16 * b + 4 * x.t);
+        const float vv[4] = {v.x, v.y, v.z, v.w};
+        const uint32_t wA = (x.t & 2) ? ((x.t & 1) ? sA4.w : sA4.z) : ((x.t & 1) ? sA4.y : sA4.x);
+        const uint32_t wB = (x.t & 2) ? ((x.t & 1) ? sB4.w : sB4.z) : ((x.t & 1) ? sB4.y : sB4.x);
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-        tA = fmaf((float)(((int)(wA << (24 - 8 * j))) >> 24), vv[j], tA);
-        tB = fmaf((float)(((int)(wB << (24 - 8 * j))) >> 24), vv[j], tB);
+        for (int j = 0; j < 4; ++j) {
+            tA = fmaf((float)(((int)(wA << (24 - 8 * j))) >> 24), vv[j], tA);
+            tB = fmaf((float)(((int)(wB << (24 - 8 * j))) >> 24), vv[j], tB);
+        }
+    } else {
+        // two vectors per launch: lane half h = t & 1 takes groups 8h..8h+7 (scale words 2h, 2h+1) of its own vector
+        const int h = x.t & 1;
+        const float4 v0 = *reinterpret_cast<const float4*>(x.xs16 + 16 * b + 8 * h);
+        const float4 v1 = *reinterpret_cast<const float4*>(x.xs16 + 16 * b + 8 * h + 4);
+        const float vv[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+        const uint32_t wA0 = h ? sA4.z : sA4.x, wA1 = h ? sA4.w : sA4.y;
+        const uint32_t wB0 = h ? sB4.z : sB4.x, wB1 = h ? sB4.w : sB4.y;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            tA = fmaf((float)(((int)(wA0 << (24 - 8 * j))) >> 24), vv[j], tA);
+            tB = fmaf((float)(((int)(wB0 << (24 - 8 * j))) >> 24), vv[j], tB);
+            tA = fmaf((float)(((int)(wA1 << (24 - 8 * j))) >> 24), vv[4 + j], tA);
+            tB = fmaf((float)(((int)(wB1 << (24 - 8 * j))) >> 24), vv[4 + j], tB);
+        }
     }
     accA += dA * (fA - 32.f * tA);
     accB += dB * (fB - 32.f * tB);

@@ -145,6 +145,34 @@ __global__ void __launch_bounds__(FIN_THREADS) finalize_token_kernel(const __gri
     }
 }
 
+// End of a two-position prompt pass (positions pos and pos + 1, both followed by a prompt token): nothing is sampled,
+// the loop state moves on by two positions.
+struct AdvanceParams {
+    Control* ctl;
+    const int* prompt;
+    int* out_tokens;
+    unsigned* epoch;
+};
+__global__ void advance_pair_kernel(const __grid_constant__ AdvanceParams a) {
+    Control* ctl = a.ctl;
+    const int* prompt = a.prompt;
+    int* out_tokens = a.out_tokens;
+    unsigned* epoch = a.epoch;
+    pdl_launch_dependents();
+    pdl_wait();
+    if (threadIdx.x == 0) {
+        const int pos = ctl->pos;
+        const int t1 = prompt[pos + 1], t2 = prompt[pos + 2];
+        if (out_tokens) {
+            out_tokens[pos] = t1;
+            out_tokens[pos + 1] = t2;
+        }
+        ctl->token = t2;
+        ctl->pos = pos + 2;
+        if (epoch) *epoch += 1u;
+    }
+}
+
 // argmax over a plain vector (isolated-operator entry point): one block.
 __global__ void __launch_bounds__(FIN_THREADS) argmax_kernel(const float* x, int n, float* out_val, int* out_idx) {
     __shared__ float s_val[32];

@@ -52,10 +52,12 @@ __global__ void dequantize_kernel(int type, const uint8_t* __restrict__ blocks, 
 
 // x = dequantize!(x, token_embedding_table[:, token]) (src/inference.jl:236): the first kernel of a token.
 // `token` is a device scalar.  For f32 tables the row is copied.
-__global__ void embed_row_kernel(int type, const uint8_t* __restrict__ table, const __half* __restrict__ d6, const int* token, int n, float* __restrict__ x) {
+// `prompt` non-null: the row of the NEXT prompt token, prompt[*pos + 1] (second position of a two-position pass).
+__global__ void embed_row_kernel(int type, const uint8_t* __restrict__ table, const __half* __restrict__ d6, const int* token, int n, float* __restrict__ x,
+                                 const int* prompt, const int* pos) {
     pdl_launch_dependents();
     pdl_wait();
-    const int tok = __ldcg(token);
+    const int tok = prompt ? __ldcg(prompt + __ldcg(pos) + 1) : __ldcg(token);
     const int nb = n / QK_K;
     for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
         float v;
@@ -80,7 +82,8 @@ __global__ void __launch_bounds__(256) export_activation_kernel(const __grid_con
     extern __shared__ __align__(128) uint8_t smem[];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
     const MvSmem L = mv_smem_layout(p.n_in, P, KQ, 0, 0);
-    build_activation<KQ, P>(p, smem, L, warp, lane, nwarps);
+    build_activation<KQ, P>(p, smem, L, warp, lane, nwarps, p.x_in, smem + L.off_act, reinterpret_cast<float*>(smem + L.off_dpl),
+                            reinterpret_cast<float*>(smem + L.off_xs));
     const int n = p.n_in, nb = n / QK_K;
     if (KQ) {
         for (int i = threadIdx.x; i < P * n; i += blockDim.x) {

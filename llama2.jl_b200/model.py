@@ -201,6 +201,12 @@ class LanguageModel:
         L.check(L.lib().l2b_session_kernels_per_token(self.device_model().session, C.byref(n)))
         return n.value
 
+    def prefill_pairs(self) -> bool:
+        """True when `generate` feeds prompts two positions per pass over the weights."""
+        n = C.c_int32()
+        L.check(L.lib().l2b_session_prefill_pairs(self.device_model().session, C.byref(n)))
+        return bool(n.value)
+
     def last_device_ms(self) -> float:
         ms = C.c_float()
         L.check(L.lib().l2b_session_last_device_ms(self.device_model().session, C.byref(ms)))

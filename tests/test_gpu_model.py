@@ -149,3 +149,40 @@ def test_native_gguf_loader_matches_python_loader(pkg, synth, tmp_path, arch):
     assert np.array_equal(sa.logits.view(np.uint32), sb.logits.view(np.uint32))
     a.close()
     b.close()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("shape", ["gqa4_interleaved", "mha_neox_q6"])
+def test_two_position_prompt_passes_match_one_position_passes(pkg, synth, orc, shape):
+    """l2b_generate feeds the prompt two positions per pass (weights streamed once for both).  The stream it produces, the
+    KV cache it leaves behind and the logits that follow must agree with the one-position path and with the oracle."""
+    if shape == "gqa4_interleaved":
+        cfg = pkg.ModelConfig(512, 1024, 3, 8, 2, 512, 64, 10000.0, False)
+        types = dict(synth.ALL(12), wv=13, w2=13, output=14)
+    else:  # NeoX pairs, every head its own kv head, q6_K layer matrices as in *_K_M files
+        cfg = pkg.ModelConfig(768, 1536, 2, 8, 8, 512, 64, 10000.0, True)
+        types = dict(synth.ALL(13), wv=14, w2=14, output=14)
+    w = synth.model_weights(cfg, types, seed=21)
+    prompt = synth.tokens(21, 9, 3, cfg.vocab_size)  # odd length: pairs (0,1) .. (18,19), then 20 alone
+    n_pos = 40
+    os.environ["L2B_PREFILL_PAIRS"] = "0"
+    try:
+        single = pkg.LanguageModel(cfg, None, w)
+        t1, _ = pkg.generate(single, prompt, n_pos)
+    finally:
+        del os.environ["L2B_PREFILL_PAIRS"]
+    paired = pkg.LanguageModel(cfg, None, w)
+    t2, _ = pkg.generate(paired, prompt, n_pos)
+    assert np.array_equal(t1, t2)
+    want = orc.OracleModel(cfg, w).sample_greedy(prompt, n_pos)
+    assert np.array_equal(t2, np.asarray(want, dtype=np.int32))
+    # logits at the next position, computed on the caches the two paths filled
+    import ctypes as C
+    from llama2_jl_b200 import _lib as L
+    la, lb = np.zeros(cfg.vocab_size, np.float32), np.zeros(cfg.vocab_size, np.float32)
+    L.check(L.lib().l2b_forward(single.device_model().session, int(t1[-1]), n_pos, L.ptr(la)))
+    L.check(L.lib().l2b_forward(paired.device_model().session, int(t2[-1]), n_pos, L.ptr(lb)))
+    rng = float(la.max() - la.min())
+    assert np.abs(la - lb).max() / rng < 1e-5
+    single.close()
+    paired.close()

@@ -221,3 +221,22 @@ def test_swiglu_argmax_sampling(L, orc):
             want = orc.sample_temperature(logits, temperature, u)[0]
             # the index whose cumulative-probability interval holds u, up to rounding of the running sum
             assert idx.value == want or abs(cdf[idx.value] - cdf[want]) < 1e-6
+
+
+@pytest.mark.parametrize("name", ["q4_K", "q5_K", "q6_K"])
+def test_matvec_activation_blocks_of_tiny_values(pkg, orc, synth, name):
+    """Blocks whose largest activation is tiny (down to denormals) beside blocks of ordinary size: the per-plane inverse
+    scales of such a block overflow f32 and must not turn the result into NaN (SwiGLU outputs look like this when the
+    gate saturates)."""
+    t = {"q4_K": 12, "q5_K": 13, "q6_K": 14}[name]
+    n_in, n_out = 1536, 64
+    A = synth.matrix(t, n_in, n_out, seed=5)
+    x = synth.normal_f32(n_in, 6, 1.0)
+    for b, scale in enumerate([1.0, 1e-30, 4e-33, 1e-36, 1e-39, 0.0]):
+        x[256 * b:256 * (b + 1)] *= np.float32(scale)
+    x[256 + 7] = 0.0
+    y = np.zeros(n_out, np.float32)
+    pkg.matmul_(y, A, x)
+    want = orc.matmul_f64(A, x)
+    assert np.isfinite(y).all()
+    assert np.abs(y - want).max() <= 4e-6 * np.abs(want).max()
