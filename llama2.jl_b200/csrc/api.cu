@@ -345,6 +345,12 @@ static MvSegment make_segment(const DevMatrix& m, int pair_mode, int epi, float*
 
 static cudaError_t launch_attention(const AttnParams& a, int gq, cudaStream_t st, bool pdl) {
     const dim3 grid((a.n_heads / gq) * a.nsplit * (a.nq > 1 ? a.nq : 1)), block(ATTN_WARPS * 32);
+    if (a.nq > 1) switch (gq) {
+            case 8: return launch_kernel(attention_split_kernel<8, 2>, grid, block, 0, st, pdl, a);
+            case 4: return launch_kernel(attention_split_kernel<4, 2>, grid, block, 0, st, pdl, a);
+            case 2: return launch_kernel(attention_split_kernel<2, 2>, grid, block, 0, st, pdl, a);
+            default: return launch_kernel(attention_split_kernel<1, 2>, grid, block, 0, st, pdl, a);
+        }
     switch (gq) {
         case 8: return launch_kernel(attention_split_kernel<8>, grid, block, 0, st, pdl, a);
         case 4: return launch_kernel(attention_split_kernel<4>, grid, block, 0, st, pdl, a);

@@ -38,12 +38,12 @@ constexpr int ATTN_WARPS = 4;
 constexpr int ATTN_UNROLL = 4;      // positions whose key/value loads a warp keeps in flight
 constexpr int ATTN_MIN_CHUNK = 16;  // positions per split below which splitting costs more than it saves
 
-template <int GQ>  // query heads served per block; GQ divides n_heads / n_kv
+template <int GQ, int NQ = 1>  // GQ: query heads served per block (divides n_heads / n_kv); NQ: query positions per launch
 __device__ __forceinline__ void attention_split_body(const AttnParams& p) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     // with two query positions the grid holds two copies of the (head group, split) blocks: copy qi serves position pos + qi
     const int ngroups = p.n_heads / GQ;
-    const int qi = (p.nq > 1) ? (int)blockIdx.x / (ngroups * p.nsplit) : 0;
+    const int qi = (NQ > 1) ? (int)blockIdx.x / (ngroups * p.nsplit) : 0;  // NQ = 1: everything below folds to the one-position code
     const int bx = (int)blockIdx.x - qi * ngroups * p.nsplit;
     const int hg = bx / p.nsplit, sp = bx % p.nsplit;
     const int kvh = (hg * GQ) / (p.n_heads / p.n_kv);
@@ -200,11 +200,11 @@ __device__ __forceinline__ void attention_split_body(const AttnParams& p) {
     }
 }
 
-template <int GQ>
+template <int GQ, int NQ = 1>
 __global__ void __launch_bounds__(ATTN_WARPS * 32) attention_split_kernel(const __grid_constant__ AttnParams p) {
     pdl_launch_dependents();
     pdl_wait();
-    attention_split_body<GQ>(p);
+    attention_split_body<GQ, NQ>(p);
 }
 
 }  // namespace l2b
