@@ -466,8 +466,33 @@ __device__ __forceinline__ void arg_update(ArgBest& b, float v, int i) {
     }
 }
 
-template <bool TP = false>
-__device__ __forceinline__ void epilogue_pair(const MvParams& p, const MvSegment& sg, int t, float vA, float vB, int pos, ArgBest& best, int seq = 0) {
+// Operands of an epilogue that come from global memory (the residual values, the RoPE factors).  The finisher warp
+// loads them BEFORE it waits for a tile's sums, so that their latency is not added to the tail of the kernel.
+struct EpiPre {
+    float rA, rB;   // EPI_RESIDUAL: resid[rowA], resid[rowB]
+    float2 cs;      // EPI_ROPE_*: (cos, sin)
+};
+__device__ __forceinline__ EpiPre epilogue_preload(const MvParams& p, const MvSegment& sg, int t, int pos, int seq = 0) {
+    EpiPre e;
+    e.rA = e.rB = 0.f;
+    e.cs = make_float2(0.f, 0.f);
+    int rowA, rowB;
+    pair_rows(p, sg, t, rowA, rowB);
+    if (sg.epi == EPI_RESIDUAL) {
+        const float* resid = p.resid + (size_t)seq * sg.out2;
+        e.rA = __ldcg(resid + rowA);
+        e.rB = __ldcg(resid + rowB);
+    } else if (sg.epi == EPI_ROPE_Q || sg.epi == EPI_ROPE_K) {
+        const int hs = sg.head_size, h2 = hs >> 1;
+        const int i = (sg.pair_mode == PAIR_NEOX) ? (rowA % hs) : ((rowA % hs) >> 1);
+        e.cs = __ldg(reinterpret_cast<const float2*>(p.rope_cs) + (size_t)pos * h2 + i);
+    }
+    return e;
+}
+
+template <bool TP = false, bool PRE = false>
+__device__ __forceinline__ void epilogue_pair(const MvParams& p, const MvSegment& sg, int t, float vA, float vB, int pos, ArgBest& best, int seq = 0,
+                                              const EpiPre* pre = nullptr) {
     // seq = 1: the second position of a two-position launch (pos is already that position's; vectors sit out2 elements further)
     int rowA, rowB;
     pair_rows(p, sg, t, rowA, rowB);
@@ -478,9 +503,14 @@ __device__ __forceinline__ void epilogue_pair(const MvParams& p, const MvSegment
             out[rowB] = vB;
             break;
         case EPI_RESIDUAL: {
-            const float* resid = p.resid + (size_t)seq * sg.out2;
-            out[rowA] = __ldcg(resid + rowA) + vA;
-            out[rowB] = __ldcg(resid + rowB) + vB;
+            if (PRE) {
+                out[rowA] = pre->rA + vA;
+                out[rowB] = pre->rB + vB;
+            } else {
+                const float* resid = p.resid + (size_t)seq * sg.out2;
+                out[rowA] = __ldcg(resid + rowA) + vA;
+                out[rowB] = __ldcg(resid + rowB) + vB;
+            }
             break;
         }
         case EPI_SWIGLU: {
@@ -493,7 +523,7 @@ __device__ __forceinline__ void epilogue_pair(const MvParams& p, const MvSegment
             const int hs = sg.head_size, h2 = hs >> 1;
             const int head = rowA / hs;
             const int i = (sg.pair_mode == PAIR_NEOX) ? (rowA % hs) : ((rowA % hs) >> 1);
-            const float2 cs = __ldg(reinterpret_cast<const float2*>(p.rope_cs) + (size_t)pos * h2 + i);
+            const float2 cs = PRE ? pre->cs : __ldg(reinterpret_cast<const float2*>(p.rope_cs) + (size_t)pos * h2 + i);
             // (a + bi)(c + si): every product and sum rounded on its own, as the reference's complex multiply
             const float oa = __fsub_rn(__fmul_rn(vA, cs.x), __fmul_rn(vB, cs.y));
             const float ob = __fadd_rn(__fmul_rn(vA, cs.y), __fmul_rn(vB, cs.x));
@@ -722,6 +752,14 @@ __global__ void __launch_bounds__((MV_MAX_CONSUMERS + 2) * 32, 1) fused_matvec_k
                 seg_first = (seg_i == 0) ? 0 : (seg_i == 1 ? p.seg_start[1] : p.seg_start[2]);
                 seg_end = (seg_i == 0) ? p.seg_start[1] : (seg_i == 1 ? p.seg_start[2] : p.seg_start[3]);
             }
+            // what the epilogue needs from global memory is fetched while the consumers are still at work on the tile
+            const int t = (unit - seg_first) * MV_TILE_PAIRS + lane;
+            const bool mine = lane < MV_TILE_PAIRS && t < sg.npairs;
+            EpiPre pre0, pre1;
+            if (mine) {
+                pre0 = epilogue_preload(p, sg, t, pos);
+                if (NB == 2) pre1 = epilogue_preload(p, sg, t, pos + 1, 1);
+            }
             if (!mbar_wait_bounded(red_full + rb, par)) {
                 dead = true;
                 break;
@@ -740,12 +778,11 @@ __global__ void __launch_bounds__((MV_MAX_CONSUMERS + 2) * 32, 1) fused_matvec_k
             if (lane == 0) mbar_arrive(red_empty + rb);  // the buffer may be rewritten
             v += __shfl_xor_sync(0xffffffffu, v, 16);     // (even warps) + (odd warps)
             const float vB = __shfl_sync(0xffffffffu, v, (lane & 7) + 8);
-            const int t = (unit - seg_first) * MV_TILE_PAIRS + lane;
-            if (lane < MV_TILE_PAIRS && t < sg.npairs) epilogue_pair<TP>(p, sg, t, v, vB, pos, best);
+            if (mine) epilogue_pair<TP, true>(p, sg, t, v, vB, pos, best, 0, &pre0);
             if (NB == 2) {  // the second position
                 v1 += __shfl_xor_sync(0xffffffffu, v1, 16);
                 const float v1B = __shfl_sync(0xffffffffu, v1, (lane & 7) + 8);
-                if (lane < MV_TILE_PAIRS && t < sg.npairs) epilogue_pair<TP>(p, sg, t, v1, v1B, pos + 1, best, 1);
+                if (mine) epilogue_pair<TP, true>(p, sg, t, v1, v1B, pos + 1, best, 1, &pre1);
             }
             if (++rb == MV_RED_BUFS) {
                 rb = 0;
