@@ -469,23 +469,31 @@ __device__ __forceinline__ void arg_update(ArgBest& b, float v, int i) {
 // Operands of an epilogue that come from global memory (the residual values, the RoPE factors).  The finisher warp
 // loads them BEFORE it waits for a tile's sums, so that their latency is not added to the tail of the kernel.
 struct EpiPre {
-    float rA, rB;   // EPI_RESIDUAL: resid[rowA], resid[rowB]
-    float2 cs;      // EPI_ROPE_*: (cos, sin)
+    int rowA, rowB;   // the pair's matrix rows
+    float rA, rB;     // EPI_RESIDUAL: resid[rowA], resid[rowB]
+    float2 cs;        // EPI_ROPE_*: (cos, sin)
+    size_t dA, dB;    // cache epilogues: element offsets of the two destinations (the divisions by head_size are done here)
 };
 __device__ __forceinline__ EpiPre epilogue_preload(const MvParams& p, const MvSegment& sg, int t, int pos, int seq = 0) {
     EpiPre e;
     e.rA = e.rB = 0.f;
     e.cs = make_float2(0.f, 0.f);
-    int rowA, rowB;
-    pair_rows(p, sg, t, rowA, rowB);
+    e.dA = e.dB = 0;
+    pair_rows(p, sg, t, e.rowA, e.rowB);
     if (sg.epi == EPI_RESIDUAL) {
         const float* resid = p.resid + (size_t)seq * sg.out2;
-        e.rA = __ldcg(resid + rowA);
-        e.rB = __ldcg(resid + rowB);
-    } else if (sg.epi == EPI_ROPE_Q || sg.epi == EPI_ROPE_K) {
+        e.rA = __ldcg(resid + e.rowA);
+        e.rB = __ldcg(resid + e.rowB);
+    } else if (sg.epi == EPI_ROPE_Q || sg.epi == EPI_ROPE_K || sg.epi == EPI_STORE_V) {
         const int hs = sg.head_size, h2 = hs >> 1;
-        const int i = (sg.pair_mode == PAIR_NEOX) ? (rowA % hs) : ((rowA % hs) >> 1);
-        e.cs = __ldg(reinterpret_cast<const float2*>(p.rope_cs) + (size_t)pos * h2 + i);
+        const int head = e.rowA / hs, inA = e.rowA - head * hs, inB = e.rowB - head * hs;  // both rows lie in one head
+        if (sg.epi != EPI_STORE_V) {
+            const int i = (sg.pair_mode == PAIR_NEOX) ? inA : (inA >> 1);
+            e.cs = __ldg(reinterpret_cast<const float2*>(p.rope_cs) + (size_t)pos * h2 + i);
+        }
+        const size_t base = ((size_t)head * p.seq_len + pos) * hs;  // cache layout [kv_head][seq_len][hs]
+        e.dA = base + inA;
+        e.dB = base + inB;
     }
     return e;
 }
@@ -495,7 +503,12 @@ __device__ __forceinline__ void epilogue_pair(const MvParams& p, const MvSegment
                                               const EpiPre* pre = nullptr) {
     // seq = 1: the second position of a two-position launch (pos is already that position's; vectors sit out2 elements further)
     int rowA, rowB;
-    pair_rows(p, sg, t, rowA, rowB);
+    if (PRE) {
+        rowA = pre->rowA;
+        rowB = pre->rowB;
+    } else {
+        pair_rows(p, sg, t, rowA, rowB);
+    }
     float* const out = sg.out + (size_t)seq * sg.out2;
     switch (sg.epi) {
         case EPI_STORE:
@@ -520,28 +533,41 @@ __device__ __forceinline__ void epilogue_pair(const MvParams& p, const MvSegment
         }
         case EPI_ROPE_Q:
         case EPI_ROPE_K: {
-            const int hs = sg.head_size, h2 = hs >> 1;
-            const int head = rowA / hs;
-            const int i = (sg.pair_mode == PAIR_NEOX) ? (rowA % hs) : ((rowA % hs) >> 1);
-            const float2 cs = PRE ? pre->cs : __ldg(reinterpret_cast<const float2*>(p.rope_cs) + (size_t)pos * h2 + i);
+            float2 cs;
+            if (PRE) {
+                cs = pre->cs;
+            } else {
+                const int hs = sg.head_size, h2 = hs >> 1;
+                const int i = (sg.pair_mode == PAIR_NEOX) ? (rowA % hs) : ((rowA % hs) >> 1);
+                cs = __ldg(reinterpret_cast<const float2*>(p.rope_cs) + (size_t)pos * h2 + i);
+            }
             // (a + bi)(c + si): every product and sum rounded on its own, as the reference's complex multiply
             const float oa = __fsub_rn(__fmul_rn(vA, cs.x), __fmul_rn(vB, cs.y));
             const float ob = __fadd_rn(__fmul_rn(vA, cs.y), __fmul_rn(vB, cs.x));
             if (sg.epi == EPI_ROPE_Q) {
                 out[rowA] = oa;
                 out[rowB] = ob;
-            } else {  // key cache [kv_head][seq_len][hs]
-                float* dst = out + ((size_t)head * p.seq_len + pos) * hs;
+            } else if (PRE) {  // key cache [kv_head][seq_len][hs]
+                out[pre->dA] = oa;
+                out[pre->dB] = ob;
+            } else {
+                const int hs = sg.head_size;
+                float* dst = out + ((size_t)(rowA / hs) * p.seq_len + pos) * hs;
                 dst[rowA % hs] = oa;
                 dst[rowB % hs] = ob;
             }
             break;
         }
         case EPI_STORE_V: {  // value cache [kv_head][seq_len][hs]
-            const int hs = sg.head_size;
-            float* dst = out + ((size_t)(rowA / hs) * p.seq_len + pos) * hs;
-            dst[rowA % hs] = vA;
-            dst[rowB % hs] = vB;
+            if (PRE) {
+                out[pre->dA] = vA;
+                out[pre->dB] = vB;
+            } else {
+                const int hs = sg.head_size;
+                float* dst = out + ((size_t)(rowA / hs) * p.seq_len + pos) * hs;
+                dst[rowA % hs] = vA;
+                dst[rowB % hs] = vB;
+            }
             break;
         }
         case EPI_LOGITS:
