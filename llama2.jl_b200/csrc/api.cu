@@ -939,6 +939,7 @@ static int32_t enqueue_token(l2b_session* s, int* nlaunch, int nb = 1) {
             a.pos = &s->ctl->pos;
             a.n_heads = m->l_heads; a.n_kv = m->l_kv; a.hs = hs; a.seq_len = c.seq_len; a.nsplit = s->nsplit;
             a.nq = nb; a.q_stride = m->l_qdim();
+            a.min_chunk = (int)env_long("L2B_ATTN_MIN_CHUNK", 0);
             CU(launch_attention(a, s->gq, s->stream, true));
             ++count;
             L2B_TRY(checked("attention"));

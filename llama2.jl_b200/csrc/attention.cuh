@@ -32,6 +32,7 @@ struct AttnParams {
     int npos_override;  // >0: attend exactly this many positions (isolated-operator entry point)
     int nq;             // 2: two consecutive query positions (pos, pos + 1) per launch; 0 or 1: one
     int q_stride;       // elements between the two positions' q (and out) vectors
+    int min_chunk;      // positions per split below which splitting is not worth it (0: ATTN_MIN_CHUNK)
 };
 
 constexpr int ATTN_WARPS = 4;
@@ -54,7 +55,8 @@ __device__ __forceinline__ void attention_split_body(const AttnParams& p) {
     int* const ticket_p = p.tickets + qi * ngroups + hg;
     // Short contexts use fewer splits (at least ATTN_MIN_CHUNK positions each): blocks beyond `active` leave at
     // once, and a single active split writes its result directly, with no partials and no merge.
-    const int active = min(p.nsplit, (npos + ATTN_MIN_CHUNK - 1) / ATTN_MIN_CHUNK);
+    const int mc = p.min_chunk > 0 ? p.min_chunk : ATTN_MIN_CHUNK;
+    const int active = min(p.nsplit, (npos + mc - 1) / mc);
     if (sp >= active) return;
     const int chunk = (npos + active - 1) / active;
     const int t0 = sp * chunk, t1 = min(npos, t0 + chunk);
