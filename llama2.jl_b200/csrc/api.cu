@@ -63,7 +63,8 @@ struct DevMatrix {
     uint8_t* data = nullptr;  // f32 rows, or block records
     __half* d6 = nullptr;     // q6_K super-block scales
     int64_t file_bytes = 0;   // bytes in the stored (file) format
-    bool panels = false;      // k-quant rows longer than 16 blocks, stored as column panels
+    bool panels = false;      // k-quant rows longer than one stage, stored as column panels
+    int kb = MV_TILE_BLOCKS;  // stage width in super-blocks this matrix is laid out for (panel width)
     bool present() const { return data != nullptr; }
 };
 
@@ -78,14 +79,32 @@ static void free_matrix(DevMatrix& m) {
 // Copy one matrix to the device (repacking q6_K).  `rows` x `in` weights.
 // Rows longer than one stage (in > 4096) are re-ordered into column panels on the device (panelize_kernel) unless
 // `panels` is false (matrices that are read row by row: the embedding table, plain dequantisation).
+static long env_long(const char* name, long dflt);
+// Stage width for a matrix: 16 super-blocks, or 8 where a row is exactly one 16-wide stage and 16-wide ring slots would leave
+// fewer than four slots beside the activation planes (then only one group of consumer warps could work, on a ring three deep;
+// measured on the q6_K classifier 128256 x 4096: 101.7 -> 88.3 us).  Longer rows keep 16: with 8-block stages the q5_K
+// 4096 x 14336 matrix went from 16.5 to 18.5 us (twice the stages per tile, twice the per-stage synchronisation).
+static int choose_stage_blocks(int type, int64_t in) {
+    const int64_t nb = in / QK_K;
+    if (type == T_F32 || nb != MV_TILE_BLOCKS) return MV_TILE_BLOCKS;
+    const long slot16 = 4L * pad_32_mod_128(4 * MV_TILE_BLOCKS * dev_block_bytes(type));
+    const long base = mv_smem_layout((int)in, 3, true, 0, 0).total;
+    const long cap = std::min<long>(env_long("L2B_MV_SMEM_KB", 208) * 1024, 226 * 1024);
+    if (env_long("L2B_MV_STAGE_BLOCKS", 0) == 8) return 8;
+    if (env_long("L2B_MV_STAGE_BLOCKS", 0) == 16) return MV_TILE_BLOCKS;
+    return (cap - base) / slot16 >= 4 ? MV_TILE_BLOCKS : 8;
+}
+
 static int32_t panelize(DevMatrix& m, cudaStream_t st) {
     const int64_t nb = m.in / QK_K;
-    if (m.type == T_F32 || nb <= MV_TILE_BLOCKS || m.out < 2) return L2B_OK;
+    if (m.type == T_F32) return L2B_OK;
+    m.kb = choose_stage_blocks(m.type, m.in);
+    if (nb <= m.kb || m.out < 2) return L2B_OK;
     const int bb = dev_block_bytes(m.type);
     const size_t bytes = (size_t)nb * m.out * bb;
     uint8_t* dst = nullptr;
     CU(cudaMalloc(&dst, bytes));
-    panelize_kernel<<<1184, 256, 0, st>>>(m.data, dst, (int)nb, m.out, bb);
+    panelize_kernel<<<1184, 256, 0, st>>>(m.data, dst, (int)nb, m.out, bb, m.kb);
     cudaError_t e = cudaGetLastError();
     if (e == cudaSuccess) e = cudaStreamSynchronize(st);
     if (e != cudaSuccess) {
@@ -180,6 +199,7 @@ struct MvLaunch {
     bool kq = true;
     int planes = 3;
     int nb = 1;  // activation vectors per launch (2: two prompt positions per pass)
+    int kb = MV_TILE_BLOCKS;  // stage width the launch's matrices are laid out for
     int grid = 0, warps = 0;
     size_t smem = 0;
 };
@@ -226,8 +246,9 @@ static int32_t plan_matvec(MvLaunch& L, const DeviceInfo& di) {
         if ((long)L.smem > di.max_smem_optin - 1024) return fail(L2B_ERR_BAD_ARG, "input vector too long for shared memory");
         return L2B_OK;
     }
-    const int kb = std::min(nb, MV_TILE_BLOCKS);  // super-blocks per row and stage
-    p.nit = (nb + MV_TILE_BLOCKS - 1) / MV_TILE_BLOCKS;
+    const int kb = std::min(nb, L.kb);  // super-blocks per row and stage
+    p.kb = L.kb;
+    p.nit = (nb + L.kb - 1) / L.kb;
     // a slot holds 16 rows of kb blocks in up to 16 copy groups, each padded to 32 mod 128 bytes
     p.row_stride = kb * max_bb + 128;
     for (int s = 0; s < p.nseg; ++s) mv_fill_geometry(p.seg[s], kb, p.nit);
@@ -886,10 +907,12 @@ static int32_t enqueue_token(l2b_session* s, int* nlaunch, int nb = 1) {
         if (tp == 1) {
             L.p.seg[L.p.nseg++] = make_segment(w, PAIR_ADJACENT, EPI_RESIDUAL, s->x, hs);
             L.p.seg[L.p.nseg - 1].out2 = c.dim;
+            L.kb = w.kb;
             L.p.resid = s->x;
             return;
         }
         L.p.seg[L.p.nseg++] = make_segment(w, PAIR_ADJACENT, EPI_PUSH, nullptr, hs);
+        L.kb = w.kb;
         L.p.tp_push = 1;
         MvTp& d = new_desc(L);
         for (int r = 0; r < tp; ++r) {
@@ -918,13 +941,18 @@ static int32_t enqueue_token(l2b_session* s, int* nlaunch, int nb = 1) {
             MvSegment segs[3] = {make_segment(w.wq, rope_mode, EPI_ROPE_Q, s->q, hs), make_segment(w.wk, rope_mode, EPI_ROPE_K, kcl, hs),
                                  make_segment(w.wv, PAIR_ADJACENT, EPI_STORE_V, vcl, hs)};
             segs[0].out2 = m->l_qdim();  // the caches take both positions at their own rows: out2 = 0
-            // matrices of one storage class (f32 or k-quant) share a launch
-            for (int cls = 0; cls < 2; ++cls) {
+            // matrices of one storage class (f32, k-quant laid out for 16-block stages, k-quant laid out for 8-block
+            // stages) share a launch
+            const DevMatrix* mats[3] = {&w.wq, &w.wk, &w.wv};
+            for (int cls = 0; cls < 3; ++cls) {
                 MvLaunch L;
                 base_params(L, c.dim);
-                for (int i = 0; i < 3; ++i)
-                    if ((segs[i].type == T_F32) == (cls == 0)) L.p.seg[L.p.nseg++] = segs[i];
+                for (int i = 0; i < 3; ++i) {
+                    const int ci = segs[i].type == T_F32 ? 0 : (mats[i]->kb == MV_TILE_BLOCKS ? 1 : 2);
+                    if (ci == cls) L.p.seg[L.p.nseg++] = segs[i];
+                }
                 if (L.p.nseg == 0) continue;
+                L.kb = cls == 2 ? 8 : MV_TILE_BLOCKS;
                 norm_input(L, w.rms_att);
                 L2B_TRY(mv(L));
             }
@@ -963,6 +991,7 @@ static int32_t enqueue_token(l2b_session* s, int* nlaunch, int nb = 1) {
             g.w2 = w.w3.data;
             g.d6_2 = w.w3.d6;
             g.out2 = m->l_hidden;
+            L.kb = w.w1.kb;
             L.p.seg[L.p.nseg++] = g;
             norm_input(L, w.rms_ffn);
             L2B_TRY(mv(L));
@@ -992,6 +1021,7 @@ static int32_t enqueue_token(l2b_session* s, int* nlaunch, int nb = 1) {
         MvLaunch L;
         base_params(L, c.dim);
         L.p.seg[L.p.nseg++] = make_segment(m->output, PAIR_ADJACENT, EPI_LOGITS, s->logits, hs);
+        L.kb = m->output.kb;
         norm_input(L, m->rms_final);
         L.p.amax_val = s->amax_val;
         L.p.amax_idx = s->amax_idx;
@@ -1645,6 +1675,7 @@ extern "C" int32_t l2b_matrix_matvec_device(l2b_matrix* m, int32_t copy, const f
     L.planes = planes == 0 ? 3 : planes;
     L.p.n_in = (int)w.in;
     L.p.seg[L.p.nseg++] = make_segment(w, PAIR_ADJACENT, EPI_STORE, dev_y, 0);
+    L.kb = w.kb;
     L.p.pro = PRO_COPY;
     L.p.x_in = dev_x;
     L.p.status = m->status;

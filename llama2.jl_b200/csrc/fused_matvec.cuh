@@ -99,7 +99,8 @@ struct MvParams {
     // schedule, precomputed on the host (plan_matvec)
     int nslots;                      // ring slots
     int row_stride;                  // bytes between tile rows inside a slot (a multiple of 16, = 32 mod 128)
-    int nit;                         // stages per tile = ceil(blocks per row / 16)
+    int nit;                         // stages per tile = ceil(blocks per row / kb)
+    int kb;                          // super-blocks per row and stage (16, or 8 where 16-wide slots would leave fewer than 4 of them)
     int seg_start[MV_MAX_SEG + 1];   // first unit of each segment; [nseg] = total; a unit is a tile (k-quant) or a pair (f32)
     int units_lo, units_rem;         // block b runs units_lo + (b < units_rem) units: b, b + grid, ...
     int consumers;                   // consumer warps per block (k-quant: blockDim/32 - 2; f32: blockDim/32)
@@ -713,10 +714,10 @@ __global__ void __launch_bounds__((MV_MAX_CONSUMERS + 2) * 32, 1) fused_matvec_k
                 uint32_t bytes = ts.bytes0, tx = ts.tx0;
                 const uint8_t* src = ts.src;
                 if (nit > 1) {  // stage `it` lives in column panel `it`, whose rows are nblk blocks wide
-                    const int nblk = min(MV_TILE_BLOCKS, nb - it * MV_TILE_BLOCKS);
+                    const int nblk = min(p.kb, nb - it * p.kb);
                     bytes = (uint32_t)(ts.nrows * nblk * ts.bb);
                     tx = (uint32_t)(ts.nvalid * nblk * ts.bb);
-                    src += (size_t)it * ts.ps - (size_t)ts.row * ((MV_TILE_BLOCKS - nblk) * ts.bb);
+                    src += (size_t)it * ts.ps - (size_t)ts.row * ((p.kb - nblk) * ts.bb);
                 }
                 if (DBG && (p.debug & 2)) bytes = tx = 0;
                 if (c == 0) mbar_arrive_expect_tx(full + slot_i, tx);
@@ -914,9 +915,9 @@ __global__ void __launch_bounds__((MV_MAX_CONSUMERS + 2) * 32, 1) fused_matvec_k
             }
             float accA = 0.f, accB = 0.f;  // the two rows of pair pj of the tile
             for (int it = 0; it < nit; ++it) {
-                const int b0 = it * MV_TILE_BLOCKS, nblk = min(MV_TILE_BLOCKS, nb - b0);
+                const int b0 = it * p.kb, nblk = min(p.kb, nb - b0);
                 int oA = offA, oB = offB;
-                if (nit > 1 && nblk < MV_TILE_BLOCKS) pair_offsets(sg, nblk * bb, pj, oA, oB);  // narrow last panel
+                if (nit > 1 && nblk < p.kb) pair_offsets(sg, nblk * bb, pj, oA, oB);  // narrow last panel
                 float dA = 0.f, dB = 0.f;
                 if (sg.type == T_Q6_K && wl < nblk) {  // fetched before the wait so that the latency overlaps it
                     dA = __half2float(__ldg(d6A + b0 + wl));

@@ -18,11 +18,11 @@ __global__ void repack_q6k_kernel(const uint8_t* __restrict__ src, uint8_t* __re
     }
 }
 
-// Matrices whose rows are longer than one stage (more than 16 super-blocks) are stored as column panels: panel k holds
-// blocks 16k .. 16k+15 of EVERY row, rows back to back.  A tile's stage is then 16 adjacent rows of one panel, which a
+// Matrices whose rows are longer than one stage (more than kb super-blocks, kb = 16 or 8) are stored as column panels: panel k
+// holds blocks kb*k .. kb*k+kb-1 of EVERY row, rows back to back.  A tile's stage is then 16 adjacent rows of one panel, which a
 // few large bulk copies bring in, instead of 16 row slices that lie a whole row apart.  Same bytes, other order.
-//   address(row, block b) = (b / 16) * rows * 16 * bb  +  row * w * bb  +  (b % 16) * bb,   w = width of panel b / 16
-__global__ void panelize_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst, int nb, int64_t rows, int bb) {
+//   address(row, block b) = (b / kb) * rows * kb * bb  +  row * w * bb  +  (b % kb) * bb,   w = width of panel b / kb
+__global__ void panelize_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst, int nb, int64_t rows, int bb, int kb) {
     const int q = bb / 16;  // 16-byte units per block
     const int64_t total = rows * nb * q;
     for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
@@ -30,8 +30,8 @@ __global__ void panelize_kernel(const uint8_t* __restrict__ src, uint8_t* __rest
         const int u = (int)(i % q);
         const int64_t r = blk / nb;
         const int b = (int)(blk % nb);
-        const int k = b / 16, w = min(16, nb - 16 * k);
-        const int64_t o = (int64_t)k * rows * 16 + r * w + (b % 16);
+        const int k = b / kb, w = min(kb, nb - kb * k);
+        const int64_t o = (int64_t)k * rows * kb + r * w + (b % kb);
         reinterpret_cast<uint4*>(dst)[o * q + u] = reinterpret_cast<const uint4*>(src)[i];
     }
 }
