@@ -323,6 +323,48 @@ __device__ __forceinline__ void build_activation(const MvParams& p, uint8_t* sme
 #pragma unroll
             for (int u = 0; u < MV_REG_BLOCKS; ++u) emit(t0 + u, ka[u], kb[u]);
         }
+    } else if (KQ) {
+        // rmsnorm in front of k-quant weights: the int8 planes do not wait for the norm.  They are built from gain .* x at
+        // once; the positive scalar 1/rms leaves them unchanged and only multiplies the plane scales and the per-16 sums,
+        // which happens after the block-wide sum of squares (one barrier, whose wait the quantisation now overlaps).
+        float ss = 0.f;
+        for (int t0 = 0; t0 < turns; t0 += MV_GAIN_BLOCKS) {
+            float4 ka[MV_GAIN_BLOCKS], kb[MV_GAIN_BLOCKS], ga[MV_GAIN_BLOCKS], gb[MV_GAIN_BLOCKS];
+#pragma unroll
+            for (int u = 0; u < MV_GAIN_BLOCKS; ++u) {
+                fetch(t0 + u, ka[u], kb[u], true);
+                const int g = group_of(t0 + u);
+                ga[u] = gb[u] = zero4;
+                if (g < n8) {
+                    ga[u] = __ldg(reinterpret_cast<const float4*>(p.gain + 8 * g));
+                    gb[u] = __ldg(reinterpret_cast<const float4*>(p.gain + 8 * g + 4));
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < MV_GAIN_BLOCKS; ++u) {
+                ss = sumsq(ka[u], kb[u], ss);
+                float4 a = ka[u], b = kb[u];
+                a.x *= ga[u].x; a.y *= ga[u].y; a.z *= ga[u].z; a.w *= ga[u].w;
+                b.x *= gb[u].x; b.y *= gb[u].y; b.z *= gb[u].z; b.w *= gb[u].w;
+                emit(t0 + u, a, b);
+            }
+        }
+        ss = warp_sum(ss);
+        if (lane == 0) red[warp] = ss;
+        consumer_sync(nwarps * 32);
+        float tot = 0.f;
+        for (int i = 0; i < nwarps; ++i) tot += red[i];  // same order in every thread
+        tot /= (float)n;
+        tot += 1e-5f;
+        const float scale = 1.0f / sqrtf(tot);
+        for (int turn = 0; turn < turns; ++turn) {  // this warp's blocks
+            const int g0 = 32 * (warp + nwarps * turn);
+            if (g0 >= n8) break;
+            const int b = g0 >> 5;
+            if (lane < ZHI) dpl[8 * b + lane] *= scale;
+            if (lane < 16) xs16[16 * b + lane] *= scale;
+        }
+        // (the barrier below also keeps `red` untouched until every thread has read it)
     } else {
         // pass 1: sum of squares; the first MV_REG_BLOCKS turns stay in registers for pass 2
         float4 ka[MV_REG_BLOCKS], kb[MV_REG_BLOCKS];
