@@ -420,6 +420,74 @@ __device__ __forceinline__ void build_activation(const MvParams& p, uint8_t* sme
     consumer_sync(nwarps * 32);
 }
 
+// The same for the two vectors of a two-position launch (k-quant weights, one GPU), both in one pass: vector 0 at x_in ->
+// planes 0..P-1, scale columns 0..3; vector 1 at x_in + n_in -> planes P..2P-1, scale columns 4..7, its own sums.
+template <int P>
+__device__ __forceinline__ void build_activation_pair(const MvParams& p, uint8_t* smem, const MvSmem& L, int warp, int lane, int nwarps) {
+    const int n = p.n_in, n8 = n / 8, turns = p.turns, nb = n / QK_K;
+    float* red = reinterpret_cast<float*>(smem + L.off_red);
+    uint8_t* act0 = smem + L.off_act;
+    uint8_t* act1 = act0 + P * L.plane_stride;
+    float* dpl0 = reinterpret_cast<float*>(smem + L.off_dpl);
+    float* dpl1 = dpl0 + 4;
+    float* xs0 = reinterpret_cast<float*>(smem + L.off_xs);
+    float* xs1 = xs0 + nb * 16;
+    const bool norm = p.pro == PRO_RMSNORM;
+    auto sumsq = [](float4 a, float4 b, float ss) {
+        ss = fmaf(a.x, a.x, ss); ss = fmaf(a.y, a.y, ss); ss = fmaf(a.z, a.z, ss); ss = fmaf(a.w, a.w, ss);
+        ss = fmaf(b.x, b.x, ss); ss = fmaf(b.y, b.y, ss); ss = fmaf(b.z, b.z, ss); ss = fmaf(b.w, b.w, ss);
+        return ss;
+    };
+    auto mul = [](float4& a, const float4& g) { a.x *= g.x; a.y *= g.y; a.z *= g.z; a.w *= g.w; };
+    float ss0 = 0.f, ss1 = 0.f;
+    for (int turn = 0; turn < turns; ++turn) {
+        const int g0 = 32 * (warp + nwarps * turn), g = g0 + lane;
+        if (g0 >= n8) break;  // whole 256-value blocks: every lane of the warp is inside the vector
+        const float* x0 = p.x_in + 8 * g;
+        const float* x1 = x0 + n;
+        float4 a0 = __ldcg(reinterpret_cast<const float4*>(x0)), b0 = __ldcg(reinterpret_cast<const float4*>(x0 + 4));
+        float4 a1 = __ldcg(reinterpret_cast<const float4*>(x1)), b1 = __ldcg(reinterpret_cast<const float4*>(x1 + 4));
+        if (norm) {  // gain .* x now, 1/rms afterwards (see build_activation)
+            const float4 ga = __ldg(reinterpret_cast<const float4*>(p.gain + 8 * g));
+            const float4 gb = __ldg(reinterpret_cast<const float4*>(p.gain + 8 * g + 4));
+            ss0 = sumsq(a0, b0, ss0);
+            ss1 = sumsq(a1, b1, ss1);
+            mul(a0, ga); mul(b0, gb); mul(a1, ga); mul(b1, gb);
+        }
+        quantise_block<P, 4>(a0, b0, lane, act0, L.plane_stride, dpl0, xs0, g0 >> 5);
+        quantise_block<P, 4>(a1, b1, lane, act1, L.plane_stride, dpl1, xs1, g0 >> 5);
+    }
+    if (norm) {
+        ss0 = warp_sum(ss0);
+        ss1 = warp_sum(ss1);
+        if (lane == 0) {
+            red[warp] = ss0;
+            red[MV_MAX_CONSUMERS + warp] = ss1;
+        }
+        consumer_sync(nwarps * 32);
+        float t0 = 0.f, t1 = 0.f;
+        for (int i = 0; i < nwarps; ++i) {  // same order in every thread
+            t0 += red[i];
+            t1 += red[MV_MAX_CONSUMERS + i];
+        }
+        const float s0 = 1.0f / sqrtf(t0 / (float)n + 1e-5f), s1 = 1.0f / sqrtf(t1 / (float)n + 1e-5f);
+        for (int turn = 0; turn < turns; ++turn) {
+            const int g0 = 32 * (warp + nwarps * turn);
+            if (g0 >= n8) break;
+            const int b = g0 >> 5;
+            if (lane < 4) {
+                dpl0[8 * b + lane] *= s0;
+                dpl1[8 * b + lane] *= s1;
+            }
+            if (lane < 16) {
+                xs0[16 * b + lane] *= s0;
+                xs1[16 * b + lane] *= s1;
+            }
+        }
+    }
+    consumer_sync(nwarps * 32);
+}
+
 // ---- work enumeration ----------------------------------------------------------------------
 // A unit is a tile of MV_TILE_PAIRS row pairs of one segment (k-quant) or one pair (f32).  Units of all segments
 // are numbered consecutively; block b takes units b, b + grid, b + 2*grid, ... so that every block streams the
@@ -890,9 +958,8 @@ __global__ void __launch_bounds__((MV_MAX_CONSUMERS + 2) * 32, 1) fused_matvec_k
         float* xs16 = reinterpret_cast<float*>(smem + L.off_xs);
         if (NB == 1) {
             build_activation<KQ, P, TP>(p, smem, L, warp, lane, W, p.x_in, act, dpl, xs16);
-        } else {  // vector s: planes s*P .., scale columns 4s .., its own sums
-            build_activation<KQ, P, TP, 4>(p, smem, L, warp, lane, W, p.x_in, act, dpl, xs16);
-            build_activation<KQ, P, TP, 4>(p, smem, L, warp, lane, W, p.x_in + p.n_in, act + P * L.plane_stride, dpl + 4, xs16 + (p.n_in / QK_K) * 16);
+        } else {
+            build_activation_pair<P>(p, smem, L, warp, lane, W);
         }
     }
     MV_TRACE(3);
