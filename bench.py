@@ -274,7 +274,7 @@ def run_ours(args):
         "config": {"workload": wl_name, "positions_per_step": n_pos, "act_planes": args.act_planes or 3,
                    "prompt": ("fed two positions per pass (%d two-position passes + %d one-position passes per step; no logits for forced positions)"
                               % (n_pair_passes, len(schedule) - n_pair_passes)) if pairs else "fed position by position",
-                   "l2": "inputs larger than L2 (%.2f GB of weights streamed per position)" % (wbytes / 1e9),
+                   "l2": "inputs larger than L2 (%.2f GB of weights streamed per pass)" % (wbytes / 1e9),
                    "multi_gpu": ("tensor parallel over %d GPUs, partial vectors exchanged by peer stores" % world) if tp_mode
                    else ("replicas only" if world > 1 else "single GPU")},
         "e2e": {"value": round(e2e_value, 2), "unit": "tok/s", "h2d_bytes_per_step": 4 * len(prompt) + 48, "d2h_bytes_per_step": 4 * n_pos + 4,
