@@ -7,20 +7,26 @@
 //
 //   prologue  : raw copy | rmsnorm (inference.jl:102-110) of a vector in global memory; then, for
 //               k-quant weights, on-device quantisation of the vector to 1..3 int8 planes
-//               (block_q8_K layout, kquants.jl:38-42).
-//   weights   : warp-specialised.  A tile is 16 output rows (8 row pairs) by up to 16 super-blocks.
-//               The lanes of one producer warp bring a tile into a ring of shared-memory slots with
-//               a few large bulk asynchronous copies (TMA): 4 copies of 4 adjacent rows, or 8 copies of
-//               2 rows when the two rows of a pair are far apart (an SM issues only ~23 bulk copies per
-//               microsecond, so 16 row-sized copies per tile would cap the stream below the HBM rate).
-//               The producer starts BEFORE the wait on the previous kernel (programmatic dependent
-//               launch): weights are constants, so the ring is already full when the activations arrive.
-//               All consumer warps work on the same slot, one or two super-block columns each, with int8
-//               tensor-core MMAs (kquants.cuh); their partial sums go to a small ring of shared-memory
-//               buffers, where a dedicated finisher warp adds them in a fixed order and runs the epilogue,
-//               so that no consumer warp ever waits for another one.
+//               (block_q8_K layout, kquants.jl:38-42).  With rmsnorm the planes are built from
+//               gain .* x while the sum of squares is still being collected; 1/rms scales the plane
+//               scales afterwards.  A two-position launch builds the planes of both positions.
+//   weights   : warp-specialised.  A tile is 16 output rows (8 row pairs) by up to 16 super-blocks (a
+//               stage).  The lanes of one producer warp bring a stage into a ring of shared-memory slots
+//               with a few large bulk asynchronous copies (TMA): 4 copies of 4 adjacent rows, or 8 copies
+//               of 2 rows when the two rows of a pair are far apart (an SM issues only ~23 bulk copies
+//               per microsecond, so 16 row-sized copies per tile would cap the stream below the HBM
+//               rate).  Rows longer than a stage are stored as column panels, so every stage of theirs
+//               looks like a short row.  The producer starts BEFORE the wait on the previous kernel
+//               (programmatic dependent launch): weights are constants, so the ring is already full
+//               when the activations arrive.  All consumer warps of a group work on the same slot, one or
+//               two super-block columns each, with int8 tensor-core MMAs (kquants.cuh); their partial
+//               sums go to a small ring of shared-memory buffers, where a dedicated finisher warp adds
+//               them in a fixed order and runs the epilogue, so that no consumer warp ever waits for
+//               another one.  The finisher fetches what the epilogue needs from global memory (residual
+//               values, RoPE factors) before it waits for a tile's sums.
 //   epilogue  : store | residual add (:284,:305) | SwiGLU (:295-299) | RoPE + KV-cache write
-//               (:255-260) | logits store + running argmax (:312,:360)
+//               (:255-260) | logits store + running argmax (:312,:360) | push of a partial vector to the
+//               other tensor-parallel ranks
 //
 // A kernel here lives for a few microseconds, so serial scalar work on the critical path matters as
 // much as bandwidth: everything that can be computed on the host (tile counts, loop bounds, division
