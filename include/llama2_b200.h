@@ -162,6 +162,11 @@ int32_t l2b_session_logits(l2b_session* session, float* host_logits);
 int32_t l2b_session_read(l2b_session* session, int32_t which, float* host_out, int64_t capacity, int64_t* n);
 /* Device time (ms, CUDA events on the session stream) of the most recent forward/decode/generate call. */
 int32_t l2b_session_last_device_ms(l2b_session* session, float* ms);
+/* The prompt phase of `sample` (src/inference.jl:349-356, where the reference runs transformer! once per prompt token) as one
+ * call: feeds tokens[0..n-1] at positions pos0 .. pos0+n-1, two positions per pass where both are followed by a prompt token.
+ * Afterwards the session holds the logits of the last prompt position (l2b_session_logits); *next (may be NULL) is their argmax.
+ * Continue with l2b_decode_next(session, chosen_token, pos0 + n, ...). */
+int32_t l2b_prefill(l2b_session* session, const int32_t* tokens, int32_t n, int32_t pos0, int32_t* next);
 /* 1 when l2b_generate feeds prompts two positions per pass (k-quant model, three activation planes, one GPU, everything fits in
  * shared memory; switch off with L2B_PREFILL_PAIRS=0): positions p, p+1 that are both followed by a prompt token share one pass
  * over the weights, and no logits are computed for them.  The reference feeds prompts token by token (src/inference.jl:349-356). */

@@ -4,7 +4,7 @@ from ._lib import L2BError, lib  # noqa: F401
 from .load_gguf import load_gguf_model  # noqa: F401
 from .load_karpathy import load_karpathy_model  # noqa: F401
 from .model import (LanguageModel, ModelConfig, QuantMatrix, RunState, TransformerLayerWeights, TransformerWeights,  # noqa: F401
-                    dequantize, generate, matmul_, sample, transformer_)
+                    dequantize, generate, matmul_, prefill, sample, transformer_)
 from .tokenizer import BPETokenizer, CharTokenizer, encode  # noqa: F401
 
 __all__ = ["ModelConfig", "CharTokenizer", "LanguageModel", "load_gguf_model", "load_karpathy_model", "encode", "sample"]

@@ -63,6 +63,7 @@ _SIGNATURES = {
     "l2b_attention": ([_P, _P, _P, _P, C.c_int32, C.c_int32, C.c_int32, C.c_int32], C.c_int32),
     "l2b_model_load_gguf": ([C.c_char_p, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32, _P, C.POINTER(_P)], C.c_int32),
     "l2b_gguf_inspect": ([C.c_char_p, _P, C.POINTER(C.c_int32), C.POINTER(C.c_int64), C.POINTER(C.c_int64)], C.c_int32),
+    "l2b_prefill": ([_P, _P, C.c_int32, C.c_int32, C.POINTER(C.c_int32)], C.c_int32),
     "l2b_session_prefill_pairs": ([_P, C.POINTER(C.c_int32)], C.c_int32),
     "l2b_session_tp_handle": ([_P, _P], C.c_int32),
     "l2b_session_tp_connect": ([_P, _P, C.c_int32], C.c_int32),

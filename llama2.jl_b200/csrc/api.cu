@@ -1327,6 +1327,40 @@ extern "C" int32_t l2b_decode_next(l2b_session* s, int32_t token, int32_t pos, f
     return L2B_OK;
 }
 
+// Feed n prompt tokens at positions pos0 .. pos0+n-1 (teacher-forced; two positions per pass where both are followed by a
+// prompt token).  The last position goes through the one-position graph, so its logits are in the session afterwards and
+// *next (if given) is their argmax; the caller continues with l2b_decode_next(session, chosen token, pos0 + n, ...).
+extern "C" int32_t l2b_prefill(l2b_session* s, const int32_t* tokens, int32_t n, int32_t pos0, int32_t* next) {
+    if (!s || !tokens) return fail(L2B_ERR_BAD_ARG, "null argument");
+    const l2b_config& c = s->model->cfg;
+    if (n < 1 || pos0 < 0 || (int64_t)pos0 + n > c.seq_len) return fail(L2B_ERR_BAD_ARG, "positions pos0 .. pos0+n-1 must lie in 0..seq_len-1");
+    for (int i = 0; i < n; ++i)
+        if (tokens[i] < 0 || tokens[i] >= c.vocab_size) return fail(L2B_ERR_BAD_ARG, "prompt token id out of range");
+    if (!s->graph) return fail(L2B_ERR_STATE, "tensor-parallel session: call l2b_session_tp_connect first");
+    CU(cudaSetDevice(s->model->device));
+    Control& h = *s->h_ctl;
+    memset(&h, 0, sizeof(h));
+    h.token = tokens[0];
+    h.pos = pos0;
+    h.n_prompt = pos0 + n;  // positions are absolute: prompt[pos] is the token fed at position pos
+    CU(cudaEventRecord(s->ev0, s->stream));
+    CU(cudaMemcpyAsync(s->prompt + pos0, tokens, (size_t)n * 4, cudaMemcpyHostToDevice, s->stream));
+    CU(cudaMemcpyAsync(s->ctl, s->h_ctl, sizeof(Control), cudaMemcpyHostToDevice, s->stream));
+    const int end = pos0 + n;
+    for (int i = pos0; i < end;) {
+        const bool pair = s->graph2 && i + 2 < end;
+        CU(cudaGraphLaunch(pair ? s->graph2 : s->graph, s->stream));
+        i += pair ? 2 : 1;
+    }
+    CU(cudaMemcpyAsync(&s->h_small[0], s->next_token, 4, cudaMemcpyDeviceToHost, s->stream));
+    CU(cudaMemcpyAsync(&s->h_small[1], s->status, 4, cudaMemcpyDeviceToHost, s->stream));
+    CU(cudaEventRecord(s->ev1, s->stream));
+    CU(cudaStreamSynchronize(s->stream));
+    CU(cudaEventElapsedTime(&s->last_ms, s->ev0, s->ev1));
+    if (next) *next = s->h_small[0];
+    return check_status_word(s);
+}
+
 extern "C" int32_t l2b_session_prefill_pairs(l2b_session* s, int32_t* enabled) {
     if (!s || !enabled) return fail(L2B_ERR_BAD_ARG, "null argument");
     *enabled = s->graph2 ? 1 : 0;

@@ -124,4 +124,18 @@ function decode_next(config::ModelConfig, weights::TransformerWeights, token::In
     return Int(next[]) + 1
 end
 
+# ---- the prompt phase of `sample` ----------------------------------------------------------------
+# Replaces the iterations of the loop in src/inference.jl:349-356 whose next token is a prompt token: all prompt tokens
+# in one call (the library streams the weights once for two positions where it can).  Returns the greedy choice after the
+# last prompt token; for temperature sampling the caller reads the logits of that position and draws from them as before.
+function prefill!(config::ModelConfig, weights::TransformerWeights, prompt_tokens::Vector{Int})
+    dm = device_model(config, weights)
+    check(ccall((:l2b_session_reset, LIB), Int32, (Ptr{Cvoid},), dm.session))
+    toks = Int32.(prompt_tokens .- 1)
+    next = Ref{Int32}(0)
+    GC.@preserve toks check(ccall((:l2b_prefill, LIB), Int32, (Ptr{Cvoid}, Ptr{Int32}, Int32, Int32, Ref{Int32}),
+                                  dm.session, pointer(toks), length(toks), 0, next))
+    return Int(next[]) + 1
+end
+
 end # module

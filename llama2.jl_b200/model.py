@@ -250,6 +250,17 @@ def transformer_(token: int, pos: int, config: ModelConfig, s: RunState, weights
     L.check(L.lib().l2b_forward(s.session, int(token), int(pos), L.ptr(s.logits)))
 
 
+def prefill(s: RunState, tokens, pos0: int = 0) -> int:
+    """The prompt phase of `sample` (src/inference.jl:349-356) in one call: tokens at positions pos0.., two positions per pass
+    over the weights where possible.  Returns the argmax after the last prompt position; its logits are read with
+    l2b_session_logits (s.logits is filled)."""
+    t = np.ascontiguousarray(tokens, dtype=np.int32)
+    nxt = C.c_int32()
+    L.check(L.lib().l2b_prefill(s.session, L.ptr(t), t.size, int(pos0), C.byref(nxt)))
+    L.check(L.lib().l2b_session_logits(s.session, L.ptr(s.logits)))
+    return nxt.value
+
+
 def generate(model: LanguageModel, prompt_tokens, n_positions: int, temperature: float = 0.0, seed: int = 0):
     """The loop of `sample` without text: returns (tokens chosen after each position, device milliseconds)."""
     dev = model.device_model()
@@ -269,8 +280,9 @@ def sample(model: LanguageModel, prompt: str = "", *, temperature: float = 0.9, 
            max_seq_len: int = sys.maxsize, bos_token: bool = True, rng: Optional[random.Random] = None, out=None) -> None:
     """sample(model, prompt; temperature, stop_on_special_token, max_seq_len, bos_token) (src/inference.jl:317-395).
 
-    Prints the text and the achieved tok/s like the reference and returns None.  Each position is one
-    l2b_decode_next call (token id in, next token id out)."""
+    Prints the text and the achieved tok/s like the reference and returns None.  The prompt positions whose next token is
+    a prompt token go through one l2b_prefill call (unless the stop condition could fire among them); every other position
+    is one l2b_decode_next call (token id in, next token id out)."""
     from .tokenizer import encode
     out = out or sys.stdout
     if not bos_token and prompt == "":
@@ -288,7 +300,19 @@ def sample(model: LanguageModel, prompt: str = "", *, temperature: float = 0.9, 
     generated_seq_len = 0
     lib = L.lib()
     nxt = C.c_int32()
-    for pos in range(min(config.seq_len, max_seq_len)):
+    limit = min(config.seq_len, max_seq_len)
+    first = 0
+    n_forced = len(prompt_tokens) - 1  # positions 0 .. n_forced-1 are followed by a prompt token
+    specials = (tokenizer.bos_token_id, tokenizer.eos_token_id)
+    if n_forced >= 2 and n_forced <= limit and not (stop_on_special_token and any(t in specials for t in prompt_tokens[1:])):
+        t = np.ascontiguousarray(prompt_tokens[:n_forced], dtype=np.int32)
+        L.check(lib.l2b_prefill(state.session, L.ptr(t), t.size, 0, None))
+        for tok in prompt_tokens[1:]:
+            out.write(_text(tokenizer.id_to_token[tok]))
+        generated_seq_len = n_forced
+        token = prompt_tokens[n_forced]
+        first = n_forced
+    for pos in range(first, limit):
         L.check(lib.l2b_decode_next(state.session, int(token), pos, float(temperature), rng.random() if temperature != 0 else 0.0,
                                     C.byref(nxt)))
         generated_seq_len += 1

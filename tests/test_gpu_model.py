@@ -186,3 +186,59 @@ def test_two_position_prompt_passes_match_one_position_passes(pkg, synth, orc, s
     assert np.abs(la - lb).max() / rng < 1e-5
     single.close()
     paired.close()
+
+
+@pytest.mark.gpu
+def test_prefill_then_decode_matches_generate(pkg, synth):
+    """l2b_prefill (the prompt phase as one call, two positions per pass) followed by l2b_decode_next calls gives the stream of
+    l2b_generate; a prompt fed in two chunks (second chunk at pos0 > 0) gives it too."""
+    import ctypes as C
+    from llama2_jl_b200 import _lib as L
+    cfg = pkg.ModelConfig(512, 1024, 2, 8, 2, 512, 64, 10000.0, False)
+    w = synth.model_weights(cfg, dict(synth.ALL(12), wv=13, w2=13, output=14), seed=3)
+    m = pkg.LanguageModel(cfg, None, w)
+    prompt = synth.tokens(13, 4, 3, cfg.vocab_size)
+    want, _ = pkg.generate(m, prompt, 30)
+    for chunks in ([13], [6, 7], [1, 12]):
+        st = pkg.RunState(m)  # zeroes the cache
+        pos, tok = 0, None
+        for n in chunks:
+            tok = pkg.prefill(st, prompt[pos:pos + n], pos)
+            pos += n
+        got = list(prompt[1:]) + [tok]
+        nxt = C.c_int32()
+        while len(got) < 30:
+            L.check(L.lib().l2b_decode_next(st.session, int(got[-1]), len(got), 0.0, 0.0, C.byref(nxt)))
+            got.append(nxt.value)
+        assert got == [int(t) for t in want], chunks
+    with pytest.raises(L.L2BError):
+        pkg.prefill(pkg.RunState(m), prompt, 60)  # runs past seq_len
+    m.close()
+
+
+@pytest.mark.gpu
+def test_sample_text_with_and_without_prefill(pkg, synth):
+    """`sample` prints the same text whether the prompt goes through l2b_prefill or position by position (a max_seq_len
+    shorter than the prompt forces the latter), and the text is the decoding of l2b_generate's tokens."""
+    import io
+    from llama2_jl_b200.tokenizer import CharTokenizer, encode
+    tk = CharTokenizer.from_text("abcdefghijklmnopqrstuvwxyz .,")
+    vocab = len(tk.id_to_token)
+    vocab += vocab % 2
+    cfg = pkg.ModelConfig(256, 512, 2, 4, 2, vocab, 48, 10000.0, False)
+    w = synth.model_weights(cfg, dict(synth.ALL(12), output=14), seed=12)
+    if len(tk.id_to_token) < vocab:
+        tk.id_to_token.append("~")
+        tk.token_to_id["~"] = vocab - 1
+    m = pkg.LanguageModel(cfg, tk, w)
+    prompt = "the quick brown fox"
+    a, b = io.StringIO(), io.StringIO()
+    pkg.sample(m, prompt, temperature=0.0, stop_on_special_token=False, out=a)
+    ids = [tk.bos_token_id] + encode(prompt, tk)
+    toks, _ = pkg.generate(m, ids, cfg.seq_len)
+    text = "".join(tk.id_to_token[int(t)] for t in toks)
+    assert a.getvalue().split("\n")[0] == text
+    # prefill is skipped when the prompt does not fit into max_seq_len: the per-position path must print the same prefix
+    pkg.sample(m, prompt, temperature=0.0, stop_on_special_token=False, max_seq_len=10, out=b)
+    assert b.getvalue().split("\n")[0] == text[:10]
+    m.close()
