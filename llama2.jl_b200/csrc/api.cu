@@ -1122,9 +1122,9 @@ extern "C" int32_t l2b_session_create(l2b_model* m, void* stream, l2b_session** 
         s->gq = choose_gq(m->l_heads, m->l_kv);
         const int groups = m->l_heads / s->gq;
         // splits of the position range: about 1.3 blocks per SM for short contexts, where the launch is latency-bound (measured:
-        // 24 splits beat 19 and 32 at the 8-group 8B shape, seq_len 512), about 3.5 per SM for long ones, where it has to keep
+        // 24 splits beat 19 and 32 at the 8-group 8B shape, seq_len 512), about 3.4 per SM for long ones, where it has to keep
         // many loads in flight (Phi-3-mini shape, seq_len 4096, 32 groups: 16 splits gave 906 tok/s, 6 gave 708, 32 gave 893)
-        const int per_sm_x10 = c.seq_len >= 2048 ? 35 : 13;
+        const int per_sm_x10 = c.seq_len >= 2048 ? 34 : 13;
         int ns = (s->di.sms * per_sm_x10 / 10 + groups - 1) / groups;
         ns = std::max(1, std::min(ns, std::min(32, (c.seq_len + 7) / 8)));
         s->nsplit = (int)env_long("L2B_ATTN_SPLITS", ns);
