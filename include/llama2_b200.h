@@ -38,7 +38,7 @@ enum l2b_status {
     L2B_ERR_BAD_ARG = 1,
     L2B_ERR_UNSUPPORTED_TYPE = 2, /* src/load_gguf.jl:153,179 "tensor type ... not implemented" */
     L2B_ERR_CUDA = 3,
-    L2B_ERR_NCCL = 4,
+    /* 4 is not used */
     L2B_ERR_TIMEOUT = 5, /* a bounded device-side wait ran out */
     L2B_ERR_OOM = 6,
     L2B_ERR_STATE = 7, /* call order: e.g. forward before finalize */
@@ -181,6 +181,10 @@ int32_t l2b_dequantize(int32_t ggml_type, const void* host_blocks, int64_t n_ele
  * host_q[p][n] int8, host_d[p][n/256] f32 (scale of plane p), host_sums[n/16] f32 = sums of the represented
  * values over groups of 16 (the role of bsums).  The reference declares block_q8_K but has no quantiser. */
 int32_t l2b_quantize_q8k(const float* host_x, int64_t n, int32_t planes, int8_t* host_q, float* host_d, float* host_sums);
+/* rmsnorm! (src/inference.jl:102-110) fused with that quantisation, as it runs in front of every k-quant matrix of the
+ * token path: the planes represent w .* (x / rms(x)).  Same outputs as l2b_quantize_q8k. */
+int32_t l2b_rmsnorm_quantize_q8k(const float* host_x, const float* host_w, int64_t n, int32_t planes, int8_t* host_q, float* host_d,
+                                 float* host_sums);
 /* matmul!(y, A, x) (src/matmul.jl:3-23) for ncols activation columns: x is [ncols][in], y is [ncols][out]. */
 int32_t l2b_matvec(int32_t ggml_type, const void* host_W, int64_t in_dim, int64_t out_dim, const float* host_x,
                    int32_t ncols, float* host_y, int32_t act_planes);
@@ -222,14 +226,6 @@ int32_t l2b_matrix_destroy(l2b_matrix* m);
 int32_t l2b_matrix_matvec_device(l2b_matrix* m, int32_t copy, const float* dev_x, float* dev_y, int32_t act_planes, void* stream);
 /* The same through host buffers (x: [ncols][in], y: [ncols][out]). */
 int32_t l2b_matrix_matvec(l2b_matrix* m, const float* host_x, int32_t ncols, float* host_y, int32_t act_planes);
-
-/* ---- seeded synthetic data (counter-based, integer-only, identical on every machine) -- */
-/* n f32 values ~ N(0, std^2) (Irwin-Hall of 12 16-bit uniforms), or the constant `std` when constant != 0. */
-int32_t l2b_synth_f32(float* host_out, int64_t n, uint64_t seed, float std, int32_t constant);
-/* n_blocks k-quant super-blocks: fp16 d, dmin = |N(0, 0.01^2)|, every other byte uniform random. */
-int32_t l2b_synth_kquant(int32_t ggml_type, void* host_out, int64_t n_blocks, uint64_t seed);
-/* n token ids uniform in [lo, hi). */
-int32_t l2b_synth_tokens(int32_t* host_out, int64_t n, uint64_t seed, int32_t lo, int32_t hi);
 
 #ifdef __cplusplus
 }

@@ -10,7 +10,7 @@ import os
 _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.environ.get("L2B_LIBRARY") or os.path.join(_HERE, "libllama2_b200.so")
 
-OK, ERR_BAD_ARG, ERR_UNSUPPORTED_TYPE, ERR_CUDA, ERR_NCCL, ERR_TIMEOUT, ERR_OOM, ERR_STATE, ERR_NO_DEVICE = range(9)
+OK, ERR_BAD_ARG, ERR_UNSUPPORTED_TYPE, ERR_CUDA, _ERR_UNUSED, ERR_TIMEOUT, ERR_OOM, ERR_STATE, ERR_NO_DEVICE = range(9)
 TYPE_F32, TYPE_Q4_K, TYPE_Q5_K, TYPE_Q6_K = 0, 12, 13, 14
 BLOCK_BYTES = {TYPE_Q4_K: 144, TYPE_Q5_K: 176, TYPE_Q6_K: 210}
 (ROLE_TOKEN_EMBEDDING, ROLE_RMS_ATT, ROLE_WQ, ROLE_WK, ROLE_WV, ROLE_WO, ROLE_RMS_FFN, ROLE_W1, ROLE_W2, ROLE_W3,
@@ -57,6 +57,7 @@ _SIGNATURES = {
     "l2b_session_kernels_per_token": ([_P, C.POINTER(C.c_int32)], C.c_int32),
     "l2b_dequantize": ([C.c_int32, _P, C.c_int64, _P], C.c_int32),
     "l2b_quantize_q8k": ([_P, C.c_int64, C.c_int32, _P, _P, _P], C.c_int32),
+    "l2b_rmsnorm_quantize_q8k": ([_P, _P, C.c_int64, C.c_int32, _P, _P, _P], C.c_int32),
     "l2b_matvec": ([C.c_int32, _P, C.c_int64, C.c_int64, _P, C.c_int32, _P, C.c_int32], C.c_int32),
     "l2b_rmsnorm": ([_P, _P, _P, C.c_int64], C.c_int32),
     "l2b_rope": ([_P, C.c_int32, C.c_int32, C.c_int32, C.c_float, C.c_int32], C.c_int32),
@@ -75,10 +76,35 @@ _SIGNATURES = {
     "l2b_matrix_destroy": ([_P], C.c_int32),
     "l2b_matrix_matvec_device": ([_P, C.c_int32, _P, _P, C.c_int32, _P], C.c_int32),
     "l2b_matrix_matvec": ([_P, _P, C.c_int32, _P, C.c_int32], C.c_int32),
+}
+# include/l2b_synth.h: the test-support library of seeded synthetic data (libl2b_synth.so, no CUDA)
+SYNTH_LIB_PATH = os.path.join(_HERE, "libl2b_synth.so")
+_SYNTH_SIGNATURES = {
     "l2b_synth_f32": ([_P, C.c_int64, C.c_uint64, C.c_float, C.c_int32], C.c_int32),
     "l2b_synth_kquant": ([C.c_int32, _P, C.c_int64, C.c_uint64], C.c_int32),
     "l2b_synth_tokens": ([_P, C.c_int64, C.c_uint64, C.c_int32, C.c_int32], C.c_int32),
 }
+_synth = None
+
+
+def synth_lib():
+    """The synthetic-data library; loading it does not load the CUDA library."""
+    global _synth
+    if _synth is None:
+        if not os.path.exists(SYNTH_LIB_PATH):
+            raise ImportError(f"{SYNTH_LIB_PATH} is missing: build it first (python -c 'import __graft_entry__ as g; g.build()')")
+        handle = C.CDLL(SYNTH_LIB_PATH)
+        for name, (argtypes, restype) in _SYNTH_SIGNATURES.items():
+            fn = getattr(handle, name)
+            fn.argtypes = argtypes
+            fn.restype = restype
+        _synth = handle
+    return _synth
+
+
+def synth_check(status):
+    if status != OK:
+        raise L2BError(status, "synthetic-data generator: bad argument or unsupported tensor type")
 
 _lib = None
 

@@ -3,10 +3,11 @@ import os
 import subprocess
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-SOURCES = ["csrc/api.cu", "csrc/synth.cpp", "csrc/gguf_reader.cpp"]
+SOURCES = ["csrc/api.cu", "csrc/gguf_reader.cpp"]
 HEADERS = ["csrc/common.cuh", "csrc/kquants.cuh", "csrc/fused_matvec.cuh", "csrc/attention.cuh", "csrc/sampling.cuh",
            "csrc/small_ops.cuh", "csrc/gguf_reader.h", "../include/llama2_b200.h"]
 OUTPUT = os.path.join(_HERE, "libllama2_b200.so")
+SYNTH_OUTPUT = os.path.join(_HERE, "libl2b_synth.so")  # test support: seeded synthetic data, plain C++
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC", "-shared"]
 
 
@@ -17,7 +18,15 @@ def needs_build():
     return any(os.path.getmtime(os.path.join(_HERE, f)) > t for f in SOURCES + HEADERS)
 
 
+def build_synth(force=False):
+    src = os.path.join(_HERE, "csrc/synth.cpp")
+    if force or not os.path.exists(SYNTH_OUTPUT) or os.path.getmtime(src) > os.path.getmtime(SYNTH_OUTPUT):
+        subprocess.run([os.environ.get("CXX", "g++"), "-O2", "-std=c++17", "-fPIC", "-shared", "-pthread", "-o", SYNTH_OUTPUT, src], check=True)
+    return SYNTH_OUTPUT
+
+
 def build(force=False, verbose=False):
+    build_synth(force)
     if not force and not needs_build():
         return OUTPUT
     nvcc = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")

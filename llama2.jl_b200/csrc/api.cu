@@ -213,7 +213,9 @@ static int32_t plan_matvec(MvLaunch& L, const DeviceInfo& di) {
     for (int s = 0; s < p.nseg; ++s)
         if ((p.seg[s].type != T_F32) != L.kq) return fail(L2B_ERR_UNSUPPORTED_TYPE, "f32 and k-quant matrices cannot share one launch");
     p.planes = L.planes;
+#ifdef L2B_MEASURE
     p.debug = (int)env_long("L2B_MV_DEBUG", 0);
+#endif
     L.grid = di.sms;
     const int nb = p.n_in / QK_K;
     const int per_unit = L.kq ? MV_TILE_PAIRS : 1;
@@ -301,10 +303,12 @@ static void set_kernel_attrs() {
         set((const void*)fused_matvec_kernel<true, 3>);
         set((const void*)fused_matvec_kernel<false, 1>);
         set((const void*)fused_matvec_kernel<true, 3, false, false, 2>);
+#ifdef L2B_MEASURE
         set((const void*)fused_matvec_kernel<true, 1, false, true>);
         set((const void*)fused_matvec_kernel<true, 2, false, true>);
         set((const void*)fused_matvec_kernel<true, 3, false, true>);
         set((const void*)fused_matvec_kernel<false, 1, false, true>);
+#endif
         set((const void*)fused_matvec_kernel<true, 1, true>);
         set((const void*)fused_matvec_kernel<true, 2, true>);
         set((const void*)fused_matvec_kernel<true, 3, true>);
@@ -323,7 +327,8 @@ static int32_t check_kernel_attrs() {
 
 static cudaError_t launch_matvec(const MvLaunch& L, cudaStream_t st, bool pdl) {
     const dim3 grid(L.grid), block(L.warps * 32);
-    if (L.p.debug || L.p.trace) {  // measurement aids: the instantiations that carry them
+#ifdef L2B_MEASURE
+    if (L.p.debug || L.p.trace) {  // measurement aids (a -DL2B_MEASURE build only): the instantiations that carry them
         if (L.p.tp) return cudaErrorNotSupported;
         if (!L.kq) return launch_kernel(fused_matvec_kernel<false, 1, false, true>, grid, block, L.smem, st, pdl, L.p);
         switch (L.planes) {
@@ -332,6 +337,7 @@ static cudaError_t launch_matvec(const MvLaunch& L, cudaStream_t st, bool pdl) {
             default: return launch_kernel(fused_matvec_kernel<true, 3, false, true>, grid, block, L.smem, st, pdl, L.p);
         }
     }
+#endif
     if (L.nb == 2) {  // two prompt positions per pass: k-quant weights, three planes, one GPU only
         if (!L.kq || L.planes != 3 || L.p.tp) return cudaErrorNotSupported;
         return launch_kernel(fused_matvec_kernel<true, 3, false, false, 2>, grid, block, L.smem, st, pdl, L.p);
@@ -480,7 +486,6 @@ extern "C" const char* l2b_status_string(int32_t s) {
         case L2B_ERR_BAD_ARG: return "bad argument";
         case L2B_ERR_UNSUPPORTED_TYPE: return "unsupported tensor type";
         case L2B_ERR_CUDA: return "CUDA error";
-        case L2B_ERR_NCCL: return "NCCL error";
         case L2B_ERR_TIMEOUT: return "device-side wait timed out";
         case L2B_ERR_OOM: return "out of device memory";
         case L2B_ERR_STATE: return "call made in the wrong state";
@@ -835,28 +840,18 @@ static int32_t enqueue_token(l2b_session* s, int* nlaunch, int nb = 1) {
     const size_t kvl = kv_layer_elems(m);
     int count = 0, last_grid = 0;
     bool first = true;
-    // Debugging aid (L2B_EAGER_CHECK=1, used by l2b_generate outside graph capture): wait after every launch and name
-    // the first one that fails.
-    const bool eager = env_long("L2B_EAGER_CHECK", 0) != 0;
-    auto checked = [&](const char* what) -> int32_t {
-        if (!eager) return L2B_OK;
-        cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
-        if (cudaStreamIsCapturing(s->stream, &cs) != cudaSuccess || cs != cudaStreamCaptureStatusNone) return L2B_OK;
-        cudaError_t e = cudaStreamSynchronize(s->stream);
-        if (e != cudaSuccess) return fail(L2B_ERR_CUDA, std::string("launch ") + std::to_string(count) + " (" + what + ", nb=" + std::to_string(nb) + "): " + cudaGetErrorString(e));
-        return L2B_OK;
-    };
     auto mv = [&](MvLaunch& L) -> int32_t {
         L.planes = m->planes;
         L.nb = nb;
         L2B_TRY(plan_matvec(L, s->di));
         if (!L.kq) s->all_kquant = false;
+#ifdef L2B_MEASURE
         if (s->trace) L.p.trace = s->trace + (size_t)(s->trace_launches++) * s->di.sms * 16;
+#endif
         CU(launch_matvec(L, s->stream, !first));
         last_grid = L.grid;
         first = false;
         ++count;
-        L2B_TRY(checked(L.p.seg[0].epi == EPI_ROPE_Q ? "qkv" : L.p.seg[0].epi == EPI_SWIGLU ? "gate/up" : L.p.seg[0].epi == EPI_LOGITS ? "logits" : (L.p.n_in == c.dim / m->tp ? "wo" : "down")));
         return L2B_OK;
     };
     auto base_params = [&](MvLaunch& L, int n_in) {
@@ -970,7 +965,6 @@ static int32_t enqueue_token(l2b_session* s, int* nlaunch, int nb = 1) {
             a.min_chunk = (int)env_long("L2B_ATTN_MIN_CHUNK", 0);
             CU(launch_attention(a, s->gq, s->stream, true));
             ++count;
-            L2B_TRY(checked("attention"));
         }
         // --- output projection + residual (inference.jl:281-284)
         {
@@ -1011,6 +1005,7 @@ static int32_t enqueue_token(l2b_session* s, int* nlaunch, int nb = 1) {
     if (nb == 2) {  // both positions are followed by prompt tokens: no classifier, no sampling, move on by two
         AdvanceParams ap;
         ap.ctl = s->ctl; ap.prompt = s->prompt; ap.out_tokens = s->out_tokens; ap.epoch = s->tp_epoch;
+        ap.vocab = c.vocab_size; ap.status = s->status;
         CU(launch_kernel(advance_pair_kernel, dim3(1), dim3(32), 0, s->stream, true, ap));
         ++count;
         if (nlaunch) *nlaunch = count;
@@ -1036,6 +1031,7 @@ static int32_t enqueue_token(l2b_session* s, int* nlaunch, int nb = 1) {
         f.amax_val = s->amax_val; f.amax_idx = s->amax_idx; f.nparts = last_grid;
         f.ctl = s->ctl; f.prompt = s->prompt; f.out_tokens = s->out_tokens; f.advance = 1; f.next_token = s->next_token;
         f.tp_epoch = s->tp_epoch;
+        f.status = s->status;
         CU(launch_kernel(finalize_token_kernel, dim3(1), dim3(FIN_THREADS), 0, s->stream, true, f));
         ++count;
     }
@@ -1051,7 +1047,7 @@ static cudaError_t cudaLaunchKernelEx_embed(const l2b_model* m, l2b_session* s, 
     cfg.stream = s->stream;
     return cudaLaunchKernelEx(&cfg, embed_row_kernel, m->tok_emb.type, (const uint8_t*)m->tok_emb.data, (const __half*)m->tok_emb.d6,
                               (const int*)&s->ctl->token, (int)m->cfg.dim, s->x + (second ? m->cfg.dim : 0), (const int*)(second ? s->prompt : nullptr),
-                              (const int*)&s->ctl->pos);
+                              (const int*)&s->ctl->pos, (int)m->cfg.vocab_size);
 }
 
 static int32_t capture_token_graph(l2b_session* s) {
@@ -1127,7 +1123,7 @@ extern "C" int32_t l2b_session_create(l2b_model* m, void* stream, l2b_session** 
         const int per_sm_x10 = c.seq_len >= 2048 ? 34 : 13;
         int ns = (s->di.sms * per_sm_x10 / 10 + groups - 1) / groups;
         ns = std::max(1, std::min(ns, std::min(32, (c.seq_len + 7) / 8)));
-        s->nsplit = (int)env_long("L2B_ATTN_SPLITS", ns);
+        s->nsplit = (int)std::max<long>(1, std::min<long>(32, env_long("L2B_ATTN_SPLITS", ns)));  // the merge gives a lane to each split
         const size_t kvl = kv_layer_elems(m);
         // q, att, hb and the caches hold this rank's heads / hidden units only (everything, on one GPU)
         // (two of each vector: the two-position prompt passes keep both positions' activations side by side)
@@ -1164,11 +1160,13 @@ extern "C" int32_t l2b_session_create(l2b_model* m, void* stream, l2b_session** 
         CU(cudaMalloc(&s->rope_cs, cs.size() * 4));
         CU(cudaMemcpyAsync(s->rope_cs, cs.data(), cs.size() * 4, cudaMemcpyHostToDevice, s->stream));
         CU(cudaStreamSynchronize(s->stream));
+#ifdef L2B_MEASURE
         if (env_long("L2B_TRACE_TOKEN", 0)) {
             const size_t n = (size_t)(4 * c.n_layers + 1) * s->di.sms * 16;
             CU(cudaMalloc(&s->trace, n * 8));
             CU(cudaMemset(s->trace, 0, n * 8));
         }
+#endif
         if (m->tp > 1) {
             // exchange memory; the token graph is captured by l2b_session_tp_connect, once the peers' mappings exist
             const size_t n_exch = 2 * (size_t)c.n_layers;
@@ -1254,6 +1252,10 @@ static int32_t check_status_word(l2b_session* s) {
         cudaMemsetAsync(s->status, 0, 4, s->stream);
         return fail(L2B_ERR_TIMEOUT, "the partial results of another tensor-parallel rank did not arrive in time");
     }
+    if (s->h_small[1] == DEV_ERR_BAD_INDEX) {
+        cudaMemsetAsync(s->status, 0, 4, s->stream);
+        return fail(L2B_ERR_CUDA, "no valid token could be chosen (the logits are not finite); token 0 was substituted");
+    }
     if (s->h_small[1] != DEV_OK) {
         cudaMemsetAsync(s->status, 0, 4, s->stream);
         return fail(L2B_ERR_CUDA, "kernel reported device status " + std::to_string(s->h_small[1]));
@@ -1287,6 +1289,7 @@ static int32_t run_one(l2b_session* s, int token, int pos, float temperature, do
     return check_status_word(s);
 }
 
+#ifdef L2B_MEASURE
 static void dump_token_trace(l2b_session* s) {
     const int nl = s->trace_launches, sms = s->di.sms;
     std::vector<unsigned long long> h((size_t)nl * sms * 16);
@@ -1310,11 +1313,14 @@ static void dump_token_trace(l2b_session* s) {
         if (k < 12 || k >= nl - 3) fprintf(stderr, "  launch %3d: %8.2f %8.2f %8.2f %8.2f %8.2f\n", k, st / 1e3, iss / nb / 1e3, wt / nb / 1e3, act / nb / 1e3, en / 1e3);
     }
 }
+#endif
 
 extern "C" int32_t l2b_forward(l2b_session* s, int32_t token, int32_t pos, float* host_logits) {
     if (!s) return fail(L2B_ERR_BAD_ARG, "null session");
     L2B_TRY(run_one(s, token, pos, 0.f, 0.0));
+#ifdef L2B_MEASURE
     if (s->trace) dump_token_trace(s);
+#endif
     if (host_logits) CU(cudaMemcpy(host_logits, s->logits, (size_t)s->model->cfg.vocab_size * 4, cudaMemcpyDeviceToHost));
     return L2B_OK;
 }
@@ -1393,8 +1399,7 @@ extern "C" int32_t l2b_generate(l2b_session* s, const int32_t* prompt, int32_t n
     // tokens are forced, so neither needs logits); everything else takes the one-position graph.
     for (int i = 0; i < n_positions;) {
         const bool pair = s->graph2 && i + 2 < n_prompt && i + 1 < n_positions;
-        if (env_long("L2B_EAGER_CHECK", 0)) L2B_TRY(enqueue_token(s, nullptr, pair ? 2 : 1));  // debugging aid: no graph, a wait per launch
-        else CU(cudaGraphLaunch(pair ? s->graph2 : s->graph, s->stream));
+        CU(cudaGraphLaunch(pair ? s->graph2 : s->graph, s->stream));
         i += pair ? 2 : 1;
     }
     CU(cudaEventRecord(s->ev1, s->stream));
@@ -1513,26 +1518,38 @@ static int32_t run_export(MvParams& p, bool kq, int planes, int8_t* q_out, float
     return L2B_OK;
 }
 
-extern "C" int32_t l2b_quantize_q8k(const float* host_x, int64_t n, int32_t planes, int8_t* host_q, float* host_d, float* host_sums) {
+static int32_t quantize_planes(const float* host_x, const float* host_w, int64_t n, int32_t planes, int8_t* host_q, float* host_d, float* host_sums) {
     if (!host_x || !host_q || !host_d || !host_sums) return fail(L2B_ERR_BAD_ARG, "null argument");
     if (n <= 0 || n % QK_K != 0) return fail(L2B_ERR_BAD_ARG, "n must be a positive multiple of 256");
     if (planes < 1 || planes > 3) return fail(L2B_ERR_BAD_ARG, "planes must be 1..3");
     L2B_TRY(require_device());
-    DevBuf x, q, d, sums;
+    DevBuf x, w, q, d, sums;
     L2B_TRY(dev_upload(x, host_x, (size_t)n * 4));
+    if (host_w) L2B_TRY(dev_upload(w, host_w, (size_t)n * 4));
     L2B_TRY(dev_alloc(q, (size_t)planes * n));
     L2B_TRY(dev_alloc(d, (size_t)planes * (n / QK_K) * 4));
     L2B_TRY(dev_alloc(sums, (size_t)(n / 16) * 4));
     MvParams p;
     memset(&p, 0, sizeof(p));
     p.n_in = (int)n;
-    p.pro = PRO_COPY;
+    p.pro = host_w ? PRO_RMSNORM : PRO_COPY;
     p.x_in = x.as<float>();
+    p.gain = host_w ? w.as<float>() : nullptr;
     L2B_TRY(run_export(p, true, planes, q.as<int8_t>(), d.as<float>(), sums.as<float>(), nullptr));
     CU(cudaMemcpy(host_q, q.p, (size_t)planes * n, cudaMemcpyDeviceToHost));
     CU(cudaMemcpy(host_d, d.p, (size_t)planes * (n / QK_K) * 4, cudaMemcpyDeviceToHost));
     CU(cudaMemcpy(host_sums, sums.p, (size_t)(n / 16) * 4, cudaMemcpyDeviceToHost));
     return L2B_OK;
+}
+
+extern "C" int32_t l2b_quantize_q8k(const float* host_x, int64_t n, int32_t planes, int8_t* host_q, float* host_d, float* host_sums) {
+    return quantize_planes(host_x, nullptr, n, planes, host_q, host_d, host_sums);
+}
+
+extern "C" int32_t l2b_rmsnorm_quantize_q8k(const float* host_x, const float* host_w, int64_t n, int32_t planes, int8_t* host_q, float* host_d,
+                                            float* host_sums) {
+    if (!host_w) return fail(L2B_ERR_BAD_ARG, "null argument");
+    return quantize_planes(host_x, host_w, n, planes, host_q, host_d, host_sums);
 }
 
 extern "C" int32_t l2b_rmsnorm(float* host_o, const float* host_x, const float* host_w, int64_t n) {
@@ -1560,12 +1577,26 @@ extern "C" int32_t l2b_rope(float* host_x, int32_t hs, int32_t n_heads, int32_t 
     L2B_TRY(require_device());
     std::vector<float> cs;
     rope_table_host(cs, pos + 1, hs, base);
-    DevBuf x, row;
-    L2B_TRY(dev_upload(x, host_x, (size_t)hs * n_heads * 4));
-    L2B_TRY(dev_upload(row, cs.data() + (size_t)pos * hs, (size_t)hs * 4));
-    rope_kernel<<<(n_heads * hs / 2 + 255) / 256, 256>>>(x.as<float>(), hs, n_heads, neox, row.as<float>());
+    DevBuf x, y, table;
+    const size_t n = (size_t)hs * n_heads;
+    L2B_TRY(dev_upload(x, host_x, n * 4));
+    L2B_TRY(dev_alloc(y, n * 4));
+    L2B_TRY(dev_upload(table, cs.data(), cs.size() * 4));
+    // the token path's own epilogue (EPI_ROPE_Q of the q projection) on the given vector
+    MvParams p;
+    memset(&p, 0, sizeof(p));
+    p.nseg = 1;
+    p.seg[0].npairs = (int)(n / 2);
+    p.seg[0].pair_mode = neox ? PAIR_NEOX : PAIR_ADJACENT;
+    p.seg[0].epi = EPI_ROPE_Q;
+    p.seg[0].out = y.as<float>();
+    p.seg[0].head_size = hs;
+    p.neox_magic = (unsigned)((0x100000000ull + hs / 2 - 1) / (hs / 2));
+    p.rope_cs = table.as<float>();
+    p.seq_len = pos + 1;
+    epilogue_probe_kernel<<<(int)std::min<size_t>(1024, (n / 2 + 255) / 256), 256>>>(p, x.as<float>(), nullptr, pos);
     CU(cudaGetLastError());
-    CU(cudaMemcpy(host_x, x.p, (size_t)hs * n_heads * 4, cudaMemcpyDeviceToHost));
+    CU(cudaMemcpy(host_x, y.p, n * 4, cudaMemcpyDeviceToHost));
     return L2B_OK;
 }
 
@@ -1606,15 +1637,24 @@ extern "C" int32_t l2b_attention(float* host_out, const float* host_q, const flo
 }
 
 extern "C" int32_t l2b_swiglu(float* host_hb, const float* host_hb2, int64_t n) {
-    if (!host_hb || !host_hb2 || n < 0) return fail(L2B_ERR_BAD_ARG, "null argument");
+    if (!host_hb || !host_hb2 || n < 0 || n > 0x7fffffff) return fail(L2B_ERR_BAD_ARG, "null argument or bad length");
     L2B_TRY(require_device());
     if (n == 0) return L2B_OK;
-    DevBuf a, b;
+    DevBuf a, b, o;
     L2B_TRY(dev_upload(a, host_hb, (size_t)n * 4));
     L2B_TRY(dev_upload(b, host_hb2, (size_t)n * 4));
-    swiglu_kernel<<<(int)std::min<int64_t>(1024, (n + 255) / 256), 256>>>(a.as<float>(), b.as<float>(), n);
+    L2B_TRY(dev_alloc(o, (size_t)n * 4));
+    // the token path's own epilogue (EPI_SWIGLU of the gate / up projections) on the given vectors
+    MvParams p;
+    memset(&p, 0, sizeof(p));
+    p.nseg = 1;
+    p.seg[0].npairs = (int)n;
+    p.seg[0].pair_mode = PAIR_DUAL;
+    p.seg[0].epi = EPI_SWIGLU;
+    p.seg[0].out = o.as<float>();
+    epilogue_probe_kernel<<<(int)std::min<int64_t>(1024, (n + 255) / 256), 256>>>(p, a.as<float>(), b.as<float>(), 0);
     CU(cudaGetLastError());
-    CU(cudaMemcpy(host_hb, a.p, (size_t)n * 4, cudaMemcpyDeviceToHost));
+    CU(cudaMemcpy(host_hb, o.p, (size_t)n * 4, cudaMemcpyDeviceToHost));
     return L2B_OK;
 }
 
@@ -1662,7 +1702,9 @@ extern "C" int32_t l2b_sample_temperature(const float* host_logits, int64_t n, f
 // ---------------------------------------------------------------------------------------------
 // resident matrices
 // ---------------------------------------------------------------------------------------------
-static unsigned long long* g_trace = nullptr;  // set only by the L2B_MV_TRACE debugging path
+#ifdef L2B_MEASURE
+static unsigned long long* g_trace = nullptr;  // set only by the L2B_MV_TRACE measurement path
+#endif
 
 struct l2b_matrix {
     std::vector<DevMatrix> copies;
@@ -1716,7 +1758,9 @@ extern "C" int32_t l2b_matrix_matvec_device(l2b_matrix* m, int32_t copy, const f
     L.p.pro = PRO_COPY;
     L.p.x_in = dev_x;
     L.p.status = m->status;
+#ifdef L2B_MEASURE
     L.p.trace = g_trace;
+#endif
     L2B_TRY(plan_matvec(L, m->di));
     CU(launch_matvec(L, (cudaStream_t)stream, false));
     return L2B_OK;
@@ -1732,7 +1776,8 @@ extern "C" int32_t l2b_matrix_matvec(l2b_matrix* m, const float* host_x, int32_t
     for (int c = 0; c < ncols; ++c)
         L2B_TRY(l2b_matrix_matvec_device(m, 0, x.as<float>() + (size_t)c * w.in, y.as<float>() + (size_t)c * w.out, planes, nullptr));
     CU(cudaDeviceSynchronize());
-    if (env_long("L2B_MV_TRACE", 0)) {  // debugging aid: per-block timeline of one more launch, printed to stderr
+#ifdef L2B_MEASURE
+    if (env_long("L2B_MV_TRACE", 0)) {  // measurement aid: per-block timeline of one more launch, printed to stderr
         DevBuf tr;
         const int NT = 16;
         L2B_TRY(dev_alloc(tr, (size_t)m->di.sms * NT * 8));
@@ -1755,6 +1800,7 @@ extern "C" int32_t l2b_matrix_matvec(l2b_matrix* m, const float* host_x, int32_t
         fprintf(stderr, "[l2b trace] ns since first block start (avg/max): start %.0f/%.0f barriers-ready %.0f issued %.0f/%.0f waited %.0f/%.0f act %.0f/%.0f end %.0f/%.0f | tiles/block %llu\n",
                 av[0], mx[0], av[7], av[1], mx[1], av[2], mx[2], av[3], mx[3], av[6], mx[6], h[14]);
     }
+#endif
     int hst = 0;
     CU(cudaMemcpy(&hst, m->status, 4, cudaMemcpyDeviceToHost));
     if (hst != DEV_OK) {

@@ -71,12 +71,20 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity
     return false;
 }
 
-// The same wait for a whole warp: one lane polls, the result is broadcast.  (Thirty-two lanes of every warp
-// polling one shared-memory word slow down the arrival they are waiting for.)
-__device__ __forceinline__ bool mbar_wait_bounded_warp(uint64_t* bar, uint32_t parity, int lane) {
-    int ok = 1;
-    if (lane == 0) ok = mbar_wait_bounded(bar, parity) ? 1 : 0;
-    return __shfl_sync(0xffffffffu, ok, 0) != 0;
+// The same wait bounded by TIME (nanoseconds of %globaltimer) instead of by polls: for warps whose partner may itself be
+// inside a long, legitimate wait (the tensor-parallel wait for another GPU's partial results).
+__device__ __forceinline__ bool mbar_wait_bounded_ns(uint64_t* bar, uint32_t parity, unsigned long long limit_ns) {
+    unsigned long long t0 = 0;
+    for (uint32_t i = 0;; ++i) {
+        if (mbar_test_wait(bar, parity)) return true;
+        if (i > 64) __nanosleep(64);
+        if ((i & 1023u) == 1023u) {
+            unsigned long long t;
+            asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+            if (t0 == 0) t0 = t;
+            else if (t - t0 > limit_ns) return false;
+        }
+    }
 }
 
 // L2 policy for weight bytes: they are read once per token, so they should not evict the
@@ -101,13 +109,6 @@ __device__ __forceinline__ void bulk_g2s(void* dst_smem, const void* src_gmem, u
 // and wait until the previous kernel's memory is visible.
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
-
-// dp4a with unsigned 8-bit weights and signed 8-bit activations.
-__device__ __forceinline__ int dp4a_us(uint32_t a_u8x4, int b_s8x4, int c) {
-    int d;
-    asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a_u8x4), "r"(b_s8x4), "r"(c));
-    return d;
-}
 
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll

@@ -730,6 +730,13 @@ __global__ void __launch_bounds__((MV_MAX_CONSUMERS + 2) * 32, 1) fused_matvec_k
     uint64_t* red_full = empty + MV_MAX_SLOTS;
     uint64_t* red_empty = red_full + MV_RED_BUFS;
     uint8_t* ring = smem + L.off_ring;
+    // Waits of the producer and finisher warps on the consumer warps.  With tensor parallelism the consumers may themselves
+    // be waiting, legitimately and for up to tp_timeout_ms, for another GPU's partial results: those waits are then bounded
+    // by that time plus a margin instead of by the short poll budget, which host-side skew between the ranks would exhaust.
+    auto wait_partner = [&](uint64_t* bar, uint32_t parity) -> bool {
+        if (TP && p.tp) return mbar_wait_bounded_ns(bar, parity, ((unsigned long long)p.tp->tp_timeout_ms + 1000ull) * 1000000ull);
+        return mbar_wait_bounded(bar, parity);
+    };
 
     if (KQ) {
         if (threadIdx.x < NS) {
@@ -820,7 +827,7 @@ __global__ void __launch_bounds__((MV_MAX_CONSUMERS + 2) * 32, 1) fused_matvec_k
                 // wait until every consumer warp of the group has released what this slot held before
                 if (ph > 0) {
                     int ok = 1;
-                    if (c == 0) ok = mbar_wait_bounded(empty + slot_i, (uint32_t)((ph & 1) ^ 1)) ? 1 : 0;
+                    if (c == 0) ok = wait_partner(empty + slot_i, (uint32_t)((ph & 1) ^ 1)) ? 1 : 0;
                     ok = __shfl_sync(0x0000ffffu, ok, 0);
                     if (!ok) {
                         dead = true;
@@ -903,7 +910,7 @@ __global__ void __launch_bounds__((MV_MAX_CONSUMERS + 2) * 32, 1) fused_matvec_k
                 pre0 = epilogue_preload(p, sg, t, pos);
                 if (NB == 2) pre1 = epilogue_preload(p, sg, t, pos + 1, 1);
             }
-            if (!mbar_wait_bounded(red_full + rb, par)) {
+            if (!wait_partner(red_full + rb, par)) {
                 dead = true;
                 break;
             }

@@ -37,7 +37,18 @@ struct FinalizeParams {
     int advance;        // 1: ctl->token = next, ctl->pos += 1
     int* next_token;    // single-slot result for one-step calls
     unsigned* tp_epoch; // tensor parallelism: count of completed tokens, advanced here (null on one GPU)
+    int* status;        // device status word: DEV_ERR_BAD_INDEX when no valid token could be chosen (may be null)
 };
+
+// The chosen token must be a row of the embedding table.  All-NaN logits (one NaN or Inf anywhere upstream, e.g. a corrupt
+// fp16 scale in a model file) leave the argmax at its start value; the next embedding lookup would then read far outside the
+// table.  Such a token is replaced by 0 and reported through the status word, so that the host call fails while every
+// access of the launches already enqueued stays in bounds.
+__device__ __forceinline__ int checked_token(int tok, int vocab, int* status) {
+    if (tok >= 0 && tok < vocab) return tok;
+    if (status) atomicExch(status, DEV_ERR_BAD_INDEX);
+    return 0;
+}
 
 constexpr int FIN_THREADS = 1024;
 
@@ -133,10 +144,11 @@ __global__ void __launch_bounds__(FIN_THREADS) finalize_token_kernel(const __gri
         __syncthreads();
     }
     if (tid == 0) {
-        int next = s_choice;
-        if (pos + 1 < p.ctl->n_prompt && p.prompt) next = p.prompt[pos + 1];
+        const int choice = checked_token(s_choice, p.vocab, p.status);
+        int next = choice;
+        if (pos + 1 < p.ctl->n_prompt && p.prompt) next = checked_token(p.prompt[pos + 1], p.vocab, p.status);
         if (p.out_tokens) p.out_tokens[pos] = next;
-        if (p.next_token) *p.next_token = s_choice;
+        if (p.next_token) *p.next_token = choice;
         if (p.advance) {
             p.ctl->token = next;
             p.ctl->pos = pos + 1;
@@ -152,6 +164,8 @@ struct AdvanceParams {
     const int* prompt;
     int* out_tokens;
     unsigned* epoch;
+    int vocab;
+    int* status;
 };
 __global__ void advance_pair_kernel(const __grid_constant__ AdvanceParams a) {
     Control* ctl = a.ctl;
@@ -162,7 +176,7 @@ __global__ void advance_pair_kernel(const __grid_constant__ AdvanceParams a) {
     pdl_wait();
     if (threadIdx.x == 0) {
         const int pos = ctl->pos;
-        const int t1 = prompt[pos + 1], t2 = prompt[pos + 2];
+        const int t1 = checked_token(prompt[pos + 1], a.vocab, a.status), t2 = checked_token(prompt[pos + 2], a.vocab, a.status);
         if (out_tokens) {
             out_tokens[pos] = t1;
             out_tokens[pos + 1] = t2;

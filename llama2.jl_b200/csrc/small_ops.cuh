@@ -1,6 +1,6 @@
-// Small kernels behind the isolated-operator entry points and the upload path.  They call the
-// same device functions as the fused decode kernels, so a parity test of an entry point is a
-// parity test of the arithmetic the token path uses.
+// Small kernels behind the isolated-operator entry points and the upload path.  Dequantisation, the activation
+// prologue (export_activation_kernel) and the epilogues (epilogue_probe_kernel: RoPE, SwiGLU) call the very device
+// functions the fused decode kernels call, so a parity test of those entry points tests the token path's arithmetic.
 #pragma once
 #include "fused_matvec.cuh"
 
@@ -53,15 +53,19 @@ __global__ void dequantize_kernel(int type, const uint8_t* __restrict__ blocks, 
 // x = dequantize!(x, token_embedding_table[:, token]) (src/inference.jl:236): the first kernel of a token.
 // `token` is a device scalar.  For f32 tables the row is copied.
 // `prompt` non-null: the row of the NEXT prompt token, prompt[*pos + 1] (second position of a two-position pass).
+// A token id outside [0, vocab) gives a row of zeros (the table is never read out of bounds).
 __global__ void embed_row_kernel(int type, const uint8_t* __restrict__ table, const __half* __restrict__ d6, const int* token, int n, float* __restrict__ x,
-                                 const int* prompt, const int* pos) {
+                                 const int* prompt, const int* pos, int vocab) {
     pdl_launch_dependents();
     pdl_wait();
     const int tok = prompt ? __ldcg(prompt + __ldcg(pos) + 1) : __ldcg(token);
+    const bool valid = tok >= 0 && tok < vocab;
     const int nb = n / QK_K;
     for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
         float v;
-        if (type == T_F32) {
+        if (!valid) {
+            v = 0.f;
+        } else if (type == T_F32) {
             v = reinterpret_cast<const float*>(table)[(size_t)tok * n + i];
         } else {
             const int b = i >> 8, k = i & 255;
@@ -100,24 +104,19 @@ __global__ void __launch_bounds__(256) export_activation_kernel(const __grid_con
     }
 }
 
-// rope! on a [n_heads][hs] vector through the epilogue's rotation.
-__global__ void rope_kernel(float* x, int hs, int n_heads, int neox, const float* rope_cs_row) {
-    const int h2 = hs >> 1;
-    for (int t = blockIdx.x * blockDim.x + threadIdx.x; t < n_heads * h2; t += gridDim.x * blockDim.x) {
-        const int head = t / h2, i = t % h2;
-        const int ia = head * hs + (neox ? i : 2 * i), ib = head * hs + (neox ? i + h2 : 2 * i + 1);
-        const float vA = x[ia], vB = x[ib];
-        const float c = rope_cs_row[2 * i], s = rope_cs_row[2 * i + 1];
-        x[ia] = __fsub_rn(__fmul_rn(vA, c), __fmul_rn(vB, s));
-        x[ib] = __fadd_rn(__fmul_rn(vA, s), __fmul_rn(vB, c));
-    }
-}
-
-__global__ void swiglu_kernel(float* hb, const float* hb2, int64_t n) {
-    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
-        const float v = hb[i];
-        const float g = v * (1.0f / (1.0f + expf(-v)));
-        hb[i] = g * hb2[i];
+// Runs the fused kernel's epilogue (epilogue_pair, with the operands preloaded as the finisher warp does) on given
+// matvec results: pair t of segment 0 takes vin[rowA], vin[rowB] (adjacent / NeoX pairs) or vin[t], vin2[t] (gate / up).
+// Behind l2b_rope (EPI_ROPE_Q) and l2b_swiglu (EPI_SWIGLU).
+__global__ void epilogue_probe_kernel(const __grid_constant__ MvParams p, const float* __restrict__ vin, const float* __restrict__ vin2, int pos) {
+    const MvSegment sg = p.seg[0];
+    ArgBest best;
+    best.v = -INFINITY;
+    best.i = 0x7fffffff;
+    for (int t = blockIdx.x * blockDim.x + threadIdx.x; t < sg.npairs; t += gridDim.x * blockDim.x) {
+        const EpiPre pre = epilogue_preload(p, sg, t, pos);
+        const float vA = sg.pair_mode == PAIR_DUAL ? vin[t] : vin[pre.rowA];
+        const float vB = sg.pair_mode == PAIR_DUAL ? vin2[t] : vin[pre.rowB];
+        epilogue_pair<false, true>(p, sg, t, vA, vB, pos, best, 0, &pre);
     }
 }
 

@@ -1,11 +1,12 @@
-// Seeded synthetic data for tests and benchmarks: counter-based, integer arithmetic only, so
+// Seeded synthetic data for tests and benchmarks (libl2b_synth.so; not part of the product library): counter-based, integer arithmetic only, so
 // the same seed gives the same bytes on every machine and compiler.
 #include <cstdint>
 #include <cstring>
 #include <thread>
 #include <vector>
 
-#include "../../include/llama2_b200.h"
+#include "../../include/l2b_synth.h"
+#include "../../include/llama2_b200.h"  // status and tensor-type enums only
 
 namespace {
 

@@ -1,5 +1,5 @@
 """Seeded synthetic weights, prompts and configurations of the benchmark shapes.  All bytes come from the
-library's counter-based generators (l2b_synth_*), so every machine builds the same model from a seed."""
+counter-based generators of the test-support library (libl2b_synth.so, include/l2b_synth.h), so every machine builds the same model from a seed."""
 import numpy as np
 
 from . import _lib as L
@@ -10,19 +10,19 @@ Q4, Q5, Q6, F32 = L.TYPE_Q4_K, L.TYPE_Q5_K, L.TYPE_Q6_K, L.TYPE_F32
 
 def normal_f32(n, seed, std):
     a = np.empty(int(n), dtype=np.float32)
-    L.check(L.lib().l2b_synth_f32(L.ptr(a), a.size, int(seed), float(std), 0))
+    L.synth_check(L.synth_lib().l2b_synth_f32(L.ptr(a), a.size, int(seed), float(std), 0))
     return a
 
 
 def kquant_bytes(ggml_type, n_blocks, seed):
     a = np.empty(int(n_blocks) * L.BLOCK_BYTES[ggml_type], dtype=np.uint8)
-    L.check(L.lib().l2b_synth_kquant(ggml_type, L.ptr(a), int(n_blocks), int(seed)))
+    L.synth_check(L.synth_lib().l2b_synth_kquant(ggml_type, L.ptr(a), int(n_blocks), int(seed)))
     return a
 
 
 def tokens(n, seed, lo, hi):
     a = np.empty(int(n), dtype=np.int32)
-    L.check(L.lib().l2b_synth_tokens(L.ptr(a), a.size, int(seed), int(lo), int(hi)))
+    L.synth_check(L.synth_lib().l2b_synth_tokens(L.ptr(a), a.size, int(seed), int(lo), int(hi)))
     return a
 
 

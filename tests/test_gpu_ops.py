@@ -188,7 +188,7 @@ def test_rope_bit_exact(L, orc, neox, hs, heads, pos):
 
 
 @pytest.mark.parametrize("n_heads,n_kv,hs", [(6, 6, 48), (32, 8, 128), (32, 32, 96), (64, 8, 128), (12, 4, 64)])
-@pytest.mark.parametrize("npos", [1, 2, 37, 512])
+@pytest.mark.parametrize("npos", [1, 2, 37, 512, 4096])
 def test_attention(L, orc, n_heads, n_kv, hs, npos):
     rng = np.random.default_rng(42)
     q = rng.normal(size=(n_heads * hs)).astype(np.float32)

@@ -19,6 +19,12 @@ def test_library_exports_every_declared_symbol(pkg):
     lib = L.lib()
     for name in declared:
         assert getattr(lib, name) is not None
+    synth_header = open(os.path.join(ROOT, "include", "l2b_synth.h")).read()
+    synth_declared = sorted(set(re.findall(r"\b(l2b_[a-z0-9_]+)\s*\(", synth_header)))
+    assert synth_declared == sorted(L._SYNTH_SIGNATURES)
+    for name in synth_declared:
+        assert getattr(L.synth_lib(), name) is not None
+        assert not hasattr(lib, name), "the synthetic-data generators are test support and stay out of the product library"
     assert lib.l2b_version() >= 100
     assert lib.l2b_status_string(L.ERR_TIMEOUT).decode() == "device-side wait timed out"
 

@@ -54,7 +54,7 @@ def _noalloc(L, torch, q, kc, vc, n_heads, n_kv, hs, npos, seq_len):
 
 
 @pytest.mark.parametrize("n_heads,n_kv,hs,npos,seq_len", [(32, 8, 128, 300, 512), (6, 6, 48, 5, 16), (64, 8, 128, 512, 512), (12, 4, 64, 37, 64)])
-def test_noalloc_matches_existing_entry_point_twice(L, n_heads, n_kv, hs, npos, seq_len):
+def test_noalloc_matches_existing_entry_point_twice(L, orc, n_heads, n_kv, hs, npos, seq_len):
     import torch
 
     # two calls in a row with DIFFERENT inputs: the second must not see anything the first left in the scratch array
@@ -64,6 +64,30 @@ def test_noalloc_matches_existing_entry_point_twice(L, n_heads, n_kv, hs, npos, 
         got = _noalloc(L, torch, q, kc, vc, n_heads, n_kv, hs, npos, seq_len)
         assert np.isfinite(got).all()
         assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+        # and against the CPU oracle (attention_weights!, softmax!, combine_values!), to the tolerance of the attention tests
+        ref = orc.attention(q, k, v, n_heads, n_kv, hs)
+        assert np.abs(got - ref).max() <= 2e-5 * max(1.0, float(np.abs(ref).max()))
+
+
+def test_noalloc_leaves_device_memory_untouched(L):
+    """After the first call on the device (which resolves the scratch array's address), a call must not change the amount
+    of free device memory: it allocates nothing and frees nothing."""
+    import torch
+
+    n_heads, n_kv, hs, npos, seq_len = 32, 8, 128, 200, 256
+    q, k, v, kc, vc = _case(3, n_heads, n_kv, hs, npos, seq_len)
+    dq, dk, dv = (torch.from_numpy(a).cuda() for a in (q, kc, vc))
+    dout = torch.zeros(n_heads * hs, device="cuda", dtype=torch.float32)
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    call = lambda: L.check(L.lib().l2b_attention_device_noalloc(_dev(dout), _dev(dq), _dev(dk), _dev(dv), npos, seq_len, n_heads, n_kv, hs, stream))
+    call()  # first call on this device in this process, or not: either way set-up is done after it
+    torch.cuda.synchronize()
+    free0, _ = torch.cuda.mem_get_info()
+    for _ in range(3):
+        call()
+    torch.cuda.synchronize()
+    free1, _ = torch.cuda.mem_get_info()
+    assert free0 == free1
 
 
 def test_noalloc_after_a_smaller_and_a_larger_shape(L):
