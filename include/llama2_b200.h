@@ -32,6 +32,7 @@ extern "C" {
 typedef struct l2b_model l2b_model;     /* TransformerWeights + ModelConfig on the device */
 typedef struct l2b_session l2b_session; /* RunState: activations, KV cache, captured token graph */
 typedef struct l2b_matrix l2b_matrix;   /* one weight matrix resident on the device */
+typedef struct l2b_tokenizer l2b_tokenizer; /* BPETokenizer (src/tokenizer.jl:3-9), host memory only */
 
 enum l2b_status {
     L2B_OK = 0,
@@ -120,6 +121,28 @@ int32_t l2b_model_load_gguf(const char* path, int32_t seq_len, int32_t act_plane
  * number of tensors, context length.  Fails with L2B_ERR_BAD_ARG ("Not a GGUF file", :89) on anything else. */
 int32_t l2b_gguf_inspect(const char* path, l2b_config* config_out, int32_t* arch_out, int64_t* n_tensors, int64_t* context_length);
 
+/* ---- tokenizer (host only; ids are 0-based here, bos / eos included) ------------------------------------
+ * BPETokenizer (src/tokenizer.jl:3-9) from a vocabulary as a file stores it: token i is
+ * token_bytes[offsets[i] .. offsets[i+1]); scores may be NULL (all 0); token_types (LLAMA_TOKEN_TYPE, src/load_gguf.jl:44-52)
+ * may be NULL when model == 0.  model selects the fix-ups load_gguf_model applies (src/load_gguf.jl:345-368):
+ *   0 none (a llama2.c tokenizer.bin, src/load_karpathy.jl:58-78); 1 "llama": U+2581 becomes a space in NORMAL tokens and
+ *   BYTE tokens "<0xNN>" become the byte; 2 "gpt2": NORMAL tokens go through the inverse of GPT-2's byte encoder (:196-209). */
+int32_t l2b_tokenizer_create(const uint8_t* token_bytes, const int64_t* offsets, int32_t n_tokens, const float* scores,
+                             const int32_t* token_types, int32_t model, int32_t bos_id, int32_t eos_id, l2b_tokenizer** tokenizer);
+/* The tokenizer part of load_gguf_model (src/load_gguf.jl:339-380): tokenizer.ggml.{tokens,token_type,model,scores,
+ * bos_token_id,eos_token_id} read from the file by the library's own GGUF parser. */
+int32_t l2b_tokenizer_load_gguf(const char* path, l2b_tokenizer** tokenizer);
+int32_t l2b_tokenizer_destroy(l2b_tokenizer* tokenizer);
+int32_t l2b_tokenizer_info(const l2b_tokenizer* tokenizer, int32_t* n_tokens, int32_t* bos_id, int32_t* eos_id);
+/* id_to_token[id] after the fix-ups (what `sample` prints, src/inference.jl:375-382): a pointer into the tokenizer, valid
+ * until it is destroyed; tokens may hold any bytes. */
+int32_t l2b_tokenizer_token(const l2b_tokenizer* tokenizer, int32_t id, const uint8_t** bytes, int64_t* n_bytes);
+/* encode(text, tokenizer; pad_input) (src/tokenizer.jl:11-57).  *n_out receives the number of tokens; when that exceeds
+ * `capacity` nothing is written and L2B_ERR_BAD_ARG is returned (n_bytes + 1 always suffices).  A byte of the text (or the
+ * space of pad_input) without a token of its own is L2B_ERR_BAD_ARG, where the reference raises a KeyError. */
+int32_t l2b_tokenizer_encode(const l2b_tokenizer* tokenizer, const uint8_t* text, int64_t n_bytes, int32_t pad_input,
+                             int32_t* ids_out, int64_t capacity, int64_t* n_out);
+
 /* ---- tensor parallelism (no counterpart in the reference, which runs on one CPU) ------
  * One process per GPU; every rank creates its model with the same l2b_config except tp_rank, uploads the FULL tensors
  * (the library keeps its shard: whole kv groups of wq/wk/wv, hidden units of w1/w3, super-block columns of wo/w2; needs
@@ -162,6 +185,9 @@ int32_t l2b_session_logits(l2b_session* session, float* host_logits);
 int32_t l2b_session_read(l2b_session* session, int32_t which, float* host_out, int64_t capacity, int64_t* n);
 /* Device time (ms, CUDA events on the session stream) of the most recent forward/decode/generate call. */
 int32_t l2b_session_last_device_ms(l2b_session* session, float* ms);
+/* The same for the most recent l2b_generate call, split where the loop of `sample` stops being teacher-forced
+ * (src/inference.jl:354-356): positions 0 .. n_prompt-1 (fed prompt tokens) and positions n_prompt .. (fed generated tokens). */
+int32_t l2b_session_last_phase_ms(l2b_session* session, float* prompt_ms, float* decode_ms);
 /* The prompt phase of `sample` (src/inference.jl:349-356, where the reference runs transformer! once per prompt token) as one
  * call: feeds tokens[0..n-1] at positions pos0 .. pos0+n-1, two positions per pass where both are followed by a prompt token.
  * Afterwards the session holds the logits of the last prompt position (l2b_session_logits); *next (may be NULL) is their argmax.
@@ -171,7 +197,8 @@ int32_t l2b_prefill(l2b_session* session, const int32_t* tokens, int32_t n, int3
  * shared memory; switch off with L2B_PREFILL_PAIRS=0): positions p, p+1 that are both followed by a prompt token share one pass
  * over the weights, and no logits are computed for them.  The reference feeds prompts token by token (src/inference.jl:349-356). */
 int32_t l2b_session_prefill_pairs(l2b_session* session, int32_t* enabled);
-/* Number of kernel launches the captured token graph contains. */
+/* Number of kernel launches per token: 1 when the whole token is one persistent kernel (k-quant model on one GPU), else
+ * 5 per layer + 3. */
 int32_t l2b_session_kernels_per_token(l2b_session* session, int32_t* n);
 
 /* ---- isolated operators (host buffers in, host buffers out) ------------------------ */

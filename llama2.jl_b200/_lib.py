@@ -54,6 +54,7 @@ _SIGNATURES = {
     "l2b_session_logits": ([_P, _P], C.c_int32),
     "l2b_session_read": ([_P, C.c_int32, _P, C.c_int64, C.POINTER(C.c_int64)], C.c_int32),
     "l2b_session_last_device_ms": ([_P, C.POINTER(C.c_float)], C.c_int32),
+    "l2b_session_last_phase_ms": ([_P, C.POINTER(C.c_float), C.POINTER(C.c_float)], C.c_int32),
     "l2b_session_kernels_per_token": ([_P, C.POINTER(C.c_int32)], C.c_int32),
     "l2b_dequantize": ([C.c_int32, _P, C.c_int64, _P], C.c_int32),
     "l2b_quantize_q8k": ([_P, C.c_int64, C.c_int32, _P, _P, _P], C.c_int32),
@@ -64,6 +65,12 @@ _SIGNATURES = {
     "l2b_attention": ([_P, _P, _P, _P, C.c_int32, C.c_int32, C.c_int32, C.c_int32], C.c_int32),
     "l2b_model_load_gguf": ([C.c_char_p, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32, _P, C.POINTER(_P)], C.c_int32),
     "l2b_gguf_inspect": ([C.c_char_p, _P, C.POINTER(C.c_int32), C.POINTER(C.c_int64), C.POINTER(C.c_int64)], C.c_int32),
+    "l2b_tokenizer_create": ([_P, _P, C.c_int32, _P, _P, C.c_int32, C.c_int32, C.c_int32, C.POINTER(_P)], C.c_int32),
+    "l2b_tokenizer_load_gguf": ([C.c_char_p, C.POINTER(_P)], C.c_int32),
+    "l2b_tokenizer_destroy": ([_P], C.c_int32),
+    "l2b_tokenizer_info": ([_P, C.POINTER(C.c_int32), C.POINTER(C.c_int32), C.POINTER(C.c_int32)], C.c_int32),
+    "l2b_tokenizer_token": ([_P, C.c_int32, C.POINTER(_P), C.POINTER(C.c_int64)], C.c_int32),
+    "l2b_tokenizer_encode": ([_P, _P, C.c_int64, C.c_int32, _P, C.c_int64, C.POINTER(C.c_int64)], C.c_int32),
     "l2b_prefill": ([_P, _P, C.c_int32, C.c_int32, C.POINTER(C.c_int32)], C.c_int32),
     "l2b_session_prefill_pairs": ([_P, C.POINTER(C.c_int32)], C.c_int32),
     "l2b_session_tp_handle": ([_P, _P], C.c_int32),

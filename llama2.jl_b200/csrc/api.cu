@@ -15,6 +15,7 @@
 #include "fused_matvec.cuh"
 #include "sampling.cuh"
 #include "small_ops.cuh"
+#include "token_kernel.cuh"
 
 using namespace l2b;
 
@@ -27,6 +28,8 @@ static int32_t fail(int32_t code, const std::string& msg) {
     g_last_error = msg;
     return code;
 }
+// for the other translation units of the library (tokenizer.cpp)
+int32_t l2b_internal_fail(int32_t code, const std::string& msg) { return fail(code, msg); }
 
 #define CU(call)                                                                                         \
     do {                                                                                                 \
@@ -312,6 +315,9 @@ static void set_kernel_attrs() {
         set((const void*)fused_matvec_kernel<true, 1, true>);
         set((const void*)fused_matvec_kernel<true, 2, true>);
         set((const void*)fused_matvec_kernel<true, 3, true>);
+        set((const void*)token_kernel<1>);
+        set((const void*)token_kernel<2>);
+        set((const void*)token_kernel<3>);
         set((const void*)export_activation_kernel<true, 1>);
         set((const void*)export_activation_kernel<true, 2>);
         set((const void*)export_activation_kernel<true, 3>);
@@ -460,8 +466,9 @@ struct l2b_session {
     cudaGraphExec_t graph2 = nullptr;  // two prompt positions per pass (null when the model does not qualify)
     bool all_kquant = true;            // set while the one-position graph is built
     int kernels_per_token = 0;
-    cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+    cudaEvent_t ev0 = nullptr, ev1 = nullptr, ev_mid = nullptr;
     float last_ms = 0.f;
+    float last_prompt_ms = 0.f, last_decode_ms = 0.f;  // l2b_generate: positions inside the prompt / after it
     unsigned long long* trace = nullptr;  // L2B_TRACE_TOKEN=1: per-launch, per-block timeline stamps (debugging aid)
     int trace_launches = 0;
     // tensor parallelism.  tp_mem = [n_exch][tp][dim] f32 partial vectors, then [n_exch][tp] u32 arrival counters;
@@ -471,6 +478,11 @@ struct l2b_session {
     size_t tp_flag_off = 0, tp_bytes = 0;
     unsigned* tp_epoch = nullptr;  // tokens completed (device word)
     uint8_t* peer_mem[MV_MAX_TP] = {nullptr};  // [r]: rank r's tp_mem as seen from this process ([rank] = own)
+    // one persistent kernel per token (token_kernel.cuh): k-quant models on one GPU
+    bool tk = false;
+    TkOp* tk_ops = nullptr;
+    unsigned long long* tk_sync = nullptr;
+    TkParams tkp;
     bool tp_connected = false;
     MvTp* tp_descs = nullptr;          // device array: one descriptor per tensor-parallel launch of the token
     std::vector<MvTp> tp_descs_host;   // filled while the token graph is captured, uploaded right after
@@ -819,10 +831,13 @@ static void session_free(l2b_session* s) {
     if (s->tp_mem) cudaFree(s->tp_mem);
     if (s->tp_epoch) cudaFree(s->tp_epoch);
     if (s->tp_descs) cudaFree(s->tp_descs);
+    if (s->tk_ops) cudaFree(s->tk_ops);
+    if (s->tk_sync) cudaFree(s->tk_sync);
     if (s->h_ctl) cudaFreeHost(s->h_ctl);
     if (s->h_small) cudaFreeHost(s->h_small);
     if (s->ev0) cudaEventDestroy(s->ev0);
     if (s->ev1) cudaEventDestroy(s->ev1);
+    if (s->ev_mid) cudaEventDestroy(s->ev_mid);
     if (s->own_stream && s->stream) cudaStreamDestroy(s->stream);
     delete s;
 }
@@ -1050,15 +1065,261 @@ static cudaError_t cudaLaunchKernelEx_embed(const l2b_model* m, l2b_session* s, 
                               (const int*)&s->ctl->pos, (int)m->cfg.vocab_size);
 }
 
+
+// ---- one persistent kernel per token (token_kernel.cuh) --------------------------------------------------
+// Fill the schedule of one matrix-vector operation of the token kernel (the counterpart of plan_matvec: the grid is always
+// one block per SM, 16 consumer warps in two groups).  Returns the bytes one ring slot must hold for it.
+static int32_t tk_plan(MvParams& p, int planes, int kb_layout, int sms, int& slot_bytes) {
+    p.planes = planes;
+    const int nb = p.n_in / QK_K;
+    int units = 0;
+    for (int i = 0; i < p.nseg; ++i) {
+        if (p.seg[i].type == T_F32) return fail(L2B_ERR_UNSUPPORTED_TYPE, "the token kernel takes k-quant matrices only");
+        p.seg_start[i] = units;
+        units += (p.seg[i].npairs + MV_TILE_PAIRS - 1) / MV_TILE_PAIRS;
+        if (p.seg[i].pair_mode == PAIR_NEOX) {
+            const int h2 = p.seg[i].head_size / 2;
+            if (h2 % MV_TILE_PAIRS != 0) return fail(L2B_ERR_BAD_ARG, "head_size must be a multiple of 16 for NeoX RoPE");
+            p.neox_magic = (unsigned)((0x100000000ull + h2 - 1) / h2);
+        }
+    }
+    for (int i = p.nseg; i <= MV_MAX_SEG; ++i) p.seg_start[i] = units;
+    p.units_lo = units / sms;
+    p.units_rem = units % sms;
+    p.kb = kb_layout;
+    p.nit = (nb + kb_layout - 1) / kb_layout;
+    const int kb = std::min(nb, kb_layout);
+    slot_bytes = 0;
+    for (int i = 0; i < p.nseg; ++i) {
+        mv_fill_geometry(p.seg[i], kb, p.nit);
+        slot_bytes = std::max(slot_bytes, p.seg[i].ngroups * p.seg[i].gs);
+    }
+    p.consumers = TK_CONSUMERS;
+    p.cgroups = TK_GROUPS;
+    p.turns = (p.n_in / 8 + 32 * TK_CONSUMERS - 1) / (32 * TK_CONSUMERS);
+    return L2B_OK;
+}
+
+// Build the operation table of a token and decide whether the token kernel can run this model (sets s->tk).
+static int32_t build_token_kernel(l2b_session* s) {
+    const l2b_model* m = s->model;
+    const l2b_config& c = m->cfg;
+    s->tk = false;
+    if (m->tp != 1 || env_long("L2B_TOKEN_KERNEL", 1) == 0) return L2B_OK;
+    const DevMatrix* all[] = {&m->tok_emb, &m->output};
+    for (const DevMatrix* w : all)
+        if (w->type == T_F32) return L2B_OK;
+    for (const LayerW& w : m->layers) {
+        const DevMatrix* ms[] = {&w.wq, &w.wk, &w.wv, &w.wo, &w.w1, &w.w2, &w.w3};
+        for (const DevMatrix* x : ms)
+            if (x->type == T_F32) return L2B_OK;
+    }
+    const int hs = c.dim / c.n_heads, sms = s->di.sms;
+    const size_t kvl = kv_layer_elems(m);
+    // activation planes kept in shared memory: the longest input of an operation that cannot be cut along its input
+    auto up256 = [](int v) { return (v + QK_K - 1) / QK_K * QK_K; };
+    int cap = up256(std::max(c.dim, m->l_qdim()));
+    auto chunk_of = [&](const DevMatrix& w) -> int {  // input values per operation for a residual matrix
+        if (!w.panels) return (int)w.in;
+        const int pw = w.kb * QK_K;  // a stored column panel
+        return std::max(pw, cap / pw * pw);
+    };
+    for (const LayerW& w : m->layers) cap = std::max(cap, std::max(up256(std::min<int>((int)w.wo.in, chunk_of(w.wo))), up256(std::min<int>((int)w.w2.in, chunk_of(w.w2)))));
+    std::vector<TkOp> ops;
+    int slot_bytes = 0;
+    auto new_op = [&](int kind, int wait) -> TkOp& {
+        TkOp o;
+        memset(&o, 0, sizeof(o));
+        o.kind = kind;
+        o.wait = wait;
+        ops.push_back(o);
+        return ops.back();
+    };
+    auto finish_mv = [&](TkOp& o, int kb_layout) -> int32_t {
+        int sb = 0;
+        L2B_TRY(tk_plan(o.mv, m->planes, kb_layout, sms, sb));
+        slot_bytes = std::max(slot_bytes, sb);
+        return L2B_OK;
+    };
+    auto base_mv = [&](TkOp& o, int n_in) {
+        o.mv.n_in = n_in;
+        o.mv.rope_cs = s->rope_cs;
+        o.mv.seq_len = c.seq_len;
+    };
+    // a matrix whose result is added to the residual stream; cut along its input when the input is longer than the planes
+    auto residual_ops = [&](const DevMatrix& w, const float* x_in) -> int32_t {
+        const int chunk = std::min<int>((int)w.in, chunk_of(w));
+        const int nb = (int)(w.in / QK_K), cb = chunk / QK_K, bb = dev_block_bytes(w.type);
+        const size_t panel_bytes = (size_t)w.out * w.kb * bb;
+        int first = 1;
+        for (int b0 = 0; b0 < nb; b0 += cb, first = 0) {
+            const int nbl = std::min(cb, nb - b0);
+            TkOp& o = new_op(TK_MATVEC, first);
+            base_mv(o, nbl * QK_K);
+            MvSegment sg = make_segment(w, PAIR_ADJACENT, EPI_RESIDUAL, s->x, hs);
+            if (b0 > 0) {
+                sg.w = w.data + (size_t)(b0 / w.kb) * panel_bytes;
+                if (sg.d6) sg.d6 = w.d6 + b0;
+            }
+            sg.d6_nb = nb;
+            o.mv.seg[o.mv.nseg++] = sg;
+            o.mv.resid = s->x;
+            o.mv.pro = PRO_COPY;
+            o.mv.x_in = x_in + (size_t)b0 * QK_K;
+            L2B_TRY(finish_mv(o, w.kb));
+        }
+        return L2B_OK;
+    };
+    const int rope_mode = c.rope_is_neox ? PAIR_NEOX : PAIR_ADJACENT;
+    const int gq = choose_gq(m->l_heads, m->l_kv);
+    const int groups = m->l_heads / gq;
+    const int tk_nsplit = std::max(1, std::min(32, std::min(std::max(1, sms / groups), (c.seq_len + 7) / 8)));
+    new_op(TK_EMBED, 0);
+    for (int l = 0; l < c.n_layers; ++l) {
+        const LayerW& w = m->layers[l];
+        float* kcl = s->kc + (size_t)l * kvl;
+        float* vcl = s->vc + (size_t)l * kvl;
+        {   // attention rmsnorm + q/k/v + RoPE + cache write; matrices laid out for different stage widths go to operations of their own
+            MvSegment segs[3] = {make_segment(w.wq, rope_mode, EPI_ROPE_Q, s->q, hs), make_segment(w.wk, rope_mode, EPI_ROPE_K, kcl, hs),
+                                 make_segment(w.wv, PAIR_ADJACENT, EPI_STORE_V, vcl, hs)};
+            const DevMatrix* mats[3] = {&w.wq, &w.wk, &w.wv};
+            int first = 1;
+            for (int cls = 0; cls < 2; ++cls) {
+                const int kb_layout = cls == 0 ? MV_TILE_BLOCKS : 8;
+                int n = 0;
+                for (int i = 0; i < 3; ++i) n += mats[i]->kb == kb_layout;
+                if (!n) continue;
+                TkOp& o = new_op(TK_MATVEC, first);
+                first = 0;
+                base_mv(o, c.dim);
+                for (int i = 0; i < 3; ++i)
+                    if (mats[i]->kb == kb_layout) o.mv.seg[o.mv.nseg++] = segs[i];
+                o.mv.pro = PRO_RMSNORM;
+                o.mv.gain = w.rms_att;
+                o.mv.x_in = s->x;
+                L2B_TRY(finish_mv(o, kb_layout));
+            }
+        }
+        {
+            TkOp& o = new_op(TK_ATTN, 1);
+            AttnParams& a = o.at;
+            a.q = s->q; a.kc = kcl; a.vc = vcl; a.out = s->att; a.tickets = s->tickets;
+            a.part_m = s->part_m; a.part_l = s->part_l; a.part_acc = s->part_acc;
+            a.n_heads = m->l_heads; a.n_kv = m->l_kv; a.hs = hs; a.seq_len = c.seq_len; a.nsplit = tk_nsplit;
+            a.min_chunk = (int)env_long("L2B_ATTN_MIN_CHUNK", 0);
+        }
+        L2B_TRY(residual_ops(w.wo, s->att));
+        {
+            TkOp& o = new_op(TK_MATVEC, 1);
+            base_mv(o, c.dim);
+            MvSegment g = make_segment(w.w1, PAIR_DUAL, EPI_SWIGLU, s->hb, hs);
+            g.npairs = (int)w.w1.out;
+            g.w2 = w.w3.data;
+            g.d6_2 = w.w3.d6;
+            o.mv.seg[o.mv.nseg++] = g;
+            o.mv.pro = PRO_RMSNORM;
+            o.mv.gain = w.rms_ffn;
+            o.mv.x_in = s->x;
+            if (w.w1.kb != w.w3.kb) return L2B_OK;
+            L2B_TRY(finish_mv(o, w.w1.kb));
+        }
+        L2B_TRY(residual_ops(w.w2, s->hb));
+    }
+    {
+        TkOp& o = new_op(TK_MATVEC, 1);
+        base_mv(o, c.dim);
+        o.mv.seg[o.mv.nseg++] = make_segment(m->output, PAIR_ADJACENT, EPI_LOGITS, s->logits, hs);
+        o.mv.pro = PRO_RMSNORM;
+        o.mv.gain = m->rms_final;
+        o.mv.x_in = s->x;
+        o.mv.amax_val = s->amax_val;
+        o.mv.amax_idx = s->amax_idx;
+        L2B_TRY(finish_mv(o, m->output.kb));
+    }
+    new_op(TK_FINAL, 1);
+    if ((int)ops.size() > TK_MAX_OPS) return L2B_OK;
+    const int max_total = std::min<int>((int)env_long("L2B_TK_SMEM_KB", 227) * 1024, s->di.max_smem_optin);
+    TkSmem sm = tk_smem_layout(m->planes, cap, tk_attention_scratch_bytes(), slot_bytes, max_total);
+    if (sm.nslots < 2 * TK_GROUPS) return L2B_OK;  // the ring would be too shallow: the kernel chain runs instead
+    TkParams& P = s->tkp;
+    memset(&P, 0, sizeof(P));
+    if (!s->tk_ops) CU(cudaMalloc(&s->tk_ops, ops.size() * sizeof(TkOp)));
+    if (!s->tk_sync) CU(cudaMalloc(&s->tk_sync, 8));
+    CU(cudaMemcpy(s->tk_ops, ops.data(), ops.size() * sizeof(TkOp), cudaMemcpyHostToDevice));
+    CU(cudaMemset(s->tk_sync, 0, 8));
+    P.ops = s->tk_ops;
+    P.n_ops = (int)ops.size();
+    P.sync = s->tk_sync;
+    P.ctl = s->ctl;
+    P.status = s->status;
+    P.timeout_ms = (unsigned)env_long("L2B_TK_TIMEOUT_MS", 2000);
+    P.embed.type = m->tok_emb.type; P.embed.table = m->tok_emb.data; P.embed.d6 = m->tok_emb.d6;
+    P.embed.n = c.dim; P.embed.vocab = c.vocab_size; P.embed.x = s->x;
+    FinalizeParams& f = P.fin;
+    f.logits = s->logits; f.vocab = c.vocab_size;
+    f.amax_val = s->amax_val; f.amax_idx = s->amax_idx; f.nparts = sms;
+    f.ctl = s->ctl; f.prompt = s->prompt; f.out_tokens = s->out_tokens; f.advance = 1; f.next_token = s->next_token;
+    f.status = s->status;
+    P.sm = sm;
+    s->tk = true;
+    return L2B_OK;
+}
+
+static cudaError_t launch_token_kernel(l2b_session* s, bool cooperative) {
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = dim3(s->di.sms);
+    cfg.blockDim = dim3(TK_THREADS);
+    cfg.dynamicSmemBytes = (size_t)s->tkp.sm.total;
+    cfg.stream = s->stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeCooperative;  // all blocks resident at once: they wait for one another
+    attr[0].val.cooperative = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = cooperative ? 1 : 0;
+    switch (s->model->planes) {
+        case 1: return cudaLaunchKernelEx(&cfg, token_kernel<1>, s->tkp);
+        case 2: return cudaLaunchKernelEx(&cfg, token_kernel<2>, s->tkp);
+        default: return cudaLaunchKernelEx(&cfg, token_kernel<3>, s->tkp);
+    }
+}
+
+// Capture the token kernel as the one-position graph.  Returns false (and leaves no graph) when that is not possible.
+static bool capture_token_kernel_graph(l2b_session* s) {
+    for (int coop = 1; coop >= 0; --coop) {
+        cudaGraph_t g = nullptr;
+        if (cudaStreamBeginCapture(s->stream, cudaStreamCaptureModeThreadLocal) != cudaSuccess) break;
+        cudaError_t le = launch_token_kernel(s, coop != 0);
+        cudaError_t ce = cudaStreamEndCapture(s->stream, &g);
+        cudaError_t ie = cudaErrorUnknown;
+        if (le == cudaSuccess && ce == cudaSuccess && g) ie = cudaGraphInstantiate(&s->graph, g, 0);
+        if (g) cudaGraphDestroy(g);
+        if (ie == cudaSuccess) {
+            s->kernels_per_token = 1;
+            return true;
+        }
+        (void)cudaGetLastError();
+        s->graph = nullptr;
+    }
+    return false;
+}
+
 static int32_t capture_token_graph(l2b_session* s) {
     cudaGraph_t g = nullptr;
     const size_t max_descs = 4 * (size_t)s->model->cfg.n_layers + 2;  // <= 2 pushes + 2 summing prologues per layer, + logits
     if (s->model->tp > 1 && !s->tp_descs) CU(cudaMalloc(&s->tp_descs, max_descs * sizeof(MvTp)));
     s->tp_descs_host.clear();
     s->tp_descs_host.reserve(max_descs + 8);
+    L2B_TRY(build_token_kernel(s));
+    int32_t es = L2B_OK;
+    cudaError_t ce = cudaSuccess;
+    if (s->tk && capture_token_kernel_graph(s)) {
+        // the one-position graph is the token kernel; the two-position prompt graph below still uses the kernel chain
+    } else {
+    s->tk = false;
     CU(cudaStreamBeginCapture(s->stream, cudaStreamCaptureModeThreadLocal));
-    int32_t es = enqueue_token(s, &s->kernels_per_token);
-    cudaError_t ce = cudaStreamEndCapture(s->stream, &g);
+    es = enqueue_token(s, &s->kernels_per_token);
+    ce = cudaStreamEndCapture(s->stream, &g);
     if (es == L2B_OK && ce == cudaSuccess && !s->tp_descs_host.empty()) {
         if (s->tp_descs_host.size() > max_descs) es = fail(L2B_ERR_STATE, "more tensor-parallel launches than descriptors");
         else ce = cudaMemcpy(s->tp_descs, s->tp_descs_host.data(), s->tp_descs_host.size() * sizeof(MvTp), cudaMemcpyHostToDevice);
@@ -1068,9 +1329,12 @@ static int32_t capture_token_graph(l2b_session* s) {
         return es;
     }
     CU(ce);
-    cudaError_t ie = cudaGraphInstantiate(&s->graph, g, 0);
-    cudaGraphDestroy(g);
-    CU(ie);
+    {
+        cudaError_t ie = cudaGraphInstantiate(&s->graph, g, 0);
+        cudaGraphDestroy(g);
+        CU(ie);
+    }
+    }
     // Second graph: two prompt positions per pass.  Needs k-quant matrices throughout, three planes, one GPU.
     if (s->model->tp == 1 && s->model->planes == 3 && s->all_kquant && !s->trace && env_long("L2B_PREFILL_PAIRS", 1) != 0) {
         cudaGraph_t g2 = nullptr;
@@ -1085,7 +1349,7 @@ static int32_t capture_token_graph(l2b_session* s) {
             if (g2) cudaGraphDestroy(g2);
             g_last_error.clear();
         } else {
-            ie = cudaGraphInstantiate(&s->graph2, g2, 0);
+            cudaError_t ie = cudaGraphInstantiate(&s->graph2, g2, 0);
             cudaGraphDestroy(g2);
             CU(ie);
         }
@@ -1135,9 +1399,10 @@ extern "C" int32_t l2b_session_create(l2b_model* m, void* stream, l2b_session** 
         CU(cudaMalloc(&s->logits, (size_t)c.vocab_size * 4));
         CU(cudaMalloc(&s->kc, kvl * c.n_layers * 4));
         CU(cudaMalloc(&s->vc, kvl * c.n_layers * 4));
-        CU(cudaMalloc(&s->part_m, (size_t)m->l_heads * s->nsplit * 4 * 2));
-        CU(cudaMalloc(&s->part_l, (size_t)m->l_heads * s->nsplit * 4 * 2));
-        CU(cudaMalloc(&s->part_acc, (size_t)m->l_heads * s->nsplit * hs * 4 * 2));
+        // (room for 32 splits, the most any launch uses: the token kernel chooses its own split count)
+        CU(cudaMalloc(&s->part_m, (size_t)m->l_heads * 32 * 4 * 2));
+        CU(cudaMalloc(&s->part_l, (size_t)m->l_heads * 32 * 4 * 2));
+        CU(cudaMalloc(&s->part_acc, (size_t)m->l_heads * 32 * hs * 4 * 2));
         CU(cudaMalloc(&s->amax_val, (size_t)s->di.sms * 4));
         CU(cudaMalloc(&s->amax_idx, (size_t)s->di.sms * 4));
         CU(cudaMalloc(&s->ctl, sizeof(Control)));
@@ -1149,6 +1414,7 @@ extern "C" int32_t l2b_session_create(l2b_model* m, void* stream, l2b_session** 
         CU(cudaMallocHost(&s->h_small, 16));
         CU(cudaEventCreate(&s->ev0));
         CU(cudaEventCreate(&s->ev1));
+        CU(cudaEventCreate(&s->ev_mid));
         CU(cudaMemsetAsync(s->kc, 0, kvl * c.n_layers * 4, s->stream));
         CU(cudaMemsetAsync(s->vc, 0, kvl * c.n_layers * 4, s->stream));
         CU(cudaMemsetAsync(s->status, 0, 4, s->stream));
@@ -1244,6 +1510,7 @@ extern "C" int32_t l2b_session_tp_connect(l2b_session* s, const void* handles, i
 }
 
 static int32_t check_status_word(l2b_session* s) {
+    if (s->h_small[1] != DEV_OK && s->tk_sync) cudaMemsetAsync(s->tk_sync, 0, 8, s->stream);  // an abandoned token leaves the arrival counter anywhere
     if (s->h_small[1] == DEV_ERR_TMA_TIMEOUT) {
         cudaMemsetAsync(s->status, 0, 4, s->stream);
         return fail(L2B_ERR_TIMEOUT, "a bounded wait on a weight copy ran out inside a kernel");
@@ -1397,16 +1664,24 @@ extern "C" int32_t l2b_generate(l2b_session* s, const int32_t* prompt, int32_t n
     CU(cudaEventRecord(s->ev0, s->stream));  // the timed region is the token loop itself: inputs are resident
     // Positions p and p + 1 go through one two-position pass when both are followed by a prompt token (their next
     // tokens are forced, so neither needs logits); everything else takes the one-position graph.
+    bool mid = false;
     for (int i = 0; i < n_positions;) {
+        if (i >= n_prompt && !mid) {  // the first position that is fed a generated token
+            CU(cudaEventRecord(s->ev_mid, s->stream));
+            mid = true;
+        }
         const bool pair = s->graph2 && i + 2 < n_prompt && i + 1 < n_positions;
         CU(cudaGraphLaunch(pair ? s->graph2 : s->graph, s->stream));
         i += pair ? 2 : 1;
     }
+    if (!mid) CU(cudaEventRecord(s->ev_mid, s->stream));
     CU(cudaEventRecord(s->ev1, s->stream));
     CU(cudaMemcpyAsync(out_tokens, s->out_tokens, (size_t)n_positions * 4, cudaMemcpyDeviceToHost, s->stream));
     CU(cudaMemcpyAsync(&s->h_small[1], s->status, 4, cudaMemcpyDeviceToHost, s->stream));
     CU(cudaStreamSynchronize(s->stream));
     CU(cudaEventElapsedTime(&s->last_ms, s->ev0, s->ev1));
+    CU(cudaEventElapsedTime(&s->last_prompt_ms, s->ev0, s->ev_mid));
+    CU(cudaEventElapsedTime(&s->last_decode_ms, s->ev_mid, s->ev1));
     if (device_ms) *device_ms = s->last_ms;
     return check_status_word(s);
 }
@@ -1441,6 +1716,12 @@ extern "C" int32_t l2b_session_read(l2b_session* s, int32_t which, float* host_o
 extern "C" int32_t l2b_session_last_device_ms(l2b_session* s, float* ms) {
     if (!s || !ms) return fail(L2B_ERR_BAD_ARG, "null argument");
     *ms = s->last_ms;
+    return L2B_OK;
+}
+extern "C" int32_t l2b_session_last_phase_ms(l2b_session* s, float* prompt_ms, float* decode_ms) {
+    if (!s || !prompt_ms || !decode_ms) return fail(L2B_ERR_BAD_ARG, "null argument");
+    *prompt_ms = s->last_prompt_ms;
+    *decode_ms = s->last_decode_ms;
     return L2B_OK;
 }
 extern "C" int32_t l2b_session_kernels_per_token(l2b_session* s, int32_t* n) {

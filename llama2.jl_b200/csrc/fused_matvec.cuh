@@ -76,6 +76,8 @@ struct MvSegment {
     int gs;              // bytes between copy groups inside a slot (= 32 mod 128)
     int rowb;            // bytes of one row in a full-width stage
     int out2;            // two-position launches: element offset of the second position's output vector (0: same base, e.g. caches)
+    int d6_nb;           // q6_K: super-block scales per row of d6 / d6_2 when that differs from n_in / 256 (a launch over a column
+                         // range of the matrix; token_kernel.cuh only); 0 = n_in / 256
 };
 
 // What a tensor-parallel launch needs to know about the other GPUs.

@@ -72,10 +72,11 @@ bool read_value(Cursor& c, uint32_t type, GgufValue& v, int depth) {
         case 10: v.inum = (int64_t)c.take<uint64_t>(); v.num = (double)v.inum; break;
         case 11: v.inum = c.take<int64_t>(); v.num = (double)v.inum; break;
         case 12: v.num = c.take<double>(); v.inum = (int64_t)v.num; break;
-        case 9: {  // array: element type, count, elements (walked, not kept)
+        case 9: {  // array: element type, count, elements (walked and bounds-checked; they stay in the map)
             v.elem_type = c.take<uint32_t>();
             v.count = c.take<uint64_t>();
             if (!c.ok) return false;
+            const size_t elems_at = c.pos;
             const int es = scalar_size(v.elem_type);
             if (es > 0) {
                 if (v.count > (c.size - c.pos) / (uint64_t)es) return c.ok = false;
@@ -92,6 +93,10 @@ bool read_value(Cursor& c, uint32_t type, GgufValue& v, int depth) {
                 }
             } else {
                 return c.ok = false;
+            }
+            if (c.ok) {
+                v.elems = c.base + elems_at;
+                v.elems_bytes = c.pos - elems_at;
             }
             break;
         }

@@ -16,8 +16,10 @@ struct GgufValue {
     double num = 0.0;        // scalars (integers, floats, bool)
     int64_t inum = 0;        // the same as an integer, for integer types
     std::string str;         // type 8
-    uint32_t elem_type = 0;  // arrays: element type and count (elements are not kept)
+    uint32_t elem_type = 0;  // arrays: element type and count; the elements stay in the file map
     uint64_t count = 0;
+    const uint8_t* elems = nullptr;  // arrays: first byte of the elements inside the map (bounds already checked)
+    uint64_t elems_bytes = 0;        // arrays: bytes the elements occupy
 };
 
 struct GgufTensor {

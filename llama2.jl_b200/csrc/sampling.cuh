@@ -52,20 +52,17 @@ __device__ __forceinline__ int checked_token(int tok, int vocab, int* status) {
 
 constexpr int FIN_THREADS = 1024;
 
-// One block.  Greedy: argmax = first maximal index (Julia argmax, src/inference.jl:360).
+// NT threads of one block (tid = 0 .. NT-1; `sync` is a barrier over exactly those threads).
+// Greedy: argmax = first maximal index (Julia argmax, src/inference.jl:360).
 // Temperature: logits ./= T; softmax!; inverse-CDF walk of StatsBase.wsample (src/inference.jl:361-368),
-// with cumulative sums kept in f64.
-__global__ void __launch_bounds__(FIN_THREADS) finalize_token_kernel(const __grid_constant__ FinalizeParams p) {
-    pdl_launch_dependents();
-    pdl_wait();
-    __shared__ float s_val[32];
-    __shared__ int s_idx[32];
-    __shared__ double s_sum[FIN_THREADS];
-    __shared__ int s_choice;
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+// with cumulative sums kept in f64.  Scratch: s_val[32], s_idx[32], s_sum[NT], s_choice in shared memory.
+template <int NT, class Sync>
+__device__ __forceinline__ void finalize_token_body(const FinalizeParams& p, int tid, float* s_val, int* s_idx, double* s_sum, int* s_choice_p,
+                                                    Sync sync) {
+    const int lane = tid & 31, warp = tid >> 5;
     float bv = -INFINITY;
     int bi = 0x7fffffff;
-    for (int i = tid; i < p.nparts; i += FIN_THREADS) {
+    for (int i = tid; i < p.nparts; i += NT) {
         const float v = __ldcg(p.amax_val + i);
         const int ix = __ldcg(p.amax_idx + i);
         if (v > bv || (v == bv && ix < bi)) {
@@ -85,49 +82,49 @@ __global__ void __launch_bounds__(FIN_THREADS) finalize_token_kernel(const __gri
         s_val[warp] = bv;
         s_idx[warp] = bi;
     }
-    __syncthreads();
+    sync();
     if (tid == 0) {
-        for (int w = 1; w < FIN_THREADS / 32; ++w)
+        for (int w = 1; w < NT / 32; ++w)
             if (s_val[w] > s_val[0] || (s_val[w] == s_val[0] && s_idx[w] < s_idx[0])) {
                 s_val[0] = s_val[w];
                 s_idx[0] = s_idx[w];
             }
-        s_choice = s_idx[0];
+        *s_choice_p = s_idx[0];
     }
-    __syncthreads();
+    sync();
     const float T = p.ctl->temperature;
     const int pos = p.ctl->pos;
     if (T != 0.f) {
         const float mx = s_val[0] / T;  // maximum of logits ./ T  (T > 0)
-        const int per = (p.vocab + FIN_THREADS - 1) / FIN_THREADS;
+        const int per = (p.vocab + NT - 1) / NT;
         const int i0 = tid * per, i1 = min(p.vocab, i0 + per);
         // pass 1: sum of exp
         float fs = 0.f;
         for (int i = i0; i < i1; ++i) fs += expf(__ldcg(p.logits + i) / T - mx);
         // total in f32 like sum(x) of the reference, order: per thread then tree
         s_sum[tid] = (double)fs;
-        __syncthreads();
-        for (int o = FIN_THREADS / 2; o > 0; o >>= 1) {
+        sync();
+        for (int o = NT / 2; o > 0; o >>= 1) {
             if (tid < o) s_sum[tid] += s_sum[tid + o];
-            __syncthreads();
+            sync();
         }
         const float denom = (float)s_sum[0];
-        __syncthreads();
+        sync();
         // pass 2: probabilities and their f64 chunk sums
         double cs = 0.0;
         for (int i = i0; i < i1; ++i) cs += (double)(expf(__ldcg(p.logits + i) / T - mx) / denom);
         s_sum[tid] = cs;
-        __syncthreads();
+        sync();
         if (tid == 0) {
             double u = p.ctl->uniform;
             if (p.ctl->use_seed) u = (double)(splitmix64(p.ctl->seed + (unsigned long long)pos) >> 11) * (1.0 / 9007199254740992.0);
             double total = 0.0;
-            for (int t = 0; t < FIN_THREADS; ++t) total += s_sum[t];
+            for (int t = 0; t < NT; ++t) total += s_sum[t];
             const double target = u * total;
             // find the chunk whose cumulative sum reaches the target, then walk inside it
             double cw = 0.0;
             int t = 0;
-            while (t < FIN_THREADS - 1 && cw + s_sum[t] < target) cw += s_sum[t++];
+            while (t < NT - 1 && cw + s_sum[t] < target) cw += s_sum[t++];
             int c0 = t * per, c1 = min(p.vocab, c0 + per);
             if (c0 >= p.vocab) {
                 c0 = p.vocab - 1;
@@ -139,12 +136,12 @@ __global__ void __launch_bounds__(FIN_THREADS) finalize_token_kernel(const __gri
                 ++i;
                 cw += (double)(expf(__ldcg(p.logits + i) / T - mx) / denom);
             }
-            s_choice = i;
+            *s_choice_p = i;
         }
-        __syncthreads();
+        sync();
     }
     if (tid == 0) {
-        const int choice = checked_token(s_choice, p.vocab, p.status);
+        const int choice = checked_token(*s_choice_p, p.vocab, p.status);
         int next = choice;
         if (pos + 1 < p.ctl->n_prompt && p.prompt) next = checked_token(p.prompt[pos + 1], p.vocab, p.status);
         if (p.out_tokens) p.out_tokens[pos] = next;
@@ -155,6 +152,17 @@ __global__ void __launch_bounds__(FIN_THREADS) finalize_token_kernel(const __gri
         }
         if (p.tp_epoch) *p.tp_epoch += 1u;
     }
+}
+
+// One block of FIN_THREADS threads.
+__global__ void __launch_bounds__(FIN_THREADS) finalize_token_kernel(const __grid_constant__ FinalizeParams p) {
+    pdl_launch_dependents();
+    pdl_wait();
+    __shared__ float s_val[32];
+    __shared__ int s_idx[32];
+    __shared__ double s_sum[FIN_THREADS];
+    __shared__ int s_choice;
+    finalize_token_body<FIN_THREADS>(p, (int)threadIdx.x, s_val, s_idx, s_sum, &s_choice, [] { __syncthreads(); });
 }
 
 // End of a two-position prompt pass (positions pos and pos + 1, both followed by a prompt token): nothing is sampled,

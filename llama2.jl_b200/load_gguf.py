@@ -179,7 +179,8 @@ def load_gguf_model(filename: str, mmap: bool = True, seq_len: int = 512, native
         dec = _gpt2_decoder()
         for i, tt in enumerate(token_types):
             if tt == _TOKEN_NORMAL:
-                id_to_token[i] = bytes(dec[ch] for ch in id_to_token[i].decode("utf-8"))
+                # String([dict[c] for c in token]) (:365): the byte VALUES as characters, i.e. UTF-8 encoded again
+                id_to_token[i] = "".join(chr(dec[ch]) for ch in id_to_token[i].decode("utf-8")).encode("utf-8")
     else:
         raise ValueError(f"unsupported tokenizer model: {tok_model}")
     token_to_id = {tok: i for i, tok in enumerate(id_to_token)}

@@ -207,6 +207,12 @@ class LanguageModel:
         L.check(L.lib().l2b_session_prefill_pairs(self.device_model().session, C.byref(n)))
         return bool(n.value)
 
+    def last_phase_ms(self):
+        """(prompt ms, decode ms) of the most recent `generate`: positions fed prompt tokens / positions fed generated tokens."""
+        a, b = C.c_float(), C.c_float()
+        L.check(L.lib().l2b_session_last_phase_ms(self.device_model().session, C.byref(a), C.byref(b)))
+        return a.value, b.value
+
     def last_device_ms(self) -> float:
         ms = C.c_float()
         L.check(L.lib().l2b_session_last_device_ms(self.device_model().session, C.byref(ms)))

@@ -119,7 +119,7 @@ def test_decode_next_session_semantics(pkg, synth):
     assert L.lib().l2b_forward(sess, 5000, 0, None) == L.ERR_BAD_ARG
     assert L.lib().l2b_forward(sess, 1, 32, None) == L.ERR_BAD_ARG
     assert L.lib().l2b_decode_next(sess, 1, 0, 1.0, 1.5, C.byref(nxt)) == L.ERR_BAD_ARG
-    assert model.kernels_per_token() == 5 * 1 + 3
+    assert model.kernels_per_token() == 1  # a k-quant model on one GPU: the whole token is one persistent kernel
     assert model.weight_bytes_per_token() > 0
     model.close()
 
@@ -242,3 +242,38 @@ def test_sample_text_with_and_without_prefill(pkg, synth):
     pkg.sample(m, prompt, temperature=0.0, stop_on_special_token=False, max_seq_len=10, out=b)
     assert b.getvalue().split("\n")[0] == text[:10]
     m.close()
+
+
+@pytest.mark.gpu
+def test_llama2c_checkpoint_files(pkg, orc, synth, tmp_path):
+    """The CPU-runnable configuration THROUGH its file format: the tiny f32 model written as a llama2.c checkpoint, loaded by
+    load_karpathy_model (src/load_karpathy.jl:80-98) and run; then the unshared-classifier variant of the format."""
+    from llama2_jl_b200 import load_karpathy as lk
+    from llama2_jl_b200.tokenizer import BPETokenizer
+    g = np.load(os.path.join(GOLDEN, "tiny_f32_golden.npz"))
+    spec = synth.TINY_F32
+    cfg = spec["config"]
+    w = synth.model_weights(cfg, spec["types"], seed=int(g["seed"]), tied_output=True)
+    vocab = [b"t%d" % i for i in range(cfg.vocab_size)]
+    tok = BPETokenizer(vocab, {t: i for i, t in enumerate(vocab)}, [0.0] * cfg.vocab_size, 1, 2)
+    ck, tk = str(tmp_path / "tiny.bin"), str(tmp_path / "tok.bin")
+    lk.write_karpathy_checkpoint(ck, cfg, w)
+    lk.write_karpathy_tokenizer(tk, tok)
+    model = pkg.load_karpathy_model(ck, tk)
+    assert model.config == cfg
+    got, _ = pkg.generate(model, g["prompt"], 256)
+    assert np.array_equal(got, g["tokens"]), "greedy stream of the model loaded from the file differs from the golden stream"
+    model.close()
+    # unshared classifier, grouped-query heads: against the oracle on the arrays that were written
+    cfg2 = pkg.ModelConfig(288, 768, 2, 6, 3, 1024, 64, 10000.0, False)
+    w2 = synth.model_weights(cfg2, synth.ALL(0), seed=5, tied_output=False)
+    ck2 = str(tmp_path / "untied.bin")
+    lk.write_karpathy_checkpoint(ck2, cfg2, w2, untied=True)
+    tok2 = BPETokenizer(vocab[:1024], {t: i for i, t in enumerate(vocab[:1024])}, [0.0] * 1024, 1, 2)
+    lk.write_karpathy_tokenizer(tk, tok2)
+    m2 = pkg.load_karpathy_model(ck2, tk)
+    prompt = synth.tokens(6, 3, 3, 1024)
+    want = orc.OracleModel(cfg2, w2).sample_greedy(prompt, 48)
+    got2, _ = pkg.generate(m2, prompt, 48)
+    assert np.array_equal(got2, want)
+    m2.close()

@@ -116,6 +116,17 @@ def test_karpathy_roundtrip(pkg, synth, tmp_path):
     assert np.array_equal(m.weights.layers[1].w2, w.layers[1].w2) and m.weights.layers[1].w2.shape == (64, 96)
     assert np.array_equal(m.weights.output_weight, m.weights.token_embedding_table)  # tied classifier
     assert "dim            = 64" in str(m)
+    # llama2.c's unshared-classifier variant (negative vocab_size in the header), grouped-query heads included
+    cfg2 = pkg.ModelConfig(64, 96, 2, 4, 2, 66, 32, 10000.0, False)
+    w2 = synth.model_weights(cfg2, synth.ALL(0), seed=2, tied_output=False)
+    ck2 = str(tmp_path / "untied.bin")
+    lk.write_karpathy_checkpoint(ck2, cfg2, w2, untied=True)
+    assert struct.unpack("<7i", open(ck2, "rb").read(28))[5] == -66
+    m2 = pkg.load_karpathy_model(ck2, tk)
+    assert m2.config == cfg2 and m2.weights.layers[0].wk.shape == (32, 64)
+    assert np.array_equal(m2.weights.output_weight, w2.output_weight)
+    assert not np.array_equal(m2.weights.output_weight, m2.weights.token_embedding_table)
+    assert np.array_equal(m2.weights.layers[1].w3, w2.layers[1].w3) and np.array_equal(m2.weights.rms_final_weight, w2.rms_final_weight)
 
 
 def _write_gguf(path, arch, cfg, w, synth, fused=False):

@@ -101,3 +101,27 @@ def test_two_gpu_greedy_run_matches_single_gpu(pkg, tmp_path):
     # against one GPU: partial sums are added in another order, so logits agree to reassociation noise
     assert r0["logit_err_over_range"] < 2e-3
     assert r0["tokens"] == r0["single_tokens"]
+
+
+@pytest.mark.gpu
+def test_two_gpu_run_rides_out_a_second_of_host_skew(pkg, tmp_path):
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    r0, r1 = _run_ranks("gpu_skew", 2, tmp_path, timeout=600)
+    assert r0["tokens"] == r1["tokens"] == r0["single_tokens"]
+    assert r0["tokens"] == r0["tokens_again"]
+
+
+@pytest.mark.gpu
+def test_two_gpu_peer_timeout_is_reported_not_hung(pkg, tmp_path):
+    """One rank does not make the call (between steps, nothing of its own in flight): the other's bounded wait runs out."""
+    import torch
+    from llama2_jl_b200 import _lib as L
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    r0, r1 = _run_ranks("gpu_timeout", 2, tmp_path, timeout=600)
+    assert r0["status"] == L.ERR_TIMEOUT, r0
+    assert "tensor-parallel rank" in r0["message"]
+    assert r0["seconds"] < 10.0
+    assert r0["after"] == 0 and r0["closed"] and r1["closed"]

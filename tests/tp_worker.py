@@ -3,6 +3,10 @@
 MODE cpu: gloo only, no GPU -- the partition is checked against the CPU oracle (the sum over ranks of the sharded
           wo / w2 products equals the unsharded product; the handle exchange returns the handles in rank order).
 MODE gpu: one GPU per rank -- a tensor-parallel greedy run is compared with the single-GPU run of the same model.
+MODE gpu_skew: the same run with rank 1 entering it a second late: the waits inside the kernels must ride that out.
+MODE gpu_timeout: L2B_TP_TIMEOUT_MS=50 and rank 1 does NOT make the call (it stays alive with its memory mapped, between
+          steps, no kernel in flight): rank 0's wait for the peer runs out, the call returns L2B_ERR_TIMEOUT, the context
+          stays usable and the session can be destroyed.  No GPU faults, traps or hangs.
 """
 import json
 import os
@@ -66,6 +70,27 @@ def main():
             lo, hi = pl[key]
             errs[name] = float(np.abs(orc.matmul(shard, x) - orc.matmul(full, x)[lo:hi]).max())
         res["errs"] = errs
+    elif mode == "gpu_timeout":
+        import ctypes as C
+        from llama2_jl_b200 import _lib as L
+        torch.cuda.set_device(rank)
+        os.environ["L2B_TP_TIMEOUT_MS"] = "50"  # read when the token graph is captured (tp.connect)
+        m = pkg.LanguageModel(cfg, None, w, device=rank, tp_size=world, tp_rank=rank)
+        tp.connect(m)
+        if rank == 0:
+            nxt = C.c_int32(-1)
+            import time
+            t0 = time.perf_counter()
+            res["status"] = int(L.lib().l2b_decode_next(m.device_model().session, 5, 0, 0.0, 0.0, C.byref(nxt)))
+            res["seconds"] = time.perf_counter() - t0
+            res["message"] = L.lib().l2b_last_error_string().decode()
+            # the context is still usable: an unrelated operator runs
+            x = np.arange(256, dtype=np.float32)
+            y = np.zeros(256, dtype=np.float32)
+            res["after"] = int(L.lib().l2b_rmsnorm(L.ptr(y), L.ptr(x), L.ptr(np.ones(256, np.float32)), 256))
+        dist.barrier()  # rank 1 has made no call; nothing of rank 0 is in flight any more
+        m.close()
+        res["closed"] = True
     else:
         torch.cuda.set_device(rank)
         prompt = synth.tokens(8, 3, 3, cfg.vocab_size)
@@ -80,6 +105,9 @@ def main():
             m1.close()
         m = pkg.LanguageModel(cfg, None, w, device=rank, tp_size=world, tp_rank=rank)
         tp.connect(m)
+        if mode == "gpu_skew" and rank == 1:
+            import time
+            time.sleep(1.0)  # host-side skew between the ranks: far beyond the kernels' short poll budget
         toks, ms = pkg.generate(m, prompt, n_pos)
         res["tokens"] = toks.tolist()
         res["ms"] = ms
