@@ -25,6 +25,15 @@ def build_synth(force=False):
     return SYNTH_OUTPUT
 
 
+def build_measure():
+    """A second library with the measurement aids compiled in (-DL2B_MEASURE): time stamps inside the kernels, switches that
+    skip parts of them.  Not the product: load it with L2B_LIBRARY=<path> for your own measurements."""
+    out = os.path.join(_HERE, "libllama2_b200_measure.so")
+    nvcc = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
+    subprocess.run([nvcc] + NVCC_FLAGS + ["-DL2B_MEASURE", "-o", out] + [os.path.join(_HERE, s) for s in SOURCES], check=True)
+    return out
+
+
 def build(force=False, verbose=False):
     build_synth(force)
     if not force and not needs_build():

@@ -481,7 +481,9 @@ struct l2b_session {
     // one persistent kernel per token (token_kernel.cuh): k-quant models on one GPU
     bool tk = false;
     TkOp* tk_ops = nullptr;
-    unsigned long long* tk_sync = nullptr;
+    unsigned* tk_sync = nullptr;          // one arrival counter per operation
+    unsigned long long* tk_trace = nullptr;  // measurement builds only
+    std::vector<int> tk_kinds;               // measurement builds only: kind and input length of every operation
     TkParams tkp;
     bool tp_connected = false;
     MvTp* tp_descs = nullptr;          // device array: one descriptor per tensor-parallel launch of the token
@@ -833,6 +835,7 @@ static void session_free(l2b_session* s) {
     if (s->tp_descs) cudaFree(s->tp_descs);
     if (s->tk_ops) cudaFree(s->tk_ops);
     if (s->tk_sync) cudaFree(s->tk_sync);
+    if (s->tk_trace) cudaFree(s->tk_trace);
     if (s->h_ctl) cudaFreeHost(s->h_ctl);
     if (s->h_small) cudaFreeHost(s->h_small);
     if (s->ev0) cudaEventDestroy(s->ev0);
@@ -1105,7 +1108,9 @@ static int32_t build_token_kernel(l2b_session* s) {
     const l2b_model* m = s->model;
     const l2b_config& c = m->cfg;
     s->tk = false;
-    if (m->tp != 1 || env_long("L2B_TOKEN_KERNEL", 1) == 0) return L2B_OK;
+    // Opt-in (L2B_TOKEN_KERNEL=1): measured on a B200 the single launch is not faster than the chain of launches yet (the
+    // consumer warps, not the hand-over between kernels, bound the token), so the chain stays the default.
+    if (m->tp != 1 || env_long("L2B_TOKEN_KERNEL", 0) == 0) return L2B_OK;
     const DevMatrix* all[] = {&m->tok_emb, &m->output};
     for (const DevMatrix* w : all)
         if (w->type == T_F32) return L2B_OK;
@@ -1244,9 +1249,18 @@ static int32_t build_token_kernel(l2b_session* s) {
     TkParams& P = s->tkp;
     memset(&P, 0, sizeof(P));
     if (!s->tk_ops) CU(cudaMalloc(&s->tk_ops, ops.size() * sizeof(TkOp)));
-    if (!s->tk_sync) CU(cudaMalloc(&s->tk_sync, 8));
+    if (!s->tk_sync) CU(cudaMalloc(&s->tk_sync, TK_MAX_OPS * sizeof(unsigned)));
     CU(cudaMemcpy(s->tk_ops, ops.data(), ops.size() * sizeof(TkOp), cudaMemcpyHostToDevice));
-    CU(cudaMemset(s->tk_sync, 0, 8));
+    CU(cudaMemset(s->tk_sync, 0, TK_MAX_OPS * sizeof(unsigned)));
+#ifdef L2B_MEASURE
+    if (env_long("L2B_TK_TRACE", 0)) {
+        if (!s->tk_trace) CU(cudaMalloc(&s->tk_trace, ops.size() * 4 * 8));
+        CU(cudaMemset(s->tk_trace, 0, ops.size() * 4 * 8));
+        P.trace = s->tk_trace;
+        s->tk_kinds.clear();
+        for (const TkOp& o : ops) s->tk_kinds.push_back(o.kind * 1000000 + (o.kind == TK_MATVEC ? o.mv.n_in : 0) + (o.wait ? 500000 : 0));
+    }
+#endif
     P.ops = s->tk_ops;
     P.n_ops = (int)ops.size();
     P.sync = s->tk_sync;
@@ -1510,7 +1524,7 @@ extern "C" int32_t l2b_session_tp_connect(l2b_session* s, const void* handles, i
 }
 
 static int32_t check_status_word(l2b_session* s) {
-    if (s->h_small[1] != DEV_OK && s->tk_sync) cudaMemsetAsync(s->tk_sync, 0, 8, s->stream);  // an abandoned token leaves the arrival counter anywhere
+    if (s->h_small[1] != DEV_OK && s->tk_sync) cudaMemsetAsync(s->tk_sync, 0, TK_MAX_OPS * sizeof(unsigned), s->stream);  // an abandoned token leaves the arrival counter anywhere
     if (s->h_small[1] == DEV_ERR_TMA_TIMEOUT) {
         cudaMemsetAsync(s->status, 0, 4, s->stream);
         return fail(L2B_ERR_TIMEOUT, "a bounded wait on a weight copy ran out inside a kernel");
@@ -1587,6 +1601,20 @@ extern "C" int32_t l2b_forward(l2b_session* s, int32_t token, int32_t pos, float
     L2B_TRY(run_one(s, token, pos, 0.f, 0.0));
 #ifdef L2B_MEASURE
     if (s->trace) dump_token_trace(s);
+    if (s->tk_trace && s->tk) {  // per-operation timeline of block 0 of the token kernel
+        const size_t n = s->tk_kinds.size();
+        std::vector<unsigned long long> h(n * 4);
+        if (cudaMemcpy(h.data(), s->tk_trace, n * 32, cudaMemcpyDeviceToHost) == cudaSuccess) {
+            const unsigned long long t0 = h[0];
+            fprintf(stderr, "[l2b token kernel trace] block 0, us since its first stamp: op kind wait n_in | wait-over  planes-built  tiles-done  arrived\n");
+            for (size_t i = 0; i < n; ++i) {
+                if (i > 26 && i + 6 < n) continue;
+                auto us = [&](int k) { return h[i * 4 + k] ? (double)(h[i * 4 + k] - t0) / 1e3 : 0.0; };
+                fprintf(stderr, "  %3zu %d %d %6d | %9.2f %9.2f %9.2f %9.2f\n", i, s->tk_kinds[i] / 1000000, (s->tk_kinds[i] / 500000) & 1, s->tk_kinds[i] % 500000,
+                        us(0), us(1), us(2), us(3));
+            }
+        }
+    }
 #endif
     if (host_logits) CU(cudaMemcpy(host_logits, s->logits, (size_t)s->model->cfg.vocab_size * 4, cudaMemcpyDeviceToHost));
     return L2B_OK;

@@ -7,9 +7,10 @@
 // classifier, next-token choice) that the host built once:
 //   * the producer warp never stops: weights are constants, so it streams the tiles of operation k+1 into the shared-memory
 //     ring while the consumer warps are still finishing operation k or waiting for the other SMs;
-//   * an operation that needs the complete result of the one before it waits on a device-wide arrival counter (every block
-//     adds one when it has finished an operation; the wait is `count >= blocks x operations so far`), which replaces the
-//     kernel boundary;
+//   * an operation that needs the complete result of the one before it waits on that operation's arrival counter (every
+//     block adds one to an operation's counter when it has finished its part; the wait is `count == blocks`), which replaces
+//     the kernel boundary.  A block arrives for its operations in order, so the counter of the operation just before
+//     covers everything earlier;
 //   * the consumer warps build the activation planes, multiply (the same int8 tensor-core tile functions as the chain), and
 //     hand their partial sums to the finisher warp, which runs the same epilogues as the chain;
 //   * a matrix whose rows are longer than the activation planes kept in shared memory and whose epilogue is a plain
@@ -56,7 +57,7 @@ struct TkEmbed {
 struct TkSmem {
     int off_bar;     // full[8] empty[8] red_full[8] red_empty[8]
     int off_misc;    // block-wide flags and small exchange arrays
-    int off_ops;     // 4 copies of a TkOp: producer, finisher, consumers (two, alternating)
+    int off_ops;     // 5 copies of a TkOp: producer (two, alternating), consumers (two, alternating), finisher
     int off_red;     // partial sums between consumer warps and the finisher warp
     int off_region;  // dpl | xs16 | activation planes; attention and next-token scratch alias it
     int off_ring;
@@ -66,7 +67,8 @@ struct TkSmem {
 struct TkParams {
     const TkOp* ops;
     int n_ops;
-    unsigned long long* sync;  // arrival counter: zero at launch, zeroed again by block 0 at the end
+    unsigned* sync;            // arrival counters, one per operation: zero at launch, zeroed again by block 0 at the end
+    unsigned long long* trace; // measurement builds: time stamps per operation (block 0), or null
     Control* ctl;
     int* status;
     unsigned timeout_ms;       // bound on a device-wide wait
@@ -95,7 +97,7 @@ __host__ inline TkSmem tk_smem_layout(int planes, int planes_cap, int attn_scrat
     s.off_misc = o;
     o += (int)((sizeof(TkMisc) + 15) & ~(size_t)15);
     s.off_ops = o;
-    o += 4 * tk_op_bytes();
+    o += 5 * tk_op_bytes();
     o = (o + 127) & ~127;
     s.off_red = o;
     o += MV_RED_BUFS * MV_MAX_CONSUMERS * 16 * 4;
@@ -123,17 +125,17 @@ __host__ inline TkSmem tk_smem_layout(int planes, int planes_cap, int attn_scrat
 }
 
 // ---- device-wide arrival counter ---------------------------------------------------------------
-__device__ __forceinline__ void tk_arrive(unsigned long long* ctr) {
-    asm volatile("red.release.gpu.global.add.u64 [%0], %1;" ::"l"(ctr), "l"(1ull) : "memory");
+__device__ __forceinline__ void tk_arrive(unsigned* ctr) {
+    asm volatile("red.release.gpu.global.add.u32 [%0], %1;" ::"l"(ctr), "r"(1u) : "memory");
 }
-__device__ __forceinline__ unsigned long long tk_load_acquire(const unsigned long long* ctr) {
-    unsigned long long v;
-    asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(ctr) : "memory");
+__device__ __forceinline__ unsigned tk_load_acquire(const unsigned* ctr) {
+    unsigned v;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(ctr) : "memory");
     return v;
 }
 // One thread polls.  Gives up when the count does not arrive within limit_ns, or when this block or any other has reported a
 // failure.
-__device__ __forceinline__ bool tk_wait_count(const unsigned long long* ctr, unsigned long long target, const int* status, volatile int* dead,
+__device__ __forceinline__ bool tk_wait_count(const unsigned* ctr, unsigned target, const int* status, volatile int* dead,
                                               unsigned long long limit_ns) {
     unsigned long long t0 = 0;
     for (uint32_t i = 0;; ++i) {
@@ -167,7 +169,7 @@ __device__ __forceinline__ void tk_load_op(TkOp* dst, const TkOp* src, int tid, 
 // One (head group, split) work item: the arithmetic of attention_split_body with TK_CONSUMERS warps walking the item's
 // positions.  The warps are merged head by head through two alternating scratch buffers in shared memory.
 template <int GQ>
-__device__ __forceinline__ void tk_attention_item(const AttnParams& p, int item, int npos, int warp, int lane, uint8_t* scratch, TkMisc* misc) {
+__device__ __noinline__ void tk_attention_item(const AttnParams& p, int item, int npos, int warp, int lane, uint8_t* scratch, TkMisc* misc) {
     constexpr int W = TK_CONSUMERS;
     const int hg = item / p.nsplit, sp = item % p.nsplit;
     const int kvh = (hg * GQ) / (p.n_heads / p.n_kv);
@@ -323,6 +325,46 @@ __device__ __forceinline__ void tk_attention_item(const AttnParams& p, int item,
     }
 }
 
+// x = dequantize!(x, token_embedding_table[:, token]) (src/inference.jl:236) by the consumer warps of block 0.
+__device__ __noinline__ void tk_embed(const TkEmbed& e, int tok, int ctid) {
+    const bool valid = tok >= 0 && tok < e.vocab;
+    const int nbr = e.n / QK_K;
+    for (int i = ctid; i < e.n; i += TK_CONSUMERS * 32) {
+        float v = 0.f;
+        if (valid) {
+            const int b = i >> 8, k = i & 255;
+            const uint8_t* blk = e.table + ((size_t)tok * nbr + b) * dev_block_bytes(e.type);
+            if (e.type == T_Q4_K) v = dequant_q45<false>(blk, k);
+            else if (e.type == T_Q5_K) v = dequant_q45<true>(blk, k);
+            else v = dequant_q6(blk, __half2float(e.d6[(size_t)tok * nbr + b]), k);
+        }
+        e.x[i] = v;
+    }
+    __threadfence();
+}
+
+// Next token (src/inference.jl:354-368) and advance, by the consumer warps of block 0.
+__device__ __noinline__ void tk_final(const FinalizeParams& f, int ctid, uint8_t* region, int* s_choice) {
+    float* s_val = reinterpret_cast<float*>(region);
+    int* s_idx = reinterpret_cast<int*>(region + 128);
+    double* s_sum = reinterpret_cast<double*>(region + 256);
+    finalize_token_body<TK_CONSUMERS * 32>(f, ctid, s_val, s_idx, s_sum, s_choice, [] { consumer_sync(TK_CONSUMERS * 32); });
+}
+
+__device__ __noinline__ void tk_attention_op(const AttnParams& a, int npos, int warp, int lane, uint8_t* region, TkMisc* misc) {
+    const int gq = a.n_heads / a.n_kv;
+    const int GQ = (gq == 8 || gq == 4 || gq == 2) ? gq : 1;
+    const int n_items = (a.n_heads / GQ) * a.nsplit;
+    for (int item = (int)blockIdx.x; item < n_items; item += (int)gridDim.x) {
+        if (GQ == 8) tk_attention_item<8>(a, item, npos, warp, lane, region, misc);
+        else if (GQ == 4) tk_attention_item<4>(a, item, npos, warp, lane, region, misc);
+        else if (GQ == 2) tk_attention_item<2>(a, item, npos, warp, lane, region, misc);
+        else tk_attention_item<1>(a, item, npos, warp, lane, region, misc);
+        consumer_sync(TK_CONSUMERS * 32);  // the scratch buffers are free again
+    }
+    __threadfence();
+}
+
 __host__ __device__ inline int tk_attention_scratch_bytes() { return 2 * (TK_CONSUMERS * 8 + TK_CONSUMERS * 32 * 16); }
 
 // ---- the kernel --------------------------------------------------------------------------------------
@@ -343,7 +385,15 @@ __global__ void __launch_bounds__(TK_THREADS, 1) token_kernel(const __grid_const
     uint8_t* ring = smem + S.off_ring;
     float* red = reinterpret_cast<float*>(smem + S.off_red);
     auto opbuf = [&](int i) { return reinterpret_cast<TkOp*>(smem + S.off_ops + i * tk_op_bytes()); };
-    const unsigned long long nblocks = gridDim.x;
+    const unsigned nblocks = gridDim.x;
+#ifdef L2B_MEASURE
+#define TK_STAMP(op_index, k)                                                                                        \
+    do {                                                                                                             \
+        if (tp.trace && blockIdx.x == 0) tp.trace[(size_t)(op_index) * 4 + (k)] = global_ns();                       \
+    } while (0)
+#else
+#define TK_STAMP(op_index, k) do { } while (0)
+#endif
 
     if (threadIdx.x < NS) {
         mbar_init(full + threadIdx.x, 1);
@@ -367,52 +417,92 @@ __global__ void __launch_bounds__(TK_THREADS, 1) token_kernel(const __grid_const
     const int pos = __ldcg(&tp.ctl->pos);
 
     // ================================ producer warp =============================================
+    // Lane c brings copy group c of every stage.  This warp runs serial address arithmetic on a busy SM (some 20 cycles per
+    // instruction), so the source of the NEXT tile is worked out right after a tile's copies have been issued, in the shadow
+    // of the wait for a free slot, and the descriptor of the next operation is fetched while this one's tiles are streamed.
     if (warp == W) {
         if (lane >= 16) return;
         const uint64_t policy = policy_evict_first();
         const int c = lane;
-        TkOp* op = opbuf(0);
         int slot_g[2] = {0, NSG}, ph_g[2] = {0, 0};
         unsigned gt = 0;  // tiles of this block so far, over all operations
         bool dead = false;
-        for (int oi = 0; oi < tp.n_ops && !dead; ++oi) {
-            if ((misc->kinds[oi] & 15) != TK_MATVEC) continue;
-            __syncwarp(0x0000ffffu);
-            tk_load_op(op, tp.ops + oi, lane, 16);
-            __syncwarp(0x0000ffffu);
+        struct TileSrc {
+            const uint8_t* src;  // first byte of this lane's copy (stage 0)
+            uint32_t bytes0;     // bytes of this lane's copy in a full-width stage (0: nothing to copy)
+            uint32_t tx0;        // bytes of the whole stage (all lanes) in a full-width stage
+            int bb, nrows, nvalid, gs, row;
+            size_t ps;           // bytes of one full column panel of the matrix
+        };
+        constexpr int OPV = (sizeof(TkOp) + 16 * 16 - 1) / (16 * 16);  // uint4 per lane that hold one descriptor
+        auto next_matvec = [&](int from) {
+            while (from < tp.n_ops && (misc->kinds[from] & 15) != TK_MATVEC) ++from;
+            return from;
+        };
+        int oi = next_matvec(0), buf = 0;
+        // descriptor buffers of this warp: 0 and 1 (the finisher keeps its own copy in registers-fed buffer 1 below)
+        if (oi < tp.n_ops) tk_load_op(opbuf(0), tp.ops + oi, lane, 16);
+        __syncwarp(0x0000ffffu);
+        while (oi < tp.n_ops && !dead) {
+            const TkOp* op = opbuf(buf);
             const MvParams& p = op->mv;
             const int nb = p.n_in / QK_K, nit = p.nit;
             const int my_units = p.units_lo + ((int)blockIdx.x < p.units_rem ? 1 : 0);
-            for (int j = 0; j < my_units && !dead; ++j, ++gt) {
-                // source of this lane's copy group for tile j
+            const int oi_next = next_matvec(oi + 1);
+            uint4 pre[OPV];  // the next operation's descriptor, on its way while this one's tiles are issued
+            if (oi_next < tp.n_ops) {
+#pragma unroll
+                for (int k = 0; k < OPV; ++k) {
+                    const int idx = lane + 16 * k;
+                    pre[k] = idx < tk_op_bytes() / 16 ? __ldg(reinterpret_cast<const uint4*>(tp.ops + oi_next) + idx) : make_uint4(0u, 0u, 0u, 0u);
+                }
+            }
+            auto tile_src = [&](int j) {
+                TileSrc ts;
+                ts.src = nullptr;
+                ts.bytes0 = ts.tx0 = 0;
+                ts.bb = ts.nrows = ts.nvalid = ts.gs = ts.row = 0;
+                ts.ps = 0;
+                if (j >= my_units) return ts;
                 const UnitInfo u = find_unit<true>(p, (int)blockIdx.x + j * (int)gridDim.x);
                 const MvSegment& sg = p.seg[u.seg];
-                const int bb = dev_block_bytes(sg.type);
-                const int pairs_left = sg.npairs - u.pair0;
-                const int nvalid = 2 * min(MV_TILE_PAIRS, pairs_left);
-                int nrows = 0, row = 0;
-                const uint8_t* src0 = nullptr;
+                ts.bb = dev_block_bytes(sg.type);
+                ts.gs = sg.gs;
+                const int pairs_left = sg.npairs - u.pair0;  // >= 1
+                ts.nvalid = 2 * min(MV_TILE_PAIRS, pairs_left);
                 if (c < sg.ngroups) {
-                    if (sg.rpg == 4) {
-                        nrows = max(0, min(4, 2 * pairs_left - 4 * c));
-                        row = 2 * u.pair0 + 4 * c;
-                        src0 = sg.w + (size_t)row * sg.rowb;
+                    if (sg.rpg == 4) {  // adjacent rows 16*tile + 4c ..
+                        ts.nrows = max(0, min(4, 2 * pairs_left - 4 * c));
+                        ts.row = 2 * u.pair0 + 4 * c;
+                        ts.src = sg.w + (size_t)ts.row * sg.rowb;
                     } else {
-                        const int half = c >> 2;
-                        const int jp = 2 * (c & 3);
-                        nrows = max(0, min(sg.rpg, pairs_left - jp));
-                        if (nrows > 0) {
+                        const int half = c >> 2;      // A or B rows
+                        const int jp = 2 * (c & 3);   // pair of the copy's first row
+                        ts.nrows = max(0, min(sg.rpg, pairs_left - jp));
+                        if (ts.nrows > 0) {
                             int rowA, rowB;
                             pair_rows(p, sg, u.pair0 + jp, rowA, rowB);
                             const uint8_t* base = (sg.pair_mode == PAIR_DUAL && half) ? sg.w2 : sg.w;
-                            row = half ? rowB : rowA;
-                            src0 = base + (size_t)row * sg.rowb;
+                            ts.row = half ? rowB : rowA;
+                            ts.src = base + (size_t)ts.row * sg.rowb;
                         }
                     }
                 }
-                const size_t ps = (size_t)(sg.pair_mode == PAIR_DUAL ? sg.npairs : 2 * sg.npairs) * sg.rowb;
+                ts.bytes0 = (uint32_t)(ts.nrows * sg.rowb);
+                ts.tx0 = (uint32_t)(ts.nvalid * sg.rowb);
+                ts.ps = (size_t)(sg.pair_mode == PAIR_DUAL ? sg.npairs : 2 * sg.npairs) * sg.rowb;
+                return ts;
+            };
+            TileSrc ts = tile_src(0);
+            // Fast path for the common case (one segment, adjacent or dual rows, full tiles): the next tile's source is the
+            // current one plus a constant.
+            const bool linear = (p.nseg == 1) && (p.seg[0].pair_mode != PAIR_NEOX);
+            const int row_step = (int)gridDim.x * (p.seg[0].pair_mode == PAIR_ADJACENT ? 16 : 8);
+            const size_t tile_step = linear ? (size_t)row_step * p.seg[0].rowb : 0;
+            const int full_tiles = linear ? p.seg[0].npairs / MV_TILE_PAIRS : 0;
+            for (int j = 0; j < my_units && !dead; ++j, ++gt) {
                 const int grp = (int)(gt & 1u);
-                int slot_i = slot_g[grp], ph = ph_g[grp];
+                int slot_i = grp ? slot_g[1] : slot_g[0], ph = grp ? ph_g[1] : ph_g[0];
                 for (int it = 0; it < nit; ++it) {
                     if (ph > 0) {
                         int ok = 1;
@@ -423,25 +513,50 @@ __global__ void __launch_bounds__(TK_THREADS, 1) token_kernel(const __grid_const
                             break;
                         }
                     }
-                    uint32_t bytes = (uint32_t)(nrows * sg.rowb), tx = (uint32_t)(nvalid * sg.rowb);
-                    const uint8_t* src = src0;
+                    uint32_t bytes = ts.bytes0, tx = ts.tx0;
+                    const uint8_t* src = ts.src;
                     if (nit > 1) {  // stage `it` lives in column panel `it`, whose rows are nblk blocks wide
                         const int nblk = min(p.kb, nb - it * p.kb);
-                        bytes = (uint32_t)(nrows * nblk * bb);
-                        tx = (uint32_t)(nvalid * nblk * bb);
-                        src += (size_t)it * ps - (size_t)row * ((p.kb - nblk) * bb);
+                        bytes = (uint32_t)(ts.nrows * nblk * ts.bb);
+                        tx = (uint32_t)(ts.nvalid * nblk * ts.bb);
+                        src += (size_t)it * ts.ps - (size_t)ts.row * ((p.kb - nblk) * ts.bb);
                     }
                     if (c == 0) mbar_arrive_expect_tx(full + slot_i, tx);
                     __syncwarp(0x0000ffffu);
-                    if (bytes) bulk_g2s(ring + (size_t)slot_i * S.slot_bytes + (size_t)c * sg.gs, src, bytes, full + slot_i, policy);
+                    if (bytes) bulk_g2s(ring + (size_t)slot_i * S.slot_bytes + (size_t)c * ts.gs, src, bytes, full + slot_i, policy);
                     if (++slot_i == (grp + 1) * NSG) {
                         slot_i = grp * NSG;
                         ++ph;
                     }
                 }
-                slot_g[grp] = slot_i;
-                ph_g[grp] = ph;
+                if (grp) {
+                    slot_g[1] = slot_i;
+                    ph_g[1] = ph;
+                } else {
+                    slot_g[0] = slot_i;
+                    ph_g[0] = ph;
+                }
+                // source of the next tile (in the shadow of the wait for its slot)
+                const int next_tile = (int)blockIdx.x + (j + 1) * (int)gridDim.x;
+                if (linear && next_tile < full_tiles) {
+                    ts.src += tile_step;
+                    ts.row += row_step;
+                } else {
+                    ts = tile_src(j + 1);
+                }
             }
+            // the next operation's descriptor goes to the other buffer
+            if (oi_next < tp.n_ops) {
+                uint4* d4 = reinterpret_cast<uint4*>(opbuf(buf ^ 1));
+#pragma unroll
+                for (int k = 0; k < OPV; ++k) {
+                    const int idx = lane + 16 * k;
+                    if (idx < tk_op_bytes() / 16) d4[idx] = pre[k];
+                }
+            }
+            __syncwarp(0x0000ffffu);
+            buf ^= 1;
+            oi = oi_next;
         }
         if (dead) {
             if (c == 0) {
@@ -455,7 +570,7 @@ __global__ void __launch_bounds__(TK_THREADS, 1) token_kernel(const __grid_const
 
     // ================================ finisher warp ==============================================
     if (warp == W + 1) {
-        TkOp* op = opbuf(1);
+        TkOp* op = opbuf(4);
         const int fq = lane >> 4, fidx = lane & 15;
         unsigned gt = 0;
         bool dead = false;
@@ -507,7 +622,10 @@ __global__ void __launch_bounds__(TK_THREADS, 1) token_kernel(const __grid_const
             // this block's part of the operation is in memory: tell everyone
             __threadfence();
             __syncwarp();
-            if (lane == 0) tk_arrive(tp.sync);
+            if (lane == 0) {
+                tk_arrive(tp.sync + oi);
+                TK_STAMP(oi, 3);
+            }
         }
         if (dead && lane == 0) {
             atomicExch(tp.status, DEV_ERR_TMA_TIMEOUT);
@@ -553,69 +671,41 @@ __global__ void __launch_bounds__(TK_THREADS, 1) token_kernel(const __grid_const
         if (kind == TK_FINAL && blockIdx.x != 0) break;  // the next token is chosen by block 0
         if (ctid == 0) {
             if ((misc->kinds[oi] >> 4) && !*dead_flag &&
-                !tk_wait_count(tp.sync, (unsigned long long)oi * nblocks, tp.status, dead_flag, limit_ns)) {
+                !tk_wait_count(tp.sync + oi - 1, nblocks, tp.status, dead_flag, limit_ns)) {
                 atomicExch(tp.status, DEV_ERR_TMA_TIMEOUT);
                 misc->dead = 1;
             }
             misc->stop = misc->dead;
+            TK_STAMP(oi, 0);
         }
         consumer_sync(W * 32);  // also: every warp has finished the previous operation (planes, descriptor buffers are free)
         if (misc->stop) break;
         if (oi + 1 < tp.n_ops) tk_load_op(opbuf(2 + ((oi + 1) & 1)), tp.ops + oi + 1, ctid, W * 32);  // visible after the next barrier
-        if (kind == TK_EMBED) {
-            // x = dequantize!(x, token_embedding_table[:, token]) (src/inference.jl:236); every block's first q/k/v prologue
-            // reads it, block 0 writes it
-            if (blockIdx.x == 0) {
-                const TkEmbed& e = tp.embed;
-                const int tok = __ldcg(&tp.ctl->token);
-                const bool valid = tok >= 0 && tok < e.vocab;
-                const int nbr = e.n / QK_K;
-                for (int i = ctid; i < e.n; i += W * 32) {
-                    float v = 0.f;
-                    if (valid) {
-                        const int b = i >> 8, k = i & 255;
-                        const uint8_t* blk = e.table + ((size_t)tok * nbr + b) * dev_block_bytes(e.type);
-                        if (e.type == T_Q4_K) v = dequant_q45<false>(blk, k);
-                        else if (e.type == T_Q5_K) v = dequant_q45<true>(blk, k);
-                        else v = dequant_q6(blk, __half2float(e.d6[(size_t)tok * nbr + b]), k);
-                    }
-                    e.x[i] = v;
-                }
-                __threadfence();
-            }
+        if (kind == TK_EMBED) {  // every block's first q/k/v prologue reads x, block 0 writes it
+            if (blockIdx.x == 0) tk_embed(tp.embed, __ldcg(&tp.ctl->token), ctid);
             consumer_sync(W * 32);
-            if (ctid == 0) tk_arrive(tp.sync);
+            if (ctid == 0) tk_arrive(tp.sync + oi);
             continue;
         }
         if (kind == TK_ATTN) {
-            const AttnParams& a = op->at;
-            const int gq = a.n_heads / a.n_kv;
-            const int GQ = (gq == 8 || gq == 4 || gq == 2) ? gq : 1;
-            const int n_items = (a.n_heads / GQ) * a.nsplit;
-            for (int item = (int)blockIdx.x; item < n_items; item += (int)gridDim.x) {
-                if (GQ == 8) tk_attention_item<8>(a, item, pos + 1, warp, lane, region, misc);
-                else if (GQ == 4) tk_attention_item<4>(a, item, pos + 1, warp, lane, region, misc);
-                else if (GQ == 2) tk_attention_item<2>(a, item, pos + 1, warp, lane, region, misc);
-                else tk_attention_item<1>(a, item, pos + 1, warp, lane, region, misc);
-                consumer_sync(W * 32);  // the scratch buffers are free again
-            }
-            __threadfence();
+            tk_attention_op(op->at, pos + 1, warp, lane, region, misc);
             consumer_sync(W * 32);
-            if (ctid == 0) tk_arrive(tp.sync);
+            if (ctid == 0) {
+                tk_arrive(tp.sync + oi);
+                TK_STAMP(oi, 3);
+            }
             continue;
         }
-        if (kind == TK_FINAL) {
-            // next token (src/inference.jl:354-368) and advance; block 0 only
-            float* s_val = reinterpret_cast<float*>(region);
-            int* s_idx = reinterpret_cast<int*>(region + 128);
-            double* s_sum = reinterpret_cast<double*>(region + 256);
-            finalize_token_body<W * 32>(tp.fin, ctid, s_val, s_idx, s_sum, &misc->s_choice, [&] { consumer_sync(W * 32); });
-            if (ctid == 0) *tp.sync = 0ull;  // every block has made its last arrival (this operation waited for all of them)
+        if (kind == TK_FINAL) {  // block 0 only
+            tk_final(tp.fin, ctid, region, &misc->s_choice);
+            // every block has made its last arrival (this operation waited for all of them): counters back to zero
+            for (int i = ctid; i < tp.n_ops; i += W * 32) tp.sync[i] = 0u;
             break;
         }
         // ---- TK_MATVEC ----
         const MvParams& p = op->mv;
         build_activation<true, P, false>(p, smem, L, warp, lane, W, p.x_in, act, dpl, xs16);
+        if (ctid == 0) TK_STAMP(oi, 1);
         const int nb = p.n_in / QK_K, nit = p.nit;
         const int my_units = p.units_lo + ((int)blockIdx.x < p.units_rem ? 1 : 0);
         // tiles of this block alternate between the two groups of consumer warps by their running number
@@ -694,6 +784,7 @@ __global__ void __launch_bounds__(TK_THREADS, 1) token_kernel(const __grid_const
             if (lane == 0 && !dead) mbar_arrive(red_full + rb);
         }
         gt += (unsigned)my_units;
+        if (ctid == 0) TK_STAMP(oi, 2);
         if (dead && lane == 0) {
             atomicExch(tp.status, DEV_ERR_TMA_TIMEOUT);
             misc->dead = 1;

@@ -119,7 +119,7 @@ def test_decode_next_session_semantics(pkg, synth):
     assert L.lib().l2b_forward(sess, 5000, 0, None) == L.ERR_BAD_ARG
     assert L.lib().l2b_forward(sess, 1, 32, None) == L.ERR_BAD_ARG
     assert L.lib().l2b_decode_next(sess, 1, 0, 1.0, 1.5, C.byref(nxt)) == L.ERR_BAD_ARG
-    assert model.kernels_per_token() == 1  # a k-quant model on one GPU: the whole token is one persistent kernel
+    assert model.kernels_per_token() == 5 * 1 + 3
     assert model.weight_bytes_per_token() > 0
     model.close()
 
@@ -277,3 +277,42 @@ def test_llama2c_checkpoint_files(pkg, orc, synth, tmp_path):
     got2, _ = pkg.generate(m2, prompt, 48)
     assert np.array_equal(got2, want)
     m2.close()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("shape", ["llama_gqa4", "phi3_neox_q6_down", "tiny_dims"])
+def test_token_kernel_matches_chain_and_oracle(pkg, orc, synth, shape):
+    """The whole token as ONE persistent launch (L2B_TOKEN_KERNEL=1) against the kernel chain and the oracle: same greedy stream,
+    logits within reassociation noise, the same stream on every run (arrival counters, ring and ticket state carry over)."""
+    from llama2_jl_b200 import _lib as L
+    if shape == "llama_gqa4":
+        cfg = pkg.ModelConfig(1024, 4608, 3, 8, 2, 1024, 96, 500000.0, False)   # hidden > dim: the down projection is cut in two
+        types = dict(synth.ALL(12), wv=13, w2=13, output=14)
+    elif shape == "phi3_neox_q6_down":
+        cfg = pkg.ModelConfig(768, 4352, 2, 8, 8, 512, 64, 10000.0, True)
+        types = dict(synth.ALL(13), wv=14, w2=14, output=14)
+    else:  # most blocks have no tile at all in most operations
+        cfg = pkg.ModelConfig(256, 512, 2, 4, 2, 64, 64, 500000.0, False)
+        types = dict(synth.ALL(12), wv=13, w2=13, output=14)
+    w = synth.model_weights(cfg, types, seed=17)
+    prompt = synth.tokens(5, 9, 3, cfg.vocab_size)
+    n_pos = 48
+    chain = pkg.LanguageModel(cfg, None, w)
+    t_chain, _ = pkg.generate(chain, prompt, n_pos)
+    assert chain.kernels_per_token() == 5 * cfg.n_layers + 3
+    os.environ["L2B_TOKEN_KERNEL"] = "1"
+    try:
+        one = pkg.LanguageModel(cfg, None, w)
+        assert one.kernels_per_token() == 1
+        runs = [pkg.generate(one, prompt, n_pos)[0] for _ in range(4)]
+    finally:
+        del os.environ["L2B_TOKEN_KERNEL"]
+    assert all(np.array_equal(r, runs[0]) for r in runs)
+    want_tokens, want_logits = orc.OracleModel(cfg, w).sample_greedy(prompt, n_pos, want_logits=True)
+    if shape != "tiny_dims":  # a 64-word vocabulary over random weights has exact ties; the stream test needs margins
+        assert np.array_equal(runs[0], want_tokens) and np.array_equal(t_chain, want_tokens)
+    fed = np.concatenate([prompt[:1], want_tokens])
+    logits = teacher_forced(pkg, one, fed, n_pos)
+    assert max(logit_err(logits[p], want_logits[p]) for p in range(n_pos)) < 5e-5
+    chain.close()
+    one.close()
