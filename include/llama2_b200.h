@@ -32,6 +32,7 @@ extern "C" {
 typedef struct l2b_model l2b_model;     /* TransformerWeights + ModelConfig on the device */
 typedef struct l2b_session l2b_session; /* RunState: activations, KV cache, captured token graph */
 typedef struct l2b_matrix l2b_matrix;   /* one weight matrix resident on the device */
+typedef struct l2b_batch l2b_batch;     /* several RunStates decoded in lock step (batched decode) */
 typedef struct l2b_tokenizer l2b_tokenizer; /* BPETokenizer (src/tokenizer.jl:3-9), host memory only */
 
 enum l2b_status {
@@ -200,6 +201,17 @@ int32_t l2b_session_prefill_pairs(l2b_session* session, int32_t* enabled);
 /* Number of kernel launches per token: 1 when the whole token is one persistent kernel (k-quant model on one GPU), else
  * 5 per layer + 3. */
 int32_t l2b_session_kernels_per_token(l2b_session* session, int32_t* n);
+
+/* ---- batched decode (no counterpart in the reference, whose `sample` serves one prompt) ----------------------
+ * n_seq independent sequences (2 .. 240), each with its own zeroed KV cache of seq_len positions, advanced one position per
+ * call: every matrix is streamed once per 20 sequences by the tensor-core GEMM instead of once per sequence.  Needs q4_K /
+ * q5_K layer matrices (the classifier may be q6_K), three activation planes, one GPU; otherwise L2B_ERR_UNSUPPORTED_TYPE.
+ * l2b_batch_decode_next: tokens[i] is fed at position positions[i] of sequence i (transformer!, src/inference.jl:222-315, for
+ * each); next_tokens[i] = argmax of its logits (src/inference.jl:360); host_logits (optional) receives [n_seq][vocab_size]. */
+int32_t l2b_batch_create(l2b_model* model, int32_t n_seq, l2b_batch** batch);
+int32_t l2b_batch_reset(l2b_batch* batch);
+int32_t l2b_batch_destroy(l2b_batch* batch);
+int32_t l2b_batch_decode_next(l2b_batch* batch, const int32_t* tokens, const int32_t* positions, int32_t* next_tokens, float* host_logits);
 
 /* ---- isolated operators (host buffers in, host buffers out) ------------------------ */
 /* dequantize! (src/kquants.jl:44-47,70-125,186-251,322-363); bit-exact. n_elems % 256 == 0 for k-quants. */

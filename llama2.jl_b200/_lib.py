@@ -65,6 +65,10 @@ _SIGNATURES = {
     "l2b_attention": ([_P, _P, _P, _P, C.c_int32, C.c_int32, C.c_int32, C.c_int32], C.c_int32),
     "l2b_model_load_gguf": ([C.c_char_p, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32, _P, C.POINTER(_P)], C.c_int32),
     "l2b_gguf_inspect": ([C.c_char_p, _P, C.POINTER(C.c_int32), C.POINTER(C.c_int64), C.POINTER(C.c_int64)], C.c_int32),
+    "l2b_batch_create": ([_P, C.c_int32, C.POINTER(_P)], C.c_int32),
+    "l2b_batch_reset": ([_P], C.c_int32),
+    "l2b_batch_destroy": ([_P], C.c_int32),
+    "l2b_batch_decode_next": ([_P, _P, _P, _P, _P], C.c_int32),
     "l2b_tokenizer_create": ([_P, _P, C.c_int32, _P, _P, C.c_int32, C.c_int32, C.c_int32, C.POINTER(_P)], C.c_int32),
     "l2b_tokenizer_load_gguf": ([C.c_char_p, C.POINTER(_P)], C.c_int32),
     "l2b_tokenizer_destroy": ([_P], C.c_int32),

@@ -5,7 +5,7 @@ import subprocess
 _HERE = os.path.dirname(os.path.abspath(__file__))
 SOURCES = ["csrc/api.cu", "csrc/gguf_reader.cpp", "csrc/tokenizer.cpp"]
 HEADERS = ["csrc/common.cuh", "csrc/kquants.cuh", "csrc/fused_matvec.cuh", "csrc/attention.cuh", "csrc/sampling.cuh",
-           "csrc/small_ops.cuh", "csrc/token_kernel.cuh", "csrc/gguf_reader.h", "../include/llama2_b200.h"]
+           "csrc/small_ops.cuh", "csrc/token_kernel.cuh", "csrc/kq_gemm.cuh", "csrc/prefill_ops.cuh", "csrc/gguf_reader.h", "../include/llama2_b200.h"]
 OUTPUT = os.path.join(_HERE, "libllama2_b200.so")
 SYNTH_OUTPUT = os.path.join(_HERE, "libl2b_synth.so")  # test support: seeded synthetic data, plain C++
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC", "-shared"]

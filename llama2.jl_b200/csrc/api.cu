@@ -15,6 +15,8 @@
 #include "fused_matvec.cuh"
 #include "sampling.cuh"
 #include "small_ops.cuh"
+#include "kq_gemm.cuh"
+#include "prefill_ops.cuh"
 #include "token_kernel.cuh"
 
 using namespace l2b;
@@ -315,6 +317,7 @@ static void set_kernel_attrs() {
         set((const void*)fused_matvec_kernel<true, 1, true>);
         set((const void*)fused_matvec_kernel<true, 2, true>);
         set((const void*)fused_matvec_kernel<true, 3, true>);
+        set((const void*)kq_gemm_kernel);
         set((const void*)token_kernel<1>);
         set((const void*)token_kernel<2>);
         set((const void*)token_kernel<3>);
@@ -394,6 +397,95 @@ static cudaError_t launch_attention(const AttnParams& a, int gq, cudaStream_t st
 static int choose_gq(int n_heads, int n_kv) {
     const int r = n_heads / n_kv;
     return (r == 8 || r == 4 || r == 2) ? r : 1;
+}
+
+// ---- tensor-core GEMM (kq_gemm.cuh): host side ----------------------------------------------------------
+// cuTensorMapEncodeTiled comes from the driver; the library links the runtime only, so the entry point is looked up.
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static EncodeTiledFn encode_tiled_fn() {
+    static EncodeTiledFn fn = [] {
+        void* f = nullptr;
+        cudaDriverEntryPointQueryResult qr;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &qr) != cudaSuccess || qr != cudaDriverEntryPointSuccess) {
+            (void)cudaGetLastError();
+            f = nullptr;
+        }
+        return (EncodeTiledFn)f;
+    }();
+    return fn;
+}
+
+static bool gemm_supported(const DevMatrix& w) { return (w.type == T_Q4_K || w.type == T_Q5_K) && w.out >= 1; }
+
+// The matrix as a 3-D byte tensor [panels][rows][panel row bytes]; box = one super-block of 128 rows.
+static int32_t gemm_tensor_maps(const DevMatrix& w, CUtensorMap& main_map, CUtensorMap& tail_map, int& kb_eff) {
+    EncodeTiledFn enc = encode_tiled_fn();
+    if (!enc) return fail(L2B_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+    const int bb = dev_block_bytes(w.type);
+    const int64_t nb = w.in / QK_K;
+    kb_eff = w.panels ? w.kb : (int)nb;
+    const int64_t full_panels = nb / kb_eff, tail_blocks = nb % kb_eff;
+    auto make = [&](CUtensorMap& m, uint8_t* base, int64_t blocks, int64_t panels) -> int32_t {
+        const cuuint64_t dims[3] = {(cuuint64_t)(blocks * bb), (cuuint64_t)w.out, (cuuint64_t)panels};
+        const cuuint64_t strides[2] = {(cuuint64_t)(blocks * bb), (cuuint64_t)(blocks * bb) * (cuuint64_t)w.out};
+        const cuuint32_t box[3] = {(cuuint32_t)bb, (cuuint32_t)GM_ROWS, 1u};
+        const cuuint32_t estr[3] = {1u, 1u, 1u};
+        const CUresult r = enc(&m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                               CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) return fail(L2B_ERR_CUDA, "cuTensorMapEncodeTiled failed with code " + std::to_string((int)r));
+        return L2B_OK;
+    };
+    if (full_panels > 0) L2B_TRY(make(main_map, w.data, kb_eff, full_panels));
+    if (tail_blocks > 0) L2B_TRY(make(tail_map, w.data + (size_t)full_panels * w.out * kb_eff * bb, tail_blocks, 1));
+    else tail_map = main_map;
+    if (full_panels == 0) main_map = tail_map;
+    return L2B_OK;
+}
+
+static size_t gemm_act_bytes(int64_t n_in, int n_tok) { return (size_t)((n_tok + GM_TOK - 1) / GM_TOK) * (size_t)(n_in / QK_K) * GM_ACT_BYTES; }
+
+// x [n_tok][ldx] f32 (optionally rmsnorm'ed with `gain`) -> int8 planes in the GEMM's operand layout
+static int32_t launch_quantise_rows(const float* x, const float* gain, uint8_t* act, int n, int ldx, int n_tok, cudaStream_t st) {
+    CU(cudaMemsetAsync(act, 0, gemm_act_bytes(n, n_tok), st));  // unused columns and tokens must read as zero
+    QuantRowsParams q;
+    q.x = x; q.gain = gain; q.act = act; q.n = n; q.ldx = ldx; q.n_tok = n_tok;
+    quantise_rows_kernel<<<n_tok, 512, 0, st>>>(q);
+    CU(cudaGetLastError());
+    return L2B_OK;
+}
+
+// y[t][ldy] (+= resid) = W x_t for n_tok activation vectors already quantised by launch_quantise_rows
+static int32_t launch_kq_gemm(const DevMatrix& w, const uint8_t* act, int n_tok, float* y, int ldy, const float* resid, int* status, cudaStream_t st) {
+    if (!gemm_supported(w)) return fail(L2B_ERR_UNSUPPORTED_TYPE, "the tensor-core GEMM takes q4_K and q5_K matrices");
+    CUtensorMap mm, mt;
+    int kb_eff = 0;
+    L2B_TRY(gemm_tensor_maps(w, mm, mt, kb_eff));
+    GemmParams g;
+    memset(&g, 0, sizeof(g));
+    g.type = w.type; g.rows = (int)w.out; g.nb = (int)(w.in / QK_K); g.kb = kb_eff; g.n_tok = n_tok;
+    g.act = act; g.y = y; g.resid = resid; g.ldy = ldy; g.mode = resid ? GM_RESIDUAL : GM_STORE; g.status = status;
+    const dim3 grid((unsigned)((w.out + GM_ROWS - 1) / GM_ROWS), (unsigned)((n_tok + GM_TOK - 1) / GM_TOK));
+    const size_t smem = (size_t)gm_smem_layout(dev_block_bytes(w.type)).total + 1024;  // + room to align the base to 1024 bytes
+    kq_gemm_kernel<<<grid, GM_THREADS, smem, st>>>(g, mm, mt);
+    CU(cudaGetLastError());
+    return L2B_OK;
+}
+
+// Buffers of a many-token pass: activations of up to PF_MAX_TOK tokens, attention scratch, quantised activations.
+struct GemmBufs {
+    float *x = nullptr, *q = nullptr, *k = nullptr, *v = nullptr, *att = nullptr, *g = nullptr, *u = nullptr;
+    float *pm = nullptr, *pl = nullptr, *pacc = nullptr;
+    int* tickets = nullptr;
+    uint8_t* act = nullptr;
+    int nsplit = 1;
+};
+
+static void free_gemm_bufs(GemmBufs& B) {
+    void* pf[] = {B.x, B.q, B.k, B.v, B.att, B.g, B.u, B.pm, B.pl, B.pacc, B.tickets, B.act};
+    for (void* b : pf)
+        if (b) cudaFree(b);
+    B = GemmBufs();
 }
 
 // cos/sin of the iterated f32 angle, exactly as rope_normal!/rope_neox! advance it
@@ -478,6 +570,9 @@ struct l2b_session {
     size_t tp_flag_off = 0, tp_bytes = 0;
     unsigned* tp_epoch = nullptr;  // tokens completed (device word)
     uint8_t* peer_mem[MV_MAX_TP] = {nullptr};  // [r]: rank r's tp_mem as seen from this process ([rank] = own)
+    // many-token prompt pass through the tensor-core GEMM (kq_gemm.cuh): buffers for PF_MAX_TOK tokens, allocated on first use
+    bool pf_checked = false, pf_ok = false;
+    GemmBufs pf;
     // one persistent kernel per token (token_kernel.cuh): k-quant models on one GPU
     bool tk = false;
     TkOp* tk_ops = nullptr;
@@ -833,6 +928,7 @@ static void session_free(l2b_session* s) {
     if (s->tp_mem) cudaFree(s->tp_mem);
     if (s->tp_epoch) cudaFree(s->tp_epoch);
     if (s->tp_descs) cudaFree(s->tp_descs);
+    free_gemm_bufs(s->pf);
     if (s->tk_ops) cudaFree(s->tk_ops);
     if (s->tk_sync) cudaFree(s->tk_sync);
     if (s->tk_trace) cudaFree(s->tk_trace);
@@ -1570,6 +1666,135 @@ static int32_t run_one(l2b_session* s, int token, int pos, float temperature, do
     return check_status_word(s);
 }
 
+// ---- many-token prompt pass ---------------------------------------------------------------------------------
+// The reference runs transformer! once per prompt token (src/inference.jl:349-356).  For prompt positions that are all followed
+// by a prompt token (no logits needed) the layers are run for up to PF_MAX_TOK tokens at once: every matrix product is one
+// launch of the tensor-core GEMM (20 tokens per pass over a weight tile), the element-wise steps are small kernels over
+// [tokens][dim] arrays, attention serves every token's query against the cache (causal: token t sees positions <= pos0 + t).
+// Needs q4_K / q5_K layer matrices, three activation planes, one GPU; otherwise the caller uses the decode passes.
+constexpr int PF_MAX_TOK = 240;
+constexpr int PF_MIN_TOK = 12;
+
+// Every layer for n tokens whose residual-stream rows are in B.x.  One sequence: token t sits at position pos0 + t and the
+// layer's caches are kc / vc + l * layer_stride.  Batched decode (pos_list non-null): token t is the next position pos_list[t]
+// of sequence t, whose caches lie seq_stride * t further.
+static int32_t enqueue_layers_gemm(const l2b_model* m, const GemmBufs& B, int n, float* kc, float* vc, size_t layer_stride, int pos0, const int* pos_list,
+                                   size_t seq_stride, const float* rope_cs, int gq, int* status, cudaStream_t st) {
+    const l2b_config& c = m->cfg;
+    const int hs = c.dim / c.n_heads, kv_dim = hs * c.n_kv_heads;
+    for (int l = 0; l < c.n_layers; ++l) {
+        const LayerW& w = m->layers[l];
+        float* kcl = kc + (size_t)l * layer_stride;
+        float* vcl = vc + (size_t)l * layer_stride;
+        L2B_TRY(launch_quantise_rows(B.x, w.rms_att, B.act, c.dim, c.dim, n, st));
+        L2B_TRY(launch_kq_gemm(w.wq, B.act, n, B.q, c.dim, nullptr, status, st));
+        L2B_TRY(launch_kq_gemm(w.wk, B.act, n, B.k, kv_dim, nullptr, status, st));
+        L2B_TRY(launch_kq_gemm(w.wv, B.act, n, B.v, kv_dim, nullptr, status, st));
+        RopeKvParams r;
+        memset(&r, 0, sizeof(r));
+        r.q = B.q; r.k = B.k; r.v = B.v; r.kc = kcl; r.vc = vcl; r.rope_cs = rope_cs;
+        r.n_tok = n; r.q_dim = c.dim; r.kv_dim = kv_dim; r.hs = hs; r.seq_len = c.seq_len; r.pos0 = pos0; r.neox = c.rope_is_neox;
+        r.pos_list = pos_list; r.cache_stride = seq_stride;
+        rope_kv_kernel<<<dim3(8, n), 256, 0, st>>>(r);
+        CU(cudaGetLastError());
+        AttnParams a;
+        memset(&a, 0, sizeof(a));
+        a.q = B.q; a.kc = kcl; a.vc = vcl; a.out = B.att; a.tickets = B.tickets;
+        a.part_m = B.pm; a.part_l = B.pl; a.part_acc = B.pacc;
+        a.pos = nullptr; a.pos_base = pos0; a.pos_list = pos_list; a.cache_stride_q = seq_stride;
+        a.n_heads = c.n_heads; a.n_kv = c.n_kv_heads; a.hs = hs; a.seq_len = c.seq_len; a.nsplit = B.nsplit;
+        a.nq = std::max(n, 2);  // (a one-token pass takes the many-query form of the kernel too: the second query copy leaves at once)
+        a.q_stride = c.dim;
+        a.min_chunk = 256;  // many queries already fill the GPU: split a query's positions only when there are many
+        if (n < 2) return fail(L2B_ERR_BAD_ARG, "a many-token pass needs at least two tokens");
+        CU(launch_attention(a, gq, st, false));
+        L2B_TRY(launch_quantise_rows(B.att, nullptr, B.act, c.dim, c.dim, n, st));
+        L2B_TRY(launch_kq_gemm(w.wo, B.act, n, B.x, c.dim, B.x, status, st));
+        L2B_TRY(launch_quantise_rows(B.x, w.rms_ffn, B.act, c.dim, c.dim, n, st));
+        L2B_TRY(launch_kq_gemm(w.w1, B.act, n, B.g, c.hidden_dim, nullptr, status, st));
+        L2B_TRY(launch_kq_gemm(w.w3, B.act, n, B.u, c.hidden_dim, nullptr, status, st));
+        swiglu_rows_kernel<<<1184, 256, 0, st>>>(B.g, B.u, (size_t)n * c.hidden_dim);
+        CU(cudaGetLastError());
+        L2B_TRY(launch_quantise_rows(B.g, nullptr, B.act, c.hidden_dim, c.hidden_dim, n, st));
+        L2B_TRY(launch_kq_gemm(w.w2, B.act, n, B.x, c.dim, B.x, status, st));
+    }
+    return L2B_OK;
+}
+
+static bool gemm_layers_supported(const l2b_model* m) {
+    if (m->tp != 1 || m->planes != 3 || !encode_tiled_fn() || m->tok_emb.type == T_F32) return false;
+    for (const LayerW& w : m->layers) {
+        const DevMatrix* ms[] = {&w.wq, &w.wk, &w.wv, &w.wo, &w.w1, &w.w2, &w.w3};
+        for (const DevMatrix* x : ms)
+            if (!gemm_supported(*x)) return false;
+    }
+    return true;
+}
+
+static bool alloc_gemm_bufs(const l2b_model* m, GemmBufs& B, size_t T) {
+    const l2b_config& c = m->cfg;
+    const int hs = c.dim / c.n_heads, kv_dim = hs * c.n_kv_heads;
+    B.nsplit = c.seq_len >= 2048 ? 4 : 1;
+    auto alloc = [&](auto*& ptr, size_t bytes) { return cudaMalloc((void**)&ptr, bytes) == cudaSuccess; };
+    bool ok = alloc(B.x, T * c.dim * 4) && alloc(B.q, T * c.dim * 4) && alloc(B.k, T * kv_dim * 4) && alloc(B.v, T * kv_dim * 4) &&
+              alloc(B.att, T * c.dim * 4) && alloc(B.g, T * c.hidden_dim * 4) && alloc(B.u, T * c.hidden_dim * 4) &&
+              alloc(B.pm, T * c.n_heads * B.nsplit * 4) && alloc(B.pl, T * c.n_heads * B.nsplit * 4) &&
+              alloc(B.pacc, T * c.n_heads * B.nsplit * hs * 4) && alloc(B.tickets, T * c.n_heads * 4) &&
+              alloc(B.act, gemm_act_bytes(std::max(c.dim, c.hidden_dim), (int)T));
+    if (ok) ok = cudaMemset(B.tickets, 0, T * c.n_heads * 4) == cudaSuccess;
+    if (!ok) {
+        (void)cudaGetLastError();
+        free_gemm_bufs(B);
+    }
+    return ok;
+}
+
+static bool prefill_gemm_eligible(l2b_session* s) {
+    if (s->pf_checked) return s->pf_ok;
+    s->pf_checked = true;
+    // (a pass that cannot get its buffers leaves prompts to the decode passes)
+    s->pf_ok = env_long("L2B_PREFILL_GEMM", 1) != 0 && gemm_layers_supported(s->model) && alloc_gemm_bufs(s->model, s->pf, PF_MAX_TOK);
+    return s->pf_ok;
+}
+
+// Positions pos0 .. pos0 + n - 1 of the prompt already in s->prompt (device), 2 <= n <= PF_MAX_TOK; all enqueued on the session stream.
+static int32_t enqueue_prefill_gemm(l2b_session* s, int pos0, int n) {
+    const l2b_model* m = s->model;
+    const l2b_config& c = m->cfg;
+    cudaStream_t st = s->stream;
+    embed_rows_kernel<<<dim3(std::max(1, std::min(16, c.dim / 256)), n), 256, 0, st>>>(m->tok_emb.type, m->tok_emb.data, m->tok_emb.d6, s->prompt + pos0, c.dim,
+                                                                                      c.vocab_size, s->pf.x);
+    CU(cudaGetLastError());
+    L2B_TRY(enqueue_layers_gemm(m, s->pf, n, s->kc, s->vc, kv_layer_elems(m), pos0, nullptr, 0, s->rope_cs, s->gq, s->status, st));
+    fill_forced_kernel<<<1, 256, 0, st>>>(s->prompt, s->out_tokens, pos0, n);
+    CU(cudaGetLastError());
+    return L2B_OK;
+}
+
+// Feed the forced positions [from, to) (each followed by a prompt token) and leave the loop state at position `to`, whose
+// token is host_tokens[to - base].  Many-token passes where possible, the decode graphs for the rest.
+static int32_t enqueue_forced_positions(l2b_session* s, int from, int to, const int32_t* host_prompt_at_from) {
+    int i = from;
+    if (to - from >= PF_MIN_TOK && prefill_gemm_eligible(s)) {
+        while (i < to) {
+            const int n = std::min(PF_MAX_TOK, to - i);
+            L2B_TRY(enqueue_prefill_gemm(s, i, n));
+            i += n;
+        }
+        // the decode graphs read the loop state from the device: move it to position i
+        Control& h = *s->h_ctl;
+        h.token = host_prompt_at_from[i - from];
+        h.pos = i;
+        CU(cudaMemcpyAsync(s->ctl, s->h_ctl, sizeof(Control), cudaMemcpyHostToDevice, s->stream));
+    }
+    while (i < to) {
+        const bool pair = s->graph2 && i + 2 <= to;
+        CU(cudaGraphLaunch(pair ? s->graph2 : s->graph, s->stream));
+        i += pair ? 2 : 1;
+    }
+    return L2B_OK;
+}
+
 #ifdef L2B_MEASURE
 static void dump_token_trace(l2b_session* s) {
     const int nl = s->trace_launches, sms = s->di.sms;
@@ -1648,11 +1873,8 @@ extern "C" int32_t l2b_prefill(l2b_session* s, const int32_t* tokens, int32_t n,
     CU(cudaMemcpyAsync(s->prompt + pos0, tokens, (size_t)n * 4, cudaMemcpyHostToDevice, s->stream));
     CU(cudaMemcpyAsync(s->ctl, s->h_ctl, sizeof(Control), cudaMemcpyHostToDevice, s->stream));
     const int end = pos0 + n;
-    for (int i = pos0; i < end;) {
-        const bool pair = s->graph2 && i + 2 < end;
-        CU(cudaGraphLaunch(pair ? s->graph2 : s->graph, s->stream));
-        i += pair ? 2 : 1;
-    }
+    L2B_TRY(enqueue_forced_positions(s, pos0, end - 1, tokens));  // every position but the last is followed by a prompt token
+    CU(cudaGraphLaunch(s->graph, s->stream));                     // the last one: its logits are wanted
     CU(cudaMemcpyAsync(&s->h_small[0], s->next_token, 4, cudaMemcpyDeviceToHost, s->stream));
     CU(cudaMemcpyAsync(&s->h_small[1], s->status, 4, cudaMemcpyDeviceToHost, s->stream));
     CU(cudaEventRecord(s->ev1, s->stream));
@@ -1693,14 +1915,14 @@ extern "C" int32_t l2b_generate(l2b_session* s, const int32_t* prompt, int32_t n
     // Positions p and p + 1 go through one two-position pass when both are followed by a prompt token (their next
     // tokens are forced, so neither needs logits); everything else takes the one-position graph.
     bool mid = false;
-    for (int i = 0; i < n_positions;) {
+    const int forced_end = std::min(n_prompt - 1, n_positions);  // positions below this are followed by a prompt token
+    L2B_TRY(enqueue_forced_positions(s, 0, forced_end, prompt));
+    for (int i = forced_end; i < n_positions; ++i) {
         if (i >= n_prompt && !mid) {  // the first position that is fed a generated token
             CU(cudaEventRecord(s->ev_mid, s->stream));
             mid = true;
         }
-        const bool pair = s->graph2 && i + 2 < n_prompt && i + 1 < n_positions;
-        CU(cudaGraphLaunch(pair ? s->graph2 : s->graph, s->stream));
-        i += pair ? 2 : 1;
+        CU(cudaGraphLaunch(s->graph, s->stream));
     }
     if (!mid) CU(cudaEventRecord(s->ev_mid, s->stream));
     CU(cudaEventRecord(s->ev1, s->stream));
@@ -1755,6 +1977,156 @@ extern "C" int32_t l2b_session_last_phase_ms(l2b_session* s, float* prompt_ms, f
 extern "C" int32_t l2b_session_kernels_per_token(l2b_session* s, int32_t* n) {
     if (!s || !n) return fail(L2B_ERR_BAD_ARG, "null argument");
     *n = s->kernels_per_token;
+    return L2B_OK;
+}
+
+// ---------------------------------------------------------------------------------------------
+// batched decode: several independent sequences in lock step (no counterpart in the reference,
+// whose `sample` serves one prompt)
+// ---------------------------------------------------------------------------------------------
+struct l2b_batch {
+    l2b_model* model = nullptr;
+    int n_seq = 0;
+    cudaStream_t stream = nullptr;
+    DeviceInfo di;
+    GemmBufs B;
+    float *kc = nullptr, *vc = nullptr;  // [layer][sequence][kv_head][seq_len][hs]
+    float* rope_cs = nullptr;
+    float* logits = nullptr;             // [n_seq][vocab]
+    int *tokens = nullptr, *pos = nullptr, *next = nullptr, *status = nullptr;
+    int* h_io = nullptr;                 // pinned: tokens, positions, next tokens, status
+    int gq = 1;
+};
+
+static void batch_free(l2b_batch* b) {
+    if (!b) return;
+    free_gemm_bufs(b->B);
+    void* bufs[] = {b->kc, b->vc, b->rope_cs, b->logits, b->tokens, b->pos, b->next, b->status};
+    for (void* p : bufs)
+        if (p) cudaFree(p);
+    if (b->h_io) cudaFreeHost(b->h_io);
+    if (b->stream) cudaStreamDestroy(b->stream);
+    delete b;
+}
+
+extern "C" int32_t l2b_batch_create(l2b_model* m, int32_t n_seq, l2b_batch** out) {
+    if (!m || !out) return fail(L2B_ERR_BAD_ARG, "null argument");
+    *out = nullptr;
+    if (!m->finalized) return fail(L2B_ERR_STATE, "l2b_model_finalize has not been called");
+    if (n_seq < 2 || n_seq > PF_MAX_TOK) return fail(L2B_ERR_BAD_ARG, "a batch holds 2 .. " + std::to_string(PF_MAX_TOK) + " sequences");
+    CU(cudaSetDevice(m->device));
+    L2B_TRY(check_kernel_attrs());
+    if (!gemm_layers_supported(m))
+        return fail(L2B_ERR_UNSUPPORTED_TYPE, "batched decode needs q4_K / q5_K layer matrices, three activation planes and one GPU");
+    const l2b_config& c = m->cfg;
+    const int hs = c.dim / c.n_heads;
+    l2b_batch* b = new l2b_batch();
+    b->model = m;
+    b->n_seq = n_seq;
+    auto run = [&]() -> int32_t {
+        L2B_TRY(query_device(b->di));
+        CU(cudaStreamCreateWithFlags(&b->stream, cudaStreamNonBlocking));
+        b->gq = choose_gq(c.n_heads, c.n_kv_heads);
+        if (!alloc_gemm_bufs(m, b->B, (size_t)n_seq)) return fail(L2B_ERR_OOM, "out of device memory for the batch buffers");
+        const size_t cache = kv_layer_elems(m) * c.n_layers * (size_t)n_seq * 4;
+        CU(cudaMalloc(&b->kc, cache));
+        CU(cudaMalloc(&b->vc, cache));
+        CU(cudaMemsetAsync(b->kc, 0, cache, b->stream));
+        CU(cudaMemsetAsync(b->vc, 0, cache, b->stream));
+        CU(cudaMalloc(&b->logits, (size_t)n_seq * c.vocab_size * 4));
+        CU(cudaMalloc(&b->tokens, (size_t)n_seq * 4));
+        CU(cudaMalloc(&b->pos, (size_t)n_seq * 4));
+        CU(cudaMalloc(&b->next, (size_t)n_seq * 4));
+        CU(cudaMalloc(&b->status, 4));
+        CU(cudaMemsetAsync(b->status, 0, 4, b->stream));
+        CU(cudaMallocHost(&b->h_io, (size_t)(3 * n_seq + 1) * 4));
+        std::vector<float> cs;
+        rope_table_host(cs, c.seq_len, hs, c.rope_freq_base);
+        CU(cudaMalloc(&b->rope_cs, cs.size() * 4));
+        CU(cudaMemcpyAsync(b->rope_cs, cs.data(), cs.size() * 4, cudaMemcpyHostToDevice, b->stream));
+        CU(cudaStreamSynchronize(b->stream));
+        return L2B_OK;
+    };
+    const int32_t st = run();
+    if (st != L2B_OK) {
+        batch_free(b);
+        return st;
+    }
+    *out = b;
+    return L2B_OK;
+}
+
+extern "C" int32_t l2b_batch_destroy(l2b_batch* b) {
+    if (!b) return L2B_OK;
+    cudaSetDevice(b->model->device);
+    if (b->stream) cudaStreamSynchronize(b->stream);
+    batch_free(b);
+    return L2B_OK;
+}
+
+extern "C" int32_t l2b_batch_reset(l2b_batch* b) {
+    if (!b) return fail(L2B_ERR_BAD_ARG, "null batch");
+    CU(cudaSetDevice(b->model->device));
+    const size_t cache = kv_layer_elems(b->model) * b->model->cfg.n_layers * (size_t)b->n_seq * 4;
+    CU(cudaMemsetAsync(b->kc, 0, cache, b->stream));
+    CU(cudaMemsetAsync(b->vc, 0, cache, b->stream));
+    CU(cudaStreamSynchronize(b->stream));
+    return L2B_OK;
+}
+
+extern "C" int32_t l2b_batch_decode_next(l2b_batch* b, const int32_t* tokens, const int32_t* positions, int32_t* next_tokens, float* host_logits) {
+    if (!b || !tokens || !positions || !next_tokens) return fail(L2B_ERR_BAD_ARG, "null argument");
+    const l2b_model* m = b->model;
+    const l2b_config& c = m->cfg;
+    const int n = b->n_seq;
+    for (int i = 0; i < n; ++i) {
+        if (tokens[i] < 0 || tokens[i] >= c.vocab_size) return fail(L2B_ERR_BAD_ARG, "token id out of range");
+        if (positions[i] < 0 || positions[i] >= c.seq_len) return fail(L2B_ERR_BAD_ARG, "position out of range (seq_len)");
+    }
+    CU(cudaSetDevice(m->device));
+    cudaStream_t st = b->stream;
+    memcpy(b->h_io, tokens, (size_t)n * 4);
+    memcpy(b->h_io + n, positions, (size_t)n * 4);
+    CU(cudaMemcpyAsync(b->tokens, b->h_io, (size_t)n * 4, cudaMemcpyHostToDevice, st));
+    CU(cudaMemcpyAsync(b->pos, b->h_io + n, (size_t)n * 4, cudaMemcpyHostToDevice, st));
+    embed_rows_kernel<<<dim3(std::max(1, std::min(16, c.dim / 256)), n), 256, 0, st>>>(m->tok_emb.type, m->tok_emb.data, m->tok_emb.d6, b->tokens, c.dim,
+                                                                                      c.vocab_size, b->B.x);
+    CU(cudaGetLastError());
+    const size_t kvl = kv_layer_elems(m);
+    L2B_TRY(enqueue_layers_gemm(m, b->B, n, b->kc, b->vc, kvl * (size_t)n, 0, b->pos, kvl, b->rope_cs, b->gq, b->status, st));
+    // final rmsnorm + classifier (src/inference.jl:309-312) for every sequence, then argmax (:360)
+    if (gemm_supported(m->output)) {
+        L2B_TRY(launch_quantise_rows(b->B.x, m->rms_final, b->B.act, c.dim, c.dim, n, st));
+        L2B_TRY(launch_kq_gemm(m->output, b->B.act, n, b->logits, c.vocab_size, nullptr, b->status, st));
+    } else {  // a q6_K classifier: one pass of the matrix-vector kernel per sequence
+        for (int i = 0; i < n; ++i) {
+            MvLaunch L;
+            memset(&L.p, 0, sizeof(L.p));
+            L.planes = m->planes;
+            L.p.n_in = c.dim;
+            L.p.seg[L.p.nseg++] = make_segment(m->output, PAIR_ADJACENT, EPI_STORE, b->logits + (size_t)i * c.vocab_size, 0);
+            L.kb = m->output.kb;
+            L.p.pro = PRO_RMSNORM;
+            L.p.gain = m->rms_final;
+            L.p.x_in = b->B.x + (size_t)i * c.dim;
+            L.p.status = b->status;
+            L2B_TRY(plan_matvec(L, b->di));
+            CU(launch_matvec(L, st, false));
+        }
+    }
+    argmax_rows_kernel<<<n, 1024, 0, st>>>(b->logits, c.vocab_size, b->next, b->status);
+    CU(cudaGetLastError());
+    CU(cudaMemcpyAsync(b->h_io + 2 * n, b->next, (size_t)n * 4, cudaMemcpyDeviceToHost, st));
+    CU(cudaMemcpyAsync(b->h_io + 3 * n, b->status, 4, cudaMemcpyDeviceToHost, st));
+    if (host_logits) CU(cudaMemcpyAsync(host_logits, b->logits, (size_t)n * c.vocab_size * 4, cudaMemcpyDeviceToHost, st));
+    CU(cudaStreamSynchronize(st));
+    const int dev_status = b->h_io[3 * n];
+    if (dev_status != DEV_OK) {
+        cudaMemsetAsync(b->status, 0, 4, st);
+        if (dev_status == DEV_ERR_BAD_INDEX) return fail(L2B_ERR_CUDA, "no valid token could be chosen (the logits are not finite); token 0 was substituted");
+        return fail(dev_status == DEV_ERR_TMA_TIMEOUT ? L2B_ERR_TIMEOUT : L2B_ERR_CUDA, "kernel reported device status " + std::to_string(dev_status));
+    }
+    memcpy(next_tokens, b->h_io + 2 * n, (size_t)n * 4);
     return L2B_OK;
 }
 
@@ -2082,8 +2454,18 @@ extern "C" int32_t l2b_matrix_matvec(l2b_matrix* m, const float* host_x, int32_t
     DevBuf x, y;
     L2B_TRY(dev_upload(x, host_x, (size_t)ncols * w.in * 4));
     L2B_TRY(dev_alloc(y, (size_t)ncols * w.out * 4));
-    for (int c = 0; c < ncols; ++c)
-        L2B_TRY(l2b_matrix_matvec_device(m, 0, x.as<float>() + (size_t)c * w.in, y.as<float>() + (size_t)c * w.out, planes, nullptr));
+    // Several columns: one pass of the tensor-core GEMM per 20 columns (every weight is unpacked once for all of them)
+    // instead of one matrix-vector pass per column.  L2B_GEMM_MIN_COLS sets the threshold (default 4; 0 switches it off).
+    const long gemm_min = env_long("L2B_GEMM_MIN_COLS", 4);
+    if (gemm_min > 0 && ncols >= gemm_min && (planes == 0 || planes == 3) && gemm_supported(w)) {
+        DevBuf act;
+        L2B_TRY(dev_alloc(act, gemm_act_bytes(w.in, ncols)));
+        L2B_TRY(launch_quantise_rows(x.as<float>(), nullptr, act.as<uint8_t>(), (int)w.in, (int)w.in, ncols, nullptr));
+        L2B_TRY(launch_kq_gemm(w, act.as<uint8_t>(), ncols, y.as<float>(), (int)w.out, nullptr, m->status, nullptr));
+    } else {
+        for (int c = 0; c < ncols; ++c)
+            L2B_TRY(l2b_matrix_matvec_device(m, 0, x.as<float>() + (size_t)c * w.in, y.as<float>() + (size_t)c * w.out, planes, nullptr));
+    }
     CU(cudaDeviceSynchronize());
 #ifdef L2B_MEASURE
     if (env_long("L2B_MV_TRACE", 0)) {  // measurement aid: per-block timeline of one more launch, printed to stderr

@@ -27,19 +27,25 @@ struct AttnParams {
     float* part_l;    // [n_heads][nsplit]
     float* part_acc;  // [n_heads][nsplit][hs]
     int* tickets;     // [n_heads / GQ], zero before the launch; left zero after it
-    const int* pos;   // device scalar, 0-based position of the query; positions 0..pos are attended
+    const int* pos;   // device scalar, 0-based position of the (first) query; positions 0..pos are attended.  Null: pos_base
     int n_heads, n_kv, hs, seq_len, nsplit;
     int npos_override;  // >0: attend exactly this many positions (isolated-operator entry point)
     int nq;             // 2: two consecutive query positions (pos, pos + 1) per launch; 0 or 1: one
     int q_stride;       // elements between the two positions' q (and out) vectors
     int min_chunk;      // positions per split below which splitting is not worth it (0: ATTN_MIN_CHUNK)
+    int pos_base;       // position of the first query when `pos` is null (launches outside the captured token graph)
+    const int* pos_list;     // batched decode: query qi belongs to its own sequence, at position pos_list[qi] ...
+    size_t cache_stride_q;   // ... whose caches start cache_stride_q * qi elements after kc / vc
 };
 
 constexpr int ATTN_WARPS = 4;
 constexpr int ATTN_UNROLL = 4;      // positions whose key/value loads a warp keeps in flight
 constexpr int ATTN_MIN_CHUNK = 16;  // positions per split below which splitting costs more than it saves
 
-template <int GQ, int NQ = 1>  // GQ: query heads served per block (divides n_heads / n_kv); NQ: query positions per launch
+// GQ: query heads served per block (divides n_heads / n_kv).  NQ = 1: one query position per launch; any other value: the grid
+// holds p.nq copies of the (head group, split) blocks, copy qi serving the query at position pos + qi (2 in the two-position
+// prompt passes of the decode chain, up to a few hundred in the many-token prompt pass).
+template <int GQ, int NQ = 1>
 __device__ __forceinline__ void attention_split_body(const AttnParams& p) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     // with two query positions the grid holds two copies of the (head group, split) blocks: copy qi serves position pos + qi
@@ -48,7 +54,9 @@ __device__ __forceinline__ void attention_split_body(const AttnParams& p) {
     const int bx = (int)blockIdx.x - qi * ngroups * p.nsplit;
     const int hg = bx / p.nsplit, sp = bx % p.nsplit;
     const int kvh = (hg * GQ) / (p.n_heads / p.n_kv);
-    const int npos = p.npos_override > 0 ? p.npos_override : (__ldcg(p.pos) + 1 + qi);
+    const int npos = p.npos_override > 0 ? p.npos_override
+                     : (NQ != 1 && p.pos_list) ? __ldg(p.pos_list + qi) + 1
+                                               : ((p.pos ? __ldcg(p.pos) : p.pos_base) + 1 + qi);
     const float* const qbase = p.q + (size_t)qi * p.q_stride;
     float* const obase = p.out + (size_t)qi * p.q_stride;
     const int hq = qi * p.n_heads;   // first row of this position in the partial-result scratch
@@ -75,8 +83,9 @@ __device__ __forceinline__ void attention_split_body(const AttnParams& p) {
         m[g] = -INFINITY;
         l[g] = 0.f;
     }
-    const float* kbase = p.kc + (size_t)kvh * p.seq_len * hs;
-    const float* vbase = p.vc + (size_t)kvh * p.seq_len * hs;
+    const size_t seq_off = (NQ != 1) ? (size_t)qi * p.cache_stride_q : 0;
+    const float* kbase = p.kc + seq_off + (size_t)kvh * p.seq_len * hs;
+    const float* vbase = p.vc + seq_off + (size_t)kvh * p.seq_len * hs;
     for (int tb = t0 + warp * ATTN_UNROLL; tb < t1; tb += ATTN_WARPS * ATTN_UNROLL) {
         float4 kk[ATTN_UNROLL], vv[ATTN_UNROLL];
 #pragma unroll

@@ -230,6 +230,42 @@ class RunState:
         self.logits = np.zeros(model.config.vocab_size, dtype=np.float32)
 
 
+class BatchRunState:
+    """Several RunStates (src/inference.jl:72-100) decoded in lock step: one zeroed KV cache per sequence, one position per call
+    for all of them.  No counterpart in the reference, whose `sample` serves one prompt; the per-sequence arithmetic is
+    transformer! unchanged."""
+
+    def __init__(self, model: LanguageModel, n_seq: int):
+        self.model, self.n_seq = model, n_seq
+        self.batch = C.c_void_p()
+        L.check(L.lib().l2b_batch_create(model.device_model().model, int(n_seq), C.byref(self.batch)))
+        self.logits = np.zeros((n_seq, model.config.vocab_size), dtype=np.float32)
+
+    def decode_next(self, tokens, positions, want_logits: bool = False) -> np.ndarray:
+        """tokens[i] at position positions[i] of sequence i; returns the greedy next token of every sequence."""
+        t = np.ascontiguousarray(tokens, dtype=np.int32)
+        p = np.ascontiguousarray(positions, dtype=np.int32)
+        if t.size != self.n_seq or p.size != self.n_seq:
+            raise ValueError("one token and one position per sequence")
+        nxt = np.zeros(self.n_seq, dtype=np.int32)
+        L.check(L.lib().l2b_batch_decode_next(self.batch, L.ptr(t), L.ptr(p), L.ptr(nxt), L.ptr(self.logits) if want_logits else None))
+        return nxt
+
+    def reset(self):
+        L.check(L.lib().l2b_batch_reset(self.batch))
+
+    def close(self):
+        if self.batch:
+            L.lib().l2b_batch_destroy(self.batch)
+            self.batch = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
 def matmul_(y: np.ndarray, A: Matrix, x: np.ndarray, act_planes: int = 0) -> None:
     """matmul!(y, A, x): y .= A' * x (src/matmul.jl:3-23).  x may hold several columns, shape (ncols, in)."""
     t, data, i, o = _matrix_info(A)
