@@ -319,7 +319,6 @@ def run_ours(args):
     wbytes = model.weight_bytes_per_token()
     kpt = model.kernels_per_token()
     pairs = model.prefill_pairs()
-    schedule = pass_schedule(n_prompt, n_pos, pairs)
     sess = model.device_model().session
     lib = L.lib()
 
@@ -383,9 +382,16 @@ def run_ours(args):
     peak, peak_kind = measured_peak()
     value = streams * n_decode * args.steps / (decode_ms / 1e3) if n_decode else 0.0
     algo, achieved, frac = decode_roofline(cfg, wbytes, n_prompt, n_pos, decode_ms / args.steps, peak) if n_decode else (0, 0.0, 0.0)
-    n_pair_passes = sum(1 for p, k in schedule if k == 2)
-    prompt_passes = sum(1 for p, k in schedule if p < n_prompt)
-    decode_launches = kpt * n_decode
+    launches_per_step = model.last_launches()  # of the l2b_generate call above, counted by the library as it enqueues
+    forced = max(min(n_prompt - 1, n_pos), 0)  # prompt positions that are followed by a prompt token (no logits needed)
+    gemm_min = model.prefill_gemm_min_tokens()
+    if gemm_min and forced >= gemm_min:
+        prefill_how = ("%d forced positions through the tensor-core GEMM pass (tcgen05 + TMA, 20 tokens per pass over a weight tile, "
+                       "no logits for forced positions), the last prompt position through the decode kernels" % forced)
+    elif pairs:
+        prefill_how = "two positions per pass of the decode kernels where both are followed by a prompt token (no logits for forced positions)"
+    else:
+        prefill_how = "position by position"
     line = {
         "metric": METRIC, "value": round(value, 2), "unit": "tok/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": round((prompt_ms + decode_ms) / args.steps, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
@@ -394,9 +400,7 @@ def run_ours(args):
         "config": shared_config(wl_name, spec, world, False),
         "value_scope": "the %d decode positions (fed generated tokens) only; prompt positions are reported under `prefill`" % n_decode,
         "prefill": {"value": round(streams * n_prompt * args.steps / (prompt_ms / 1e3), 2), "unit": "tok/s", "positions": n_prompt,
-                    "passes": prompt_passes, "ms": round(prompt_ms / args.steps, 3),
-                    "how": ("two positions per pass where both are followed by a prompt token (%d such passes; no logits for forced positions)" % n_pair_passes)
-                    if pairs else "position by position"},
+                    "ms": round(prompt_ms / args.steps, 3), "how": prefill_how},
         "blended": {"value": round(streams * n_pos * args.steps / ((prompt_ms + decode_ms) / 1e3), 2), "unit": "positions/s",
                     "note": "all positions / device time: what `sample` prints (src/inference.jl:391-392)"},
         "e2e": {"value": round(streams * n_decode * e2e_steps / percall_s, 2) if n_decode else 0.0, "unit": "tok/s",
@@ -405,8 +409,7 @@ def run_ours(args):
                         "a step here is one position",
                 "loop_call": {"value": round(streams * n_pos * e2e_steps / loop_s, 2), "unit": "positions/s", "h2d_bytes": 4 * n_prompt + 48,
                               "d2h_bytes": 4 * n_pos + 4, "note": "one l2b_generate call for all positions (host prompt in, host tokens out), wall clock"}},
-        # a two-position pass runs the kernel chain (2 embedding rows, 5 launches per layer, the advance); every other pass kpt launches
-        "gpu_launches": (n_pair_passes * (5 * cfg.n_layers + 3) + (len(schedule) - n_pair_passes) * kpt) * args.steps,
+        "gpu_launches": launches_per_step * args.steps,  # kernels of this library enqueued by the timed l2b_generate calls
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s", "frac": round(frac, 4),
                      "traffic": None, "peak_kind": peak_kind, "frac_of_nominal_8000": round(achieved / 8000.0, 4),
                      "scope": "decode positions: weight + KV bytes per position / device time per position (every kernel of the token)",

@@ -194,10 +194,18 @@ int32_t l2b_session_last_phase_ms(l2b_session* session, float* prompt_ms, float*
  * Afterwards the session holds the logits of the last prompt position (l2b_session_logits); *next (may be NULL) is their argmax.
  * Continue with l2b_decode_next(session, chosen_token, pos0 + n, ...). */
 int32_t l2b_prefill(l2b_session* session, const int32_t* tokens, int32_t n, int32_t pos0, int32_t* next);
+/* *min_tokens > 0: runs of at least that many prompt positions that are all followed by a prompt token go through the
+ * many-token pass (every matrix product one launch of the tensor-core GEMM, tcgen05 + TMA, 20 tokens per pass over a weight
+ * tile; up to 240 tokens per pass over the layers).  0: not available for this model (needs q4_K / q5_K layer matrices, three
+ * activation planes, one GPU; L2B_PREFILL_GEMM=0 switches it off) -- prompts then go through the decode kernels.  The reference
+ * feeds prompts token by token (src/inference.jl:349-356). */
+int32_t l2b_session_prefill_gemm(l2b_session* session, int32_t* min_tokens);
 /* 1 when l2b_generate feeds prompts two positions per pass (k-quant model, three activation planes, one GPU, everything fits in
  * shared memory; switch off with L2B_PREFILL_PAIRS=0): positions p, p+1 that are both followed by a prompt token share one pass
  * over the weights, and no logits are computed for them.  The reference feeds prompts token by token (src/inference.jl:349-356). */
 int32_t l2b_session_prefill_pairs(l2b_session* session, int32_t* enabled);
+/* Kernel launches the most recent l2b_forward / l2b_decode_next / l2b_prefill / l2b_generate call enqueued. */
+int32_t l2b_session_last_launches(l2b_session* session, int64_t* n);
 /* Number of kernel launches per token: 1 when the whole token is one persistent kernel (k-quant model on one GPU), else
  * 5 per layer + 3. */
 int32_t l2b_session_kernels_per_token(l2b_session* session, int32_t* n);

@@ -55,6 +55,7 @@ _SIGNATURES = {
     "l2b_session_read": ([_P, C.c_int32, _P, C.c_int64, C.POINTER(C.c_int64)], C.c_int32),
     "l2b_session_last_device_ms": ([_P, C.POINTER(C.c_float)], C.c_int32),
     "l2b_session_last_phase_ms": ([_P, C.POINTER(C.c_float), C.POINTER(C.c_float)], C.c_int32),
+    "l2b_session_last_launches": ([_P, C.POINTER(C.c_int64)], C.c_int32),
     "l2b_session_kernels_per_token": ([_P, C.POINTER(C.c_int32)], C.c_int32),
     "l2b_dequantize": ([C.c_int32, _P, C.c_int64, _P], C.c_int32),
     "l2b_quantize_q8k": ([_P, C.c_int64, C.c_int32, _P, _P, _P], C.c_int32),
@@ -76,6 +77,7 @@ _SIGNATURES = {
     "l2b_tokenizer_token": ([_P, C.c_int32, C.POINTER(_P), C.POINTER(C.c_int64)], C.c_int32),
     "l2b_tokenizer_encode": ([_P, _P, C.c_int64, C.c_int32, _P, C.c_int64, C.POINTER(C.c_int64)], C.c_int32),
     "l2b_prefill": ([_P, _P, C.c_int32, C.c_int32, C.POINTER(C.c_int32)], C.c_int32),
+    "l2b_session_prefill_gemm": ([_P, C.POINTER(C.c_int32)], C.c_int32),
     "l2b_session_prefill_pairs": ([_P, C.POINTER(C.c_int32)], C.c_int32),
     "l2b_session_tp_handle": ([_P, _P], C.c_int32),
     "l2b_session_tp_connect": ([_P, _P, C.c_int32], C.c_int32),

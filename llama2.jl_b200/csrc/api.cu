@@ -558,6 +558,8 @@ struct l2b_session {
     cudaGraphExec_t graph2 = nullptr;  // two prompt positions per pass (null when the model does not qualify)
     bool all_kquant = true;            // set while the one-position graph is built
     int kernels_per_token = 0;
+    int kernels_per_pair = 0;      // launches of the two-position prompt graph
+    long long last_launches = 0;   // kernel launches of the most recent forward / decode / prefill / generate call
     cudaEvent_t ev0 = nullptr, ev1 = nullptr, ev_mid = nullptr;
     float last_ms = 0.f;
     float last_prompt_ms = 0.f, last_decode_ms = 0.f;  // l2b_generate: positions inside the prompt / after it
@@ -1451,6 +1453,7 @@ static int32_t capture_token_graph(l2b_session* s) {
         int n2 = 0;
         CU(cudaStreamBeginCapture(s->stream, cudaStreamCaptureModeThreadLocal));
         es = enqueue_token(s, &n2, 2);
+        s->kernels_per_pair = n2;
         ce = cudaStreamEndCapture(s->stream, &g2);
         if (es != L2B_OK || ce != cudaSuccess) {
             // e.g. two sets of activation planes of a very long input do not fit in shared memory: prompts then
@@ -1658,6 +1661,7 @@ static int32_t run_one(l2b_session* s, int token, int pos, float temperature, do
     CU(cudaEventRecord(s->ev0, s->stream));
     CU(cudaMemcpyAsync(s->ctl, s->h_ctl, sizeof(Control), cudaMemcpyHostToDevice, s->stream));
     CU(cudaGraphLaunch(s->graph, s->stream));
+    s->last_launches = s->kernels_per_token;
     CU(cudaMemcpyAsync(&s->h_small[0], s->next_token, 4, cudaMemcpyDeviceToHost, s->stream));
     CU(cudaMemcpyAsync(&s->h_small[1], s->status, 4, cudaMemcpyDeviceToHost, s->stream));
     CU(cudaEventRecord(s->ev1, s->stream));
@@ -1768,6 +1772,7 @@ static int32_t enqueue_prefill_gemm(l2b_session* s, int pos0, int n) {
     L2B_TRY(enqueue_layers_gemm(m, s->pf, n, s->kc, s->vc, kv_layer_elems(m), pos0, nullptr, 0, s->rope_cs, s->gq, s->status, st));
     fill_forced_kernel<<<1, 256, 0, st>>>(s->prompt, s->out_tokens, pos0, n);
     CU(cudaGetLastError());
+    s->last_launches += 2 + 14LL * c.n_layers;  // per layer: 4 quantise, 7 GEMM, RoPE + cache write, attention, SwiGLU
     return L2B_OK;
 }
 
@@ -1790,6 +1795,7 @@ static int32_t enqueue_forced_positions(l2b_session* s, int from, int to, const 
     while (i < to) {
         const bool pair = s->graph2 && i + 2 <= to;
         CU(cudaGraphLaunch(pair ? s->graph2 : s->graph, s->stream));
+        s->last_launches += pair ? s->kernels_per_pair : s->kernels_per_token;
         i += pair ? 2 : 1;
     }
     return L2B_OK;
@@ -1873,8 +1879,10 @@ extern "C" int32_t l2b_prefill(l2b_session* s, const int32_t* tokens, int32_t n,
     CU(cudaMemcpyAsync(s->prompt + pos0, tokens, (size_t)n * 4, cudaMemcpyHostToDevice, s->stream));
     CU(cudaMemcpyAsync(s->ctl, s->h_ctl, sizeof(Control), cudaMemcpyHostToDevice, s->stream));
     const int end = pos0 + n;
+    s->last_launches = 0;
     L2B_TRY(enqueue_forced_positions(s, pos0, end - 1, tokens));  // every position but the last is followed by a prompt token
     CU(cudaGraphLaunch(s->graph, s->stream));                     // the last one: its logits are wanted
+    s->last_launches += s->kernels_per_token;
     CU(cudaMemcpyAsync(&s->h_small[0], s->next_token, 4, cudaMemcpyDeviceToHost, s->stream));
     CU(cudaMemcpyAsync(&s->h_small[1], s->status, 4, cudaMemcpyDeviceToHost, s->stream));
     CU(cudaEventRecord(s->ev1, s->stream));
@@ -1882,6 +1890,13 @@ extern "C" int32_t l2b_prefill(l2b_session* s, const int32_t* tokens, int32_t n,
     CU(cudaEventElapsedTime(&s->last_ms, s->ev0, s->ev1));
     if (next) *next = s->h_small[0];
     return check_status_word(s);
+}
+
+extern "C" int32_t l2b_session_prefill_gemm(l2b_session* s, int32_t* min_tokens) {
+    if (!s || !min_tokens) return fail(L2B_ERR_BAD_ARG, "null argument");
+    CU(cudaSetDevice(s->model->device));
+    *min_tokens = prefill_gemm_eligible(s) ? PF_MIN_TOK : 0;
+    return L2B_OK;
 }
 
 extern "C" int32_t l2b_session_prefill_pairs(l2b_session* s, int32_t* enabled) {
@@ -1916,7 +1931,9 @@ extern "C" int32_t l2b_generate(l2b_session* s, const int32_t* prompt, int32_t n
     // tokens are forced, so neither needs logits); everything else takes the one-position graph.
     bool mid = false;
     const int forced_end = std::min(n_prompt - 1, n_positions);  // positions below this are followed by a prompt token
+    s->last_launches = 0;
     L2B_TRY(enqueue_forced_positions(s, 0, forced_end, prompt));
+    s->last_launches += (long long)(n_positions - forced_end) * s->kernels_per_token;
     for (int i = forced_end; i < n_positions; ++i) {
         if (i >= n_prompt && !mid) {  // the first position that is fed a generated token
             CU(cudaEventRecord(s->ev_mid, s->stream));
@@ -1972,6 +1989,11 @@ extern "C" int32_t l2b_session_last_phase_ms(l2b_session* s, float* prompt_ms, f
     if (!s || !prompt_ms || !decode_ms) return fail(L2B_ERR_BAD_ARG, "null argument");
     *prompt_ms = s->last_prompt_ms;
     *decode_ms = s->last_decode_ms;
+    return L2B_OK;
+}
+extern "C" int32_t l2b_session_last_launches(l2b_session* s, int64_t* n) {
+    if (!s || !n) return fail(L2B_ERR_BAD_ARG, "null argument");
+    *n = s->last_launches;
     return L2B_OK;
 }
 extern "C" int32_t l2b_session_kernels_per_token(l2b_session* s, int32_t* n) {

@@ -207,6 +207,18 @@ class LanguageModel:
         L.check(L.lib().l2b_session_prefill_pairs(self.device_model().session, C.byref(n)))
         return bool(n.value)
 
+    def prefill_gemm_min_tokens(self) -> int:
+        """Smallest run of forced prompt positions that goes through the tensor-core GEMM pass (0: not available for this model)."""
+        n = C.c_int32()
+        L.check(L.lib().l2b_session_prefill_gemm(self.device_model().session, C.byref(n)))
+        return n.value
+
+    def last_launches(self) -> int:
+        """Kernel launches the most recent forward / decode / prefill / generate call enqueued."""
+        n = C.c_int64()
+        L.check(L.lib().l2b_session_last_launches(self.device_model().session, C.byref(n)))
+        return n.value
+
     def last_phase_ms(self):
         """(prompt ms, decode ms) of the most recent `generate`: positions fed prompt tokens / positions fed generated tokens."""
         a, b = C.c_float(), C.c_float()

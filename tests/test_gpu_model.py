@@ -289,7 +289,7 @@ def test_token_kernel_matches_chain_and_oracle(pkg, orc, synth, shape):
         cfg = pkg.ModelConfig(1024, 4608, 3, 8, 2, 1024, 96, 500000.0, False)   # hidden > dim: the down projection is cut in two
         types = dict(synth.ALL(12), wv=13, w2=13, output=14)
     elif shape == "phi3_neox_q6_down":
-        cfg = pkg.ModelConfig(768, 4352, 2, 8, 8, 512, 64, 10000.0, True)
+        cfg = pkg.ModelConfig(768, 2048, 2, 8, 8, 512, 64, 10000.0, True)
         types = dict(synth.ALL(13), wv=14, w2=14, output=14)
     else:  # most blocks have no tile at all in most operations
         cfg = pkg.ModelConfig(256, 512, 2, 4, 2, 64, 64, 500000.0, False)
