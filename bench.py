@@ -124,24 +124,28 @@ def kv_bytes(cfg, schedule, tp=1):
     return per_pos * sum(p + k for p, k in schedule)              # a pass reads the cache once, up to its last position
 
 
-def time_matvec(ggml_type, n_in, n_out, copies, launches, steps, warmup, planes):
+def time_matvec(ggml_type, n_in, n_out, copies, launches, steps, warmup, planes, cols=1):
     """Average device time of one fused_matvec_kernel launch (CUDA events on the launching stream), weights rotated
-    through `copies` copies of the matrix so that every launch streams from HBM."""
+    through `copies` copies of the matrix so that every launch streams from HBM.  cols > 1: one call of the tensor-core GEMM
+    (quantise + kq_gemm_kernel) over that many activation columns instead."""
     import torch
     import __graft_entry__ as g
     g.load_package()
     from llama2_jl_b200 import _lib as L
     from llama2_jl_b200 import synth
     A = synth.matrix(ggml_type, n_in, n_out, seed=77)
-    x = torch.from_numpy(synth.normal_f32(n_in, 78, 1.0)).cuda()
-    y = torch.zeros(n_out, dtype=torch.float32, device="cuda")
+    x = torch.from_numpy(synth.normal_f32(cols * n_in, 78, 1.0)).cuda()
+    y = torch.zeros(cols * n_out, dtype=torch.float32, device="cuda")
     h = C.c_void_p()
     L.check(L.lib().l2b_matrix_create(ggml_type, L.ptr(A.data), n_in, n_out, copies, C.byref(h)))
     stream = torch.cuda.current_stream().cuda_stream
 
     def run(n):
         for i in range(n):
-            L.check(L.lib().l2b_matrix_matvec_device(h, i % copies, x.data_ptr(), y.data_ptr(), planes, stream))
+            if cols > 1:
+                L.check(L.lib().l2b_matrix_matmul_device(h, i % copies, x.data_ptr(), cols, y.data_ptr(), stream))
+            else:
+                L.check(L.lib().l2b_matrix_matvec_device(h, i % copies, x.data_ptr(), y.data_ptr(), planes, stream))
     run(warmup * copies)
     torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -166,13 +170,16 @@ def run_matvec(args):
     n_in, n_out, copies = args.matvec_in, args.matvec_out, args.matvec_copies
     planes = args.act_planes or 3
     launches = args.matvec_launches
-    ms, us, nbytes = time_matvec(t, n_in, n_out, copies, launches, args.steps, args.warmup, planes)
+    cols = args.matvec_cols
+    ms, us, nbytes = time_matvec(t, n_in, n_out, copies, launches, args.steps, args.warmup, planes, cols)
     peak, kind = measured_peak()
-    traffic = profiled_traffic("fused_matvec_kernel__q4_K_14336x4096.md") if (t, n_in, n_out) == (12, 4096, 14336) else None
-    line = {"metric": "k-quant dequant-matvec, batch 1", "value": round(us, 3), "unit": "us per matvec", "n_gpus": 1, "steps": args.steps,
+    traffic = profiled_traffic("fused_matvec_kernel__q4_K_14336x4096.md") if (t, n_in, n_out, cols) == (12, 4096, 14336, 1) else None
+    line = {"metric": "k-quant dequant-matvec, batch %d" % cols, "value": round(us, 3), "unit": "us per matvec" if cols == 1 else "us per %d-column product" % cols,
+            "n_gpus": 1, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": round(ms / args.steps, 4), "higher_is_better": False, "vs_baseline": None,
             "dtype": f"int8 activation planes x k-quant integers on int8 tensor-core MMAs, f32 accumulate; {planes} int8 activation plane(s)",
-            "data": "synthetic", "config": {"workload": f"{args.workload} W {n_out}x{n_in}, {copies} rotating copies, {launches} launches per step"},
+            "data": "synthetic", "config": {"workload": f"{args.workload} W {n_out}x{n_in}, {cols} column(s), {copies} rotating copies, {launches} launches per step"},
+            "columns_per_s": round(cols / us * 1e6, 1), "tflops": round(2.0 * n_in * n_out * cols / us / 1e6, 2),
             "gpu_launches": args.steps * launches,
             "roofline": {"bound": "hbm", "achieved": round(nbytes / us / 1e3, 1), "peak": peak, "unit": "GB/s",
                          "frac": round(nbytes / us / 1e3 / peak, 4), "traffic": traffic, "peak_kind": kind, "bytes_per_launch": nbytes}}
@@ -314,6 +321,9 @@ def run_ours(args):
     weights = synth.model_weights(cfg, spec["types"], seed=2024, tied_output=spec["tied"])
     model = pkg.LanguageModel(cfg, None, weights, act_planes=args.act_planes, device=local)
     prompt = synth.prompt_tokens(spec, 2024)[:n_pos]
+    if args.prompt_len > 0:
+        prompt = prompt[:args.prompt_len]
+        wl_name += f" [prompt shortened to {len(prompt)} ids]"
     n_prompt = len(prompt)
     n_decode = n_pos - n_prompt
     wbytes = model.weight_bytes_per_token()
@@ -511,6 +521,8 @@ def main():
     ap.add_argument("--matvec-out", type=int, default=14336)
     ap.add_argument("--matvec-copies", type=int, default=8)
     ap.add_argument("--matvec-launches", type=int, default=64)
+    ap.add_argument("--matvec-cols", type=int, default=1, help="activation columns per product (more than 1: the tensor-core GEMM)")
+    ap.add_argument("--prompt-len", type=int, default=0, help="use only this many prompt ids (0 = the workload's prompt; for profiler captures)")
     ap.add_argument("--act-planes", type=int, default=0, help="int8 planes per activation (1..3; 0 = library default 3)")
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the oracle run (parity and cpu_baseline keys)")
     ap.add_argument("--no-tp", action="store_true", help="with --gpus > 1: skip the tensor-parallel 70B leg")

@@ -271,7 +271,11 @@ int32_t l2b_matrix_create(int32_t ggml_type, const void* host_W, int64_t in_dim,
 int32_t l2b_matrix_destroy(l2b_matrix* m);
 /* y = A' x on device pointers (x: [in] f32, y: [out] f32), copy index `copy`, on `stream` (cudaStream_t; NULL = default). */
 int32_t l2b_matrix_matvec_device(l2b_matrix* m, int32_t copy, const float* dev_x, float* dev_y, int32_t act_planes, void* stream);
-/* The same through host buffers (x: [ncols][in], y: [ncols][out]). */
+/* ncols columns at once on device pointers (x: [ncols][in], y: [ncols][out]) through the tensor-core GEMM (q4_K / q5_K): the
+ * weights are streamed once per 20 columns.  The first call (and any call with more columns than before) allocates the buffer
+ * of quantised columns. */
+int32_t l2b_matrix_matmul_device(l2b_matrix* m, int32_t copy, const float* dev_x, int32_t ncols, float* dev_y, void* stream);
+/* The same through host buffers (x: [ncols][in], y: [ncols][out]); 4 or more columns of a q4_K / q5_K matrix take the GEMM. */
 int32_t l2b_matrix_matvec(l2b_matrix* m, const float* host_x, int32_t ncols, float* host_y, int32_t act_planes);
 
 #ifdef __cplusplus

@@ -88,6 +88,7 @@ _SIGNATURES = {
     "l2b_matrix_create": ([C.c_int32, _P, C.c_int64, C.c_int64, C.c_int32, C.POINTER(_P)], C.c_int32),
     "l2b_matrix_destroy": ([_P], C.c_int32),
     "l2b_matrix_matvec_device": ([_P, C.c_int32, _P, _P, C.c_int32, _P], C.c_int32),
+    "l2b_matrix_matmul_device": ([_P, C.c_int32, _P, C.c_int32, _P, _P], C.c_int32),
     "l2b_matrix_matvec": ([_P, _P, C.c_int32, _P, C.c_int32], C.c_int32),
 }
 # include/l2b_synth.h: the test-support library of seeded synthetic data (libl2b_synth.so, no CUDA)

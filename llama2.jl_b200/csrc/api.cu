@@ -2414,6 +2414,8 @@ struct l2b_matrix {
     int device = 0;
     DeviceInfo di;
     int* status = nullptr;
+    uint8_t* act = nullptr;  // quantised activation columns of l2b_matrix_matmul_device (grown on demand)
+    size_t act_bytes = 0;
 };
 
 extern "C" int32_t l2b_matrix_create(int32_t type, const void* host_W, int64_t in_dim, int64_t out_dim, int32_t copies, l2b_matrix** out) {
@@ -2443,8 +2445,29 @@ extern "C" int32_t l2b_matrix_destroy(l2b_matrix* m) {
     cudaSetDevice(m->device);
     for (auto& c : m->copies) free_matrix(c);
     if (m->status) cudaFree(m->status);
+    if (m->act) cudaFree(m->act);
     delete m;
     return L2B_OK;
+}
+
+// y[c] = A' x[c] for ncols columns on device pointers (x: [ncols][in], y: [ncols][out]) through the tensor-core GEMM:
+// the columns are quantised once, then every weight tile is unpacked once per 20 columns.
+extern "C" int32_t l2b_matrix_matmul_device(l2b_matrix* m, int32_t copy, const float* dev_x, int32_t ncols, float* dev_y, void* stream) {
+    if (!m || !dev_x || !dev_y || ncols < 1) return fail(L2B_ERR_BAD_ARG, "bad argument");
+    if (copy < 0 || copy >= (int)m->copies.size()) return fail(L2B_ERR_BAD_ARG, "copy index out of range");
+    const DevMatrix& w = m->copies[copy];
+    if (!gemm_supported(w)) return fail(L2B_ERR_UNSUPPORTED_TYPE, "the tensor-core GEMM takes q4_K and q5_K matrices");
+    CU(cudaSetDevice(m->device));
+    const size_t need = gemm_act_bytes(w.in, ncols);
+    if (need > m->act_bytes) {
+        if (m->act) cudaFree(m->act);
+        m->act = nullptr;
+        m->act_bytes = 0;
+        CU(cudaMalloc(&m->act, need));
+        m->act_bytes = need;
+    }
+    L2B_TRY(launch_quantise_rows(dev_x, nullptr, m->act, (int)w.in, (int)w.in, ncols, (cudaStream_t)stream));
+    return launch_kq_gemm(w, m->act, ncols, dev_y, (int)w.out, nullptr, m->status, (cudaStream_t)stream);
 }
 
 extern "C" int32_t l2b_matrix_matvec_device(l2b_matrix* m, int32_t copy, const float* dev_x, float* dev_y, int32_t planes, void* stream) {

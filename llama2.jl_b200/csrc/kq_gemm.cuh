@@ -74,8 +74,9 @@ __host__ __device__ inline GmSmem gm_smem_layout(int block_bytes) {
     s.off_tmem = o;
     o += 16;
     o = (o + 127) & ~127;
-    s.off_hdr = o;  // [2][128] GmRowHdr
-    o += 2 * GM_ROWS * (int)sizeof(GmRowHdr);
+    s.off_hdr = o;  // [GM_STAGES][128] GmRowHdr: one set per ring stage, because a stage is refilled only after the epilogue
+                    // of the step that used it has finished (a set per unpack buffer would be rewritten while still being read)
+    o += GM_STAGES * GM_ROWS * (int)sizeof(GmRowHdr);
     o = (o + 1023) & ~1023;
     s.off_au = o;   // [2] unpacked weights
     o += 2 * GM_A_BYTES;
@@ -312,7 +313,7 @@ __global__ void __launch_bounds__(GM_THREADS, 1) kq_gemm_kernel(const __grid_con
                 hd.dmin = half_bits_to_float(h.x >> 16);
                 *reinterpret_cast<uint64_t*>(hd.sc) = sc8;
                 *reinterpret_cast<uint64_t*>(hd.m) = m8;
-                hdr[buf * GM_ROWS + r] = hd;
+                hdr[s * GM_ROWS + r] = hd;
                 uint8_t* dst = au + (size_t)buf * GM_A_BYTES + (r >> 3) * 128 + (r & 7) * 16;
                 const uint8_t* qs = blk + (p.type == T_Q5_K ? 48 : 16);
                 uint4 qh0 = make_uint4(0u, 0u, 0u, 0u), qh1 = qh0;
@@ -359,7 +360,7 @@ __global__ void __launch_bounds__(GM_THREADS, 1) kq_gemm_kernel(const __grid_con
             if (ok && !mbar_wait_bounded(mma_done + buf, (uint32_t)((b >> 1) & 1))) ok = false;
             if (ok) {
                 tc_fence_after();
-                const GmRowHdr hd = hdr[buf * GM_ROWS + r];
+                const GmRowHdr hd = hdr[s * GM_ROWS + r];
                 int S[3 * GM_HALF_TOK];
 #pragma unroll
                 for (int n = 0; n < 3 * GM_HALF_TOK; ++n) S[n] = 0;

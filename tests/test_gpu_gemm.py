@@ -41,6 +41,18 @@ def test_gemm_is_deterministic_and_matches_the_vector_kernel(pkg, synth):
     assert np.abs(y - Y1[3]).max() <= 2e-6 * np.abs(y).max()
 
 
+def test_gemm_many_blocks_at_once_repeated(pkg, orc, synth):
+    """112 row tiles resident at the same time, several times over: unpack, MMA and epilogue warps of a block run out of step
+    with one another differently on every run, so anything one of them rewrites too early shows up here."""
+    A = synth.matrix(12, 4096, 14336, seed=1234)
+    for ncols in (4, 20, 4, 7, 4):
+        X = synth.normal_f32(ncols * 4096, 78 + ncols, 1.0).reshape(ncols, 4096)
+        Y = np.zeros((ncols, 14336), dtype=np.float32)
+        pkg.matmul_(Y, A, X)
+        for c in (0, ncols - 1):
+            assert rel_err(Y[c], orc.matmul_f64(A, X[c])) < 4e-6, (ncols, c)
+
+
 def test_q6_k_columns_fall_back_to_the_vector_kernel(pkg, orc, synth):
     A = synth.matrix(14, 1024, 64, seed=9)
     X = synth.normal_f32(6 * 1024, 8, 1.0).reshape(6, 1024)

@@ -124,7 +124,8 @@ def test_matvec_full_size_and_batch(pkg, orc, synth):
     Y = np.zeros((4, 14336), dtype=np.float32)
     pkg.matmul_(Y, A, X)
     for c in range(4):
-        assert rel_err(Y[c], orc.matmul_f64(A, X[c])) < 4e-6
+        e = rel_err(Y[c], orc.matmul_f64(A, X[c]))
+        assert e < 4e-6, (c, e)
     # linearity, a size-independent property: A'(2x) == 2 A'x exactly (power-of-two scaling commutes with rounding)
     y1 = np.zeros(14336, dtype=np.float32)
     y2 = np.zeros(14336, dtype=np.float32)
