@@ -388,10 +388,10 @@ static cudaError_t launch_attention(const AttnParams& a, int gq, cudaStream_t st
             default: return launch_kernel(attention_split_kernel<1, 2>, grid, block, 0, st, pdl, a);
         }
     switch (gq) {
-        case 8: return launch_kernel(attention_split_kernel<8>, grid, block, 0, st, pdl, a);
-        case 4: return launch_kernel(attention_split_kernel<4>, grid, block, 0, st, pdl, a);
-        case 2: return launch_kernel(attention_split_kernel<2>, grid, block, 0, st, pdl, a);
-        default: return launch_kernel(attention_split_kernel<1>, grid, block, 0, st, pdl, a);
+        case 8: return launch_kernel(attention_decode_kernel<8>, grid, block, 0, st, pdl, a);
+        case 4: return launch_kernel(attention_decode_kernel<4>, grid, block, 0, st, pdl, a);
+        case 2: return launch_kernel(attention_decode_kernel<2>, grid, block, 0, st, pdl, a);
+        default: return launch_kernel(attention_decode_kernel<1>, grid, block, 0, st, pdl, a);
     }
 }
 static int choose_gq(int n_heads, int n_kv) {
@@ -564,6 +564,7 @@ struct l2b_session {
     float last_ms = 0.f;
     float last_prompt_ms = 0.f, last_decode_ms = 0.f;  // l2b_generate: positions inside the prompt / after it
     unsigned long long* trace = nullptr;  // L2B_TRACE_TOKEN=1: per-launch, per-block timeline stamps (debugging aid)
+    unsigned long long* attn_trace = nullptr;  // the same for the decode attention kernel: [layer][1024 blocks][8]
     int trace_launches = 0;
     // tensor parallelism.  tp_mem = [n_exch][tp][dim] f32 partial vectors, then [n_exch][tp] u32 arrival counters;
     // n_exch = 2 * n_layers (one exchange after wo, one after w2).  Peers write into it through IPC mappings.
@@ -923,6 +924,7 @@ static void session_free(l2b_session* s) {
     for (void* b : bufs)
         if (b) cudaFree(b);
     if (s->trace) cudaFree(s->trace);
+    if (s->attn_trace) cudaFree(s->attn_trace);
     if (s->model)
         for (int r = 0; r < s->model->tp; ++r)
             if (s->peer_mem[r] && r != s->model->rank) cudaIpcCloseMemHandle(s->peer_mem[r]);
@@ -1079,6 +1081,9 @@ static int32_t enqueue_token(l2b_session* s, int* nlaunch, int nb = 1) {
             a.n_heads = m->l_heads; a.n_kv = m->l_kv; a.hs = hs; a.seq_len = c.seq_len; a.nsplit = s->nsplit;
             a.nq = nb; a.q_stride = m->l_qdim();
             a.min_chunk = (int)env_long("L2B_ATTN_MIN_CHUNK", 0);
+#ifdef L2B_MEASURE
+            if (s->attn_trace) a.trace = s->attn_trace + (size_t)l * 1024 * 8;
+#endif
             CU(launch_attention(a, s->gq, s->stream, true));
             ++count;
         }
@@ -1544,6 +1549,8 @@ extern "C" int32_t l2b_session_create(l2b_model* m, void* stream, l2b_session** 
             const size_t n = (size_t)(4 * c.n_layers + 1) * s->di.sms * 16;
             CU(cudaMalloc(&s->trace, n * 8));
             CU(cudaMemset(s->trace, 0, n * 8));
+            CU(cudaMalloc(&s->attn_trace, (size_t)c.n_layers * 1024 * 8 * 8));
+            CU(cudaMemset(s->attn_trace, 0, (size_t)c.n_layers * 1024 * 8 * 8));
         }
 #endif
         if (m->tp > 1) {
@@ -1809,20 +1816,46 @@ static void dump_token_trace(l2b_session* s) {
     unsigned long long t0 = ~0ull;
     for (int b = 0; b < sms; ++b)
         if (h[b * 16]) t0 = std::min(t0, h[b * 16]);
-    fprintf(stderr, "[l2b token trace] per fused launch, us since the first: first-block-start / avg first-copy-issued / avg waited(prev kernel done) / avg activations-built / last-block-end\n");
+    fprintf(stderr, "[l2b token trace] per fused launch, us after the previous fused launch's last block ended: block start min/avg/max | first copy issued avg/max | "
+                    "wait over min/avg/max | planes built avg/max | consumers done min/avg/max | finisher done avg/max | blocks\n");
+    double prev_end = 0;
     for (int k = 0; k < nl; ++k) {
-        double st = 1e30, en = 0, iss = 0, wt = 0, act = 0;
+        double mn[8], mx[8], av[8];
+        for (int i = 0; i < 8; ++i) mn[i] = 1e30, mx[i] = -1e30, av[i] = 0;
         int nb = 0;
         for (int b = 0; b < sms; ++b) {
             const unsigned long long* r = &h[((size_t)k * sms + b) * 16];
             if (!r[0]) continue;
             ++nb;
-            st = std::min(st, (double)(r[0] - t0));
-            en = std::max(en, (double)(r[6] - t0));
-            iss += (double)(r[1] - t0); wt += (double)(r[2] - t0); act += (double)(r[3] - t0);
+            for (int i : {0, 1, 2, 3, 6, 7}) {
+                const int src = i == 7 ? 8 : i;  // slot 7 of the statistics: the finisher warp's end (stamp 8)
+                const double v = r[src] ? (double)(r[src] - t0) / 1e3 : 0.0;
+                mn[i] = std::min(mn[i], v); mx[i] = std::max(mx[i], v); av[i] += v;
+            }
         }
         if (!nb) continue;
-        if (k < 12 || k >= nl - 3) fprintf(stderr, "  launch %3d: %8.2f %8.2f %8.2f %8.2f %8.2f\n", k, st / 1e3, iss / nb / 1e3, wt / nb / 1e3, act / nb / 1e3, en / 1e3);
+        auto rel = [&](double v) { return v - prev_end; };
+        if (k < 16 || k >= nl - 3)
+            fprintf(stderr, "  launch %3d: start %6.2f %6.2f %6.2f | copy %6.2f %6.2f | wait %6.2f %6.2f %6.2f | planes %6.2f %6.2f | end %6.2f %6.2f %6.2f | fin %6.2f %6.2f | %d  (abs %.2f)\n", k,
+                    rel(mn[0]), rel(av[0] / nb), rel(mx[0]), rel(av[1] / nb), rel(mx[1]), rel(mn[2]), rel(av[2] / nb), rel(mx[2]), rel(av[3] / nb), rel(mx[3]),
+                    rel(mn[6]), rel(av[6] / nb), rel(mx[6]), rel(av[7] / nb), rel(mx[7]), nb, mx[7]);
+        prev_end = std::max(mx[6], mx[7]);
+        if (s->attn_trace && k % 4 == 0 && k / 4 < s->model->cfg.n_layers && k < 16) {  // the attention launch that follows this layer's qkv launch
+            std::vector<unsigned long long> a((size_t)1024 * 8);
+            if (cudaMemcpy(a.data(), s->attn_trace + (size_t)(k / 4) * 1024 * 8, a.size() * 8, cudaMemcpyDeviceToHost) != cudaSuccess) continue;
+            double amn[4], amx[4], aav[4];
+            int cnt[4] = {0, 0, 0, 0};
+            for (int i = 0; i < 4; ++i) amn[i] = 1e30, amx[i] = -1e30, aav[i] = 0;
+            for (int b = 0; b < 1024; ++b)
+                for (int i = 0; i < 4; ++i) {
+                    if (!a[(size_t)b * 8 + i]) continue;
+                    const double v = (double)(a[(size_t)b * 8 + i] - t0) / 1e3 - prev_end;
+                    amn[i] = std::min(amn[i], v); amx[i] = std::max(amx[i], v); aav[i] += v; ++cnt[i];
+                }
+            fprintf(stderr, "     attention: blocks %d | start %6.2f %6.2f %6.2f | wait over %6.2f %6.2f %6.2f | positions done %6.2f %6.2f %6.2f | merged %6.2f %6.2f %6.2f\n", cnt[0],
+                    amn[0], aav[0] / std::max(cnt[0], 1), amx[0], amn[1], aav[1] / std::max(cnt[1], 1), amx[1], amn[2], aav[2] / std::max(cnt[2], 1), amx[2],
+                    amn[3], aav[3] / std::max(cnt[3], 1), amx[3]);
+        }
     }
 }
 #endif
@@ -2588,7 +2621,7 @@ float* g_na_scratch_addr[NA_MAX_DEVICES] = {nullptr};
 
 template <int GQ>
 __global__ void __launch_bounds__(ATTN_WARPS * 32) attention_static_scratch_kernel(const __grid_constant__ AttnParams p) {
-    attention_split_body<GQ>(p);
+    attention_decode_body<GQ, false>(p);  // the arithmetic of l2b_attention, in the same order
 }
 
 }  // namespace

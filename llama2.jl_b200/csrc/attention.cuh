@@ -1,4 +1,5 @@
-// Split-KV ("flash-decoding") attention for one query position with grouped query heads.
+// Split-KV ("flash-decoding") attention with grouped query heads: one query position per launch on the decode path
+// (attention_decode_kernel), several in the prompt passes and batched decode (attention_split_kernel).
 // Replaces attention_weights! + the 1/sqrt(head_size) division + softmax! + combine_values!
 // (src/inference.jl:263-278, 169-220).
 //
@@ -36,11 +37,132 @@ struct AttnParams {
     int pos_base;       // position of the first query when `pos` is null (launches outside the captured token graph)
     const int* pos_list;     // batched decode: query qi belongs to its own sequence, at position pos_list[qi] ...
     size_t cache_stride_q;   // ... whose caches start cache_stride_q * qi elements after kc / vc
+    unsigned long long* trace;  // measurement build only: 8 time stamps per block of the decode kernel, or null
 };
+
+#ifdef L2B_MEASURE
+#define ATTN_TRACE(i)                                                                                                   \
+    do {                                                                                                                \
+        if (p.trace && threadIdx.x == 0) asm volatile("{.reg .u64 t; mov.u64 t, %%globaltimer; st.global.u64 [%0], t;}" \
+                                                      ::"l"(p.trace + (size_t)blockIdx.x * 8 + (i)) : "memory");          \
+    } while (0)
+#else
+#define ATTN_TRACE(i) do {} while (0)
+#endif
 
 constexpr int ATTN_WARPS = 4;
 constexpr int ATTN_UNROLL = 4;      // positions whose key/value loads a warp keeps in flight
+constexpr int ATTN_MERGE_BATCH = 16;  // partial results of the splits fetched together by the merging block
 constexpr int ATTN_MIN_CHUNK = 16;  // positions per split below which splitting costs more than it saves
+
+// What follows the walk over the positions: the warps of a block are merged in shared memory; with one active split the
+// block writes the attention output, otherwise (max, sum, unnormalised output) per query head go to scratch memory and the
+// block that finishes last for the head group (an atomic ticket) merges the splits.
+template <int GQ>
+__device__ __forceinline__ void attention_merge(const AttnParams& p, const float (&m)[GQ], const float (&l)[GQ], const float4 (&acc)[GQ], int hg, int sp, int active,
+                                                int hq, float* obase, int* ticket_p, bool lane_active) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int hs = p.hs;
+    const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
+    __shared__ float sm[ATTN_WARPS][GQ], sl[ATTN_WARPS][GQ];
+    __shared__ float4 sacc[ATTN_WARPS][GQ][32];
+    __shared__ int s_last;
+#pragma unroll
+    for (int g = 0; g < GQ; ++g) {
+        if (lane == 0) {
+            sm[warp][g] = m[g];
+            sl[warp][g] = l[g];
+        }
+        sacc[warp][g][lane] = acc[g];
+    }
+    __syncthreads();
+    for (int g = warp; g < GQ; g += ATTN_WARPS) {
+        float M = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < ATTN_WARPS; ++w) M = fmaxf(M, sm[w][g]);
+        float Ls = 0.f;
+        float4 a = zero4;
+#pragma unroll
+        for (int w = 0; w < ATTN_WARPS; ++w) {
+            const float wgt = (sm[w][g] == -INFINITY) ? 0.f : expf(sm[w][g] - M);
+            Ls = fmaf(sl[w][g], wgt, Ls);
+            const float4 b = sacc[w][g][lane];
+            a.x = fmaf(b.x, wgt, a.x);
+            a.y = fmaf(b.y, wgt, a.y);
+            a.z = fmaf(b.z, wgt, a.z);
+            a.w = fmaf(b.w, wgt, a.w);
+        }
+        const int h = hg * GQ + g;
+        if (active == 1) {  // nothing to merge across blocks
+            if (lane_active) {
+                a.x /= Ls; a.y /= Ls; a.z /= Ls; a.w /= Ls;
+                reinterpret_cast<float4*>(obase + (size_t)h * hs)[lane] = a;
+            }
+        } else {
+            if (lane == 0) {
+                p.part_m[(size_t)(hq + h) * p.nsplit + sp] = M;
+                p.part_l[(size_t)(hq + h) * p.nsplit + sp] = Ls;
+            }
+            if (lane_active) reinterpret_cast<float4*>(p.part_acc + ((size_t)(hq + h) * p.nsplit + sp) * hs)[lane] = a;
+        }
+    }
+    if (active == 1) return;
+    // The last block of this head group merges the splits.  One thread per block publishes: the barrier orders the block's
+    // partial results before its fence, and fences are cumulative, so the 127 other fences (about a microsecond of waiting
+    // each, all on the critical path of a token) are not needed.
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence();
+        const int ticket = atomicAdd(ticket_p, 1);
+        s_last = (ticket == active - 1);
+        if (s_last) {
+            *ticket_p = 0;  // ready for the next launch
+            __threadfence();
+        }
+    }
+    __syncthreads();
+    if (!s_last) return;
+    for (int g = warp; g < GQ; g += ATTN_WARPS) {
+        const int h = hg * GQ + g;
+        const float* pm = p.part_m + (size_t)(hq + h) * p.nsplit;
+        const float* pl = p.part_l + (size_t)(hq + h) * p.nsplit;
+        // Up to ATTN_MERGE_BATCH partial results are fetched together, and before the arithmetic on the maxima: a loop of small
+        // batches would pay the L2 latency once per batch, in series, on the critical path of the token.
+        float4 b[ATTN_MERGE_BATCH];
+        auto fetch = [&](int s0) {
+#pragma unroll
+            for (int u = 0; u < ATTN_MERGE_BATCH; ++u) {
+                b[u] = zero4;
+                if (lane_active && s0 + u < active) b[u] = __ldcg(reinterpret_cast<const float4*>(p.part_acc + ((size_t)(hq + h) * p.nsplit + s0 + u) * hs) + lane);
+            }
+        };
+        fetch(0);
+        // lane s holds split s (nsplit <= 32)
+        const float ms = lane < active ? __ldcg(pm + lane) : -INFINITY;
+        const float ls = lane < active ? __ldcg(pl + lane) : 0.f;
+        const float M = warp_max(ms);
+        const float wgt = (ms == -INFINITY) ? 0.f : expf(ms - M);
+        const float Ls = warp_sum(ls * wgt);
+        float4 a = zero4;
+        for (int s0 = 0; s0 < active; s0 += ATTN_MERGE_BATCH) {
+            if (s0) fetch(s0);
+#pragma unroll
+            for (int u = 0; u < ATTN_MERGE_BATCH; ++u) {
+                const float wu = __shfl_sync(0xffffffffu, wgt, (s0 + u) & 31);
+                if (s0 + u < active) {
+                    a.x = fmaf(b[u].x, wu, a.x);
+                    a.y = fmaf(b[u].y, wu, a.y);
+                    a.z = fmaf(b[u].z, wu, a.z);
+                    a.w = fmaf(b[u].w, wu, a.w);
+                }
+            }
+        }
+        if (lane_active) {
+            a.x /= Ls; a.y /= Ls; a.z /= Ls; a.w /= Ls;
+            reinterpret_cast<float4*>(obase + (size_t)h * hs)[lane] = a;
+        }
+    }
+}
 
 // GQ: query heads served per block (divides n_heads / n_kv).  NQ = 1: one query position per launch; any other value: the grid
 // holds p.nq copies of the (head group, split) blocks, copy qi serving the query at position pos + qi (2 in the two-position
@@ -120,95 +242,128 @@ __device__ __forceinline__ void attention_split_body(const AttnParams& p) {
             }
         }
     }
-    // merge the warps of this block
-    __shared__ float sm[ATTN_WARPS][GQ], sl[ATTN_WARPS][GQ];
-    __shared__ float4 sacc[ATTN_WARPS][GQ][32];
-    __shared__ int s_last;
+    attention_merge<GQ>(p, m, l, acc, hg, sp, active, hq, obase, ticket_p, lane_active);
+}
+
+// One query position per launch (the decode path), built for latency.  The keys and values of earlier positions were
+// written by earlier tokens, so the first batch of every warp is fetched BEFORE the wait on the previous kernel (which
+// writes q and this position's key and value): the cache latency hides behind that kernel's tail.  A batch of
+// ATTN_UNROLL positions is scored without branches (all dot products and their lane reductions are independent), then
+// folded into the running softmax with one maximum and one set of exponentials per batch.
+// PDL = false: launched without a programmatic dependency (no previous kernel to wait for).
+template <int GQ, bool PDL>
+__device__ __forceinline__ void attention_decode_body(const AttnParams& p) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    ATTN_TRACE(0);
+    const int hg = (int)blockIdx.x / p.nsplit, sp = (int)blockIdx.x % p.nsplit;
+    const int kvh = (hg * GQ) / (p.n_heads / p.n_kv);
+    const int npos = p.npos_override > 0 ? p.npos_override : ((p.pos ? __ldcg(p.pos) : p.pos_base) + 1);  // the position is set before the token starts
+    const int mc = p.min_chunk > 0 ? p.min_chunk : ATTN_MIN_CHUNK;
+    const int active = min(p.nsplit, (npos + mc - 1) / mc);
+    if (sp >= active) return;
+    const int chunk = (npos + active - 1) / active;
+    const int t0 = sp * chunk, t1 = min(npos, t0 + chunk);
+    const int hs = p.hs;
+    const bool lane_active = 4 * lane < hs;
+    const float div = sqrtf((float)hs);
+    const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
+    const float* kbase = p.kc + (size_t)kvh * p.seq_len * hs;
+    const float* vbase = p.vc + (size_t)kvh * p.seq_len * hs;
+    const int tb0 = t0 + warp * ATTN_UNROLL;
+
+    float4 kk[ATTN_UNROLL], vv[ATTN_UNROLL];
+#pragma unroll
+    for (int u = 0; u < ATTN_UNROLL; ++u) {
+        kk[u] = vv[u] = zero4;
+        const int t = tb0 + u;
+        if (lane_active && t < t1 && t < npos - 1) {
+            kk[u] = __ldcg(reinterpret_cast<const float4*>(kbase + (size_t)t * hs) + lane);
+            vv[u] = __ldcg(reinterpret_cast<const float4*>(vbase + (size_t)t * hs) + lane);
+        }
+    }
+    if (PDL) pdl_wait();
+    ATTN_TRACE(1);
+    float4 qv[GQ], acc[GQ];
+    float m[GQ], l[GQ];
 #pragma unroll
     for (int g = 0; g < GQ; ++g) {
-        if (lane == 0) {
-            sm[warp][g] = m[g];
-            sl[warp][g] = l[g];
-        }
-        sacc[warp][g][lane] = acc[g];
+        qv[g] = lane_active ? __ldcg(reinterpret_cast<const float4*>(p.q + (size_t)(hg * GQ + g) * hs) + lane) : zero4;
+        acc[g] = zero4;
+        m[g] = -INFINITY;
+        l[g] = 0.f;
     }
-    __syncthreads();
-    for (int g = warp; g < GQ; g += ATTN_WARPS) {
-        float M = -INFINITY;
 #pragma unroll
-        for (int w = 0; w < ATTN_WARPS; ++w) M = fmaxf(M, sm[w][g]);
-        float Ls = 0.f;
-        float4 a = zero4;
-#pragma unroll
-        for (int w = 0; w < ATTN_WARPS; ++w) {
-            const float wgt = (sm[w][g] == -INFINITY) ? 0.f : expf(sm[w][g] - M);
-            Ls = fmaf(sl[w][g], wgt, Ls);
-            const float4 b = sacc[w][g][lane];
-            a.x = fmaf(b.x, wgt, a.x);
-            a.y = fmaf(b.y, wgt, a.y);
-            a.z = fmaf(b.z, wgt, a.z);
-            a.w = fmaf(b.w, wgt, a.w);
-        }
-        const int h = hg * GQ + g;
-        if (active == 1) {  // nothing to merge across blocks
-            if (lane_active) {
-                a.x /= Ls; a.y /= Ls; a.z /= Ls; a.w /= Ls;
-                reinterpret_cast<float4*>(obase + (size_t)h * hs)[lane] = a;
-            }
-        } else {
-            if (lane == 0) {
-                p.part_m[(size_t)(hq + h) * p.nsplit + sp] = M;
-                p.part_l[(size_t)(hq + h) * p.nsplit + sp] = Ls;
-            }
-            if (lane_active) reinterpret_cast<float4*>(p.part_acc + ((size_t)(hq + h) * p.nsplit + sp) * hs)[lane] = a;
+    for (int u = 0; u < ATTN_UNROLL; ++u) {  // the position the previous kernel has just written, if it is in this batch
+        const int t = tb0 + u;
+        if (lane_active && t < t1 && t == npos - 1) {
+            kk[u] = __ldcg(reinterpret_cast<const float4*>(kbase + (size_t)t * hs) + lane);
+            vv[u] = __ldcg(reinterpret_cast<const float4*>(vbase + (size_t)t * hs) + lane);
         }
     }
-    if (active == 1) return;
-    // the last block of this head group merges the splits
-    __threadfence();
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        const int ticket = atomicAdd(ticket_p, 1);
-        s_last = (ticket == active - 1);
-        if (s_last) *ticket_p = 0;  // ready for the next launch
-    }
-    __syncthreads();
-    if (!s_last) return;
-    __threadfence();
-    for (int g = warp; g < GQ; g += ATTN_WARPS) {
-        const int h = hg * GQ + g;
-        const float* pm = p.part_m + (size_t)(hq + h) * p.nsplit;
-        const float* pl = p.part_l + (size_t)(hq + h) * p.nsplit;
-        // lane s holds split s (nsplit <= 32)
-        const float ms = lane < active ? __ldcg(pm + lane) : -INFINITY;
-        const float ls = lane < active ? __ldcg(pl + lane) : 0.f;
-        const float M = warp_max(ms);
-        const float wgt = (ms == -INFINITY) ? 0.f : expf(ms - M);
-        const float Ls = warp_sum(ls * wgt);
-        float4 a = zero4;
-        for (int s0 = 0; s0 < active; s0 += 4) {
-            float4 b[4];
+    for (int tb = tb0; tb < t1; tb += ATTN_WARPS * ATTN_UNROLL) {
+        if (tb != tb0) {
 #pragma unroll
-            for (int u = 0; u < 4; ++u) {
-                b[u] = zero4;
-                if (lane_active && s0 + u < active) b[u] = __ldcg(reinterpret_cast<const float4*>(p.part_acc + ((size_t)(hq + h) * p.nsplit + s0 + u) * hs) + lane);
-            }
-#pragma unroll
-            for (int u = 0; u < 4; ++u) {
-                const float wu = __shfl_sync(0xffffffffu, wgt, (s0 + u) & 31);
-                if (s0 + u < active) {
-                    a.x = fmaf(b[u].x, wu, a.x);
-                    a.y = fmaf(b[u].y, wu, a.y);
-                    a.z = fmaf(b[u].z, wu, a.z);
-                    a.w = fmaf(b[u].w, wu, a.w);
+            for (int u = 0; u < ATTN_UNROLL; ++u) {
+                kk[u] = vv[u] = zero4;
+                if (lane_active && tb + u < t1) {
+                    kk[u] = __ldcg(reinterpret_cast<const float4*>(kbase + (size_t)(tb + u) * hs) + lane);
+                    vv[u] = __ldcg(reinterpret_cast<const float4*>(vbase + (size_t)(tb + u) * hs) + lane);
                 }
             }
         }
-        if (lane_active) {
-            a.x /= Ls; a.y /= Ls; a.z /= Ls; a.w /= Ls;
-            reinterpret_cast<float4*>(obase + (size_t)h * hs)[lane] = a;
+        float s[ATTN_UNROLL][GQ];
+#pragma unroll
+        for (int u = 0; u < ATTN_UNROLL; ++u)
+#pragma unroll
+            for (int g = 0; g < GQ; ++g) {
+                float d = qv[g].x * kk[u].x;
+                d = fmaf(qv[g].y, kk[u].y, d);
+                d = fmaf(qv[g].z, kk[u].z, d);
+                s[u][g] = fmaf(qv[g].w, kk[u].w, d);
+            }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+            for (int u = 0; u < ATTN_UNROLL; ++u)
+#pragma unroll
+                for (int g = 0; g < GQ; ++g) s[u][g] += __shfl_xor_sync(0xffffffffu, s[u][g], o);
+#pragma unroll
+        for (int g = 0; g < GQ; ++g) {
+            float mx = m[g];
+#pragma unroll
+            for (int u = 0; u < ATTN_UNROLL; ++u) {
+                s[u][g] = (tb + u < t1) ? s[u][g] / div : -INFINITY;  // att ./= sqrt(Float32(head_size)); positions beyond the range weigh nothing
+                mx = fmaxf(mx, s[u][g]);
+            }
+            const float corr = expf(m[g] - mx);  // 0 for the first batch (m = -inf; the batch's first position is always in range)
+            float ps = 0.f;
+            float4 pv = zero4;
+#pragma unroll
+            for (int u = 0; u < ATTN_UNROLL; ++u) {
+                const float pr = expf(s[u][g] - mx);
+                ps += pr;
+                pv.x = fmaf(pr, vv[u].x, pv.x);
+                pv.y = fmaf(pr, vv[u].y, pv.y);
+                pv.z = fmaf(pr, vv[u].z, pv.z);
+                pv.w = fmaf(pr, vv[u].w, pv.w);
+            }
+            l[g] = fmaf(l[g], corr, ps);
+            acc[g].x = fmaf(acc[g].x, corr, pv.x);
+            acc[g].y = fmaf(acc[g].y, corr, pv.y);
+            acc[g].z = fmaf(acc[g].z, corr, pv.z);
+            acc[g].w = fmaf(acc[g].w, corr, pv.w);
+            m[g] = mx;
         }
     }
+    ATTN_TRACE(2);
+    attention_merge<GQ>(p, m, l, acc, hg, sp, active, 0, p.out, p.tickets + hg, lane_active);
+    ATTN_TRACE(3);
+}
+
+template <int GQ>
+__global__ void __launch_bounds__(ATTN_WARPS * 32) attention_decode_kernel(const __grid_constant__ AttnParams p) {
+    pdl_launch_dependents();
+    attention_decode_body<GQ, true>(p);
 }
 
 template <int GQ, int NQ = 1>

@@ -958,6 +958,7 @@ __global__ void __launch_bounds__((MV_MAX_CONSUMERS + 2) * 32, 1) fused_matvec_k
                 p.amax_idx[blockIdx.x] = best.i;
             }
         }
+        if (DBG && p.trace && lane == 0) p.trace[blockIdx.x * 16 + 8] = global_ns();
         return;
     }
 
@@ -989,17 +990,8 @@ __global__ void __launch_bounds__((MV_MAX_CONSUMERS + 2) * 32, 1) fused_matvec_k
         cx.act = smem + L.off_act;
         cx.dpl = reinterpret_cast<const float*>(smem + L.off_dpl);
         cx.xs16 = reinterpret_cast<const float*>(smem + L.off_xs);
-        cx.plane_stride = L.plane_stride;
-        cx.g = lane >> 2;
-        cx.t = lane & 3;
-        cx.colv = cx.g < P;
-        if (NB == 2) {
-            // MMA column g carries plane g & 3 of vector g >> 2; lanes t = 0, 1 collect vector 0, lanes t = 2, 3 vector 1
-            const int pl = (cx.g >> 2) * P + (cx.g & 3);
-            cx.colv = (cx.g & 3) < P;
-            cx.act = smem + L.off_act + (pl - cx.g) * L.plane_stride;  // the tile functions add g * plane_stride
-            cx.xs16 = reinterpret_cast<const float*>(smem + L.off_xs) + (cx.t >> 1) * (p.n_in / QK_K) * 16;
-        }
+        tile_ctx_columns<NB, P>(cx, smem + L.off_act, L.plane_stride, lane);
+        if (NB == 2) cx.xs16 = reinterpret_cast<const float*>(smem + L.off_xs) + (cx.t >> 1) * (p.n_in / QK_K) * 16;  // this lane's vector
         const int pj = ((cx.g & 3) << 1) | (cx.g >> 2);  // the pair of the tile this lane group works on: (0,2,4,6,1,3,5,7)[g]
         float* red = reinterpret_cast<float*>(smem + L.off_red);
         bool dead = false;

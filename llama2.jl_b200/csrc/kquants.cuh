@@ -101,13 +101,53 @@ __device__ __forceinline__ void decode_scales_k4(const uint4& hd, uint64_t& sc8,
 __device__ __forceinline__ int byte64(uint64_t w, int i) { return (int)((w >> (8 * i)) & 0xFFull); }
 
 struct TileCtx {
-    const uint8_t* act;  // plane 0 of the activations
-    const float* dpl;    // [nb][8] column scales
+    const uint8_t* act;  // the activation plane carried by this lane's MMA column g (meaningful when colv)
+    const float* dpl;    // [nb][8] plane scales
     const float* xs16;   // [nb][16]
-    int plane_stride;
     int g, t;            // lane = 4*g + t
     bool colv;           // this lane's column g carries an activation plane
 };
+
+// Which plane rides in which MMA column.  One vector per launch (NB = 1): plane k in column 2k, so that every lane t holds
+// exactly one useful result column (2t: c[0] for row g, c[2] for row g+8) and applies the sub-block scale to two integers
+// instead of four; the odd columns are zero.  Two vectors (NB = 2): planes of vector v in columns 4v .. 4v+2, lanes t = 0, 1
+// collect vector 0 and t = 2, 3 vector 1.
+template <int NB, int P>
+__device__ __forceinline__ void tile_ctx_columns(TileCtx& cx, const uint8_t* planes, int plane_stride, int lane) {
+    cx.g = lane >> 2;
+    cx.t = lane & 3;
+    if (NB == 1) {
+        cx.colv = !(cx.g & 1) && (cx.g >> 1) < P;
+        cx.act = planes + (cx.g >> 1) * plane_stride;
+    } else {
+        cx.colv = (cx.g & 3) < P;
+        cx.act = planes + ((cx.g >> 2) * P + (cx.g & 3)) * plane_stride;
+    }
+}
+
+template <int NB>
+__device__ __forceinline__ void scale_add(int (&S)[4], int sa, int sb, const int (&c)[4]) {
+    S[0] += sa * c[0];
+    S[2] += sb * c[2];
+    if (NB != 1) {
+        S[1] += sa * c[1];
+        S[3] += sb * c[3];
+    }
+}
+
+// integer sums -> f32, times the scale of the plane(s) this lane holds
+template <int NB>
+__device__ __forceinline__ void plane_scale(const TileCtx& x, int b, const int (&S)[4], float& fA, float& fB) {
+    if (NB == 1) {
+        const float dp = x.dpl[8 * b + x.t];  // 0 for t >= planes
+        fA = dp * (float)S[0];
+        fB = dp * (float)S[2];
+    } else {
+        const float2 dp = *reinterpret_cast<const float2*>(x.dpl + 8 * b + 2 * x.t);
+        fA = fmaf(dp.x, (float)S[0], dp.y * (float)S[1]);
+        fB = fmaf(dp.x, (float)S[2], dp.y * (float)S[3]);
+    }
+}
 
 // sum over this lane's two sub-blocks (2t, 2t+1) of m_s * sum(activations of sub-block s)
 __device__ __forceinline__ float min_term_lane(uint64_t m8, const float* xs16b, int t) {
@@ -135,7 +175,7 @@ __device__ __forceinline__ void tile_q4k(const uint8_t* rA, const uint8_t* rB, i
     uint64_t scA, mA, scB, mB;
     decode_scales_k4(hA, scA, mA);
     decode_scales_k4(hB, scB, mB);
-    const uint8_t* ap = x.act + x.g * x.plane_stride + 256 * b + 8 * x.t;
+    const uint8_t* ap = x.act + 256 * b + 8 * x.t;
     int S[4] = {0, 0, 0, 0};
 #pragma unroll
     for (int p = 0; p < 4; ++p) {
@@ -150,15 +190,14 @@ __device__ __forceinline__ void tile_q4k(const uint8_t* rA, const uint8_t* rB, i
         // sub-block 2p: low nibbles.  Its scale is taken x16 so that it matches the high nibbles left in place below.
         mma_u8s8_k32(c, wA.x & 0x0f0f0f0fu, wB.x & 0x0f0f0f0fu, wA.y & 0x0f0f0f0fu, wB.y & 0x0f0f0f0fu, be.x, be.y);
         int sa = byte64(scA, 2 * p) << 4, sb = byte64(scB, 2 * p) << 4;
-        S[0] += sa * c[0]; S[1] += sa * c[1]; S[2] += sb * c[2]; S[3] += sb * c[3];
+        scale_add<NB>(S, sa, sb, c);
         // sub-block 2p+1: high nibbles, 16 * q
         mma_u8s8_k32(c, wA.x & 0xf0f0f0f0u, wB.x & 0xf0f0f0f0u, wA.y & 0xf0f0f0f0u, wB.y & 0xf0f0f0f0u, bo.x, bo.y);
         sa = byte64(scA, 2 * p + 1); sb = byte64(scB, 2 * p + 1);
-        S[0] += sa * c[0]; S[1] += sa * c[1]; S[2] += sb * c[2]; S[3] += sb * c[3];
+        scale_add<NB>(S, sa, sb, c);
     }
-    const float2 dp = *reinterpret_cast<const float2*>(x.dpl + 8 * b + 2 * x.t);
-    const float fA = fmaf(dp.x, (float)S[0], dp.y * (float)S[1]);
-    const float fB = fmaf(dp.x, (float)S[2], dp.y * (float)S[3]);
+    float fA, fB;
+    plane_scale<NB>(x, b, S, fA, fB);
     const float dA = half_bits_to_float(hA.x & 0xFFFFu), dminA = half_bits_to_float(hA.x >> 16);
     const float dB = half_bits_to_float(hB.x & 0xFFFFu), dminB = half_bits_to_float(hB.x >> 16);
     if (NB == 1) {
@@ -181,7 +220,7 @@ __device__ __forceinline__ void tile_q5k(const uint8_t* rA, const uint8_t* rB, i
     // fifth bits of values l = 8t..8t+7 of every sub-block: bit s of byte qh[l]
     const uint2 qA = *reinterpret_cast<const uint2*>(rA + 16 + 8 * x.t);
     const uint2 qB = *reinterpret_cast<const uint2*>(rB + 16 + 8 * x.t);
-    const uint8_t* ap = x.act + x.g * x.plane_stride + 256 * b + 8 * x.t;
+    const uint8_t* ap = x.act + 256 * b + 8 * x.t;
     int S[4] = {0, 0, 0, 0};
 #pragma unroll
     for (int p = 0; p < 4; ++p) {
@@ -196,17 +235,16 @@ __device__ __forceinline__ void tile_q5k(const uint8_t* rA, const uint8_t* rB, i
         mma_u8s8_k32(c, (wA.x & 0x0f0f0f0fu) | (((qA.x >> (2 * p)) & 0x01010101u) << 4), (wB.x & 0x0f0f0f0fu) | (((qB.x >> (2 * p)) & 0x01010101u) << 4),
                      (wA.y & 0x0f0f0f0fu) | (((qA.y >> (2 * p)) & 0x01010101u) << 4), (wB.y & 0x0f0f0f0fu) | (((qB.y >> (2 * p)) & 0x01010101u) << 4), be.x, be.y);
         int sa = byte64(scA, 2 * p), sb = byte64(scB, 2 * p);
-        S[0] += sa * c[0]; S[1] += sa * c[1]; S[2] += sb * c[2]; S[3] += sb * c[3];
+        scale_add<NB>(S, sa, sb, c);
         mma_u8s8_k32(c, ((wA.x >> 4) & 0x0f0f0f0fu) | (((qA.x >> (2 * p + 1)) & 0x01010101u) << 4),
                      ((wB.x >> 4) & 0x0f0f0f0fu) | (((qB.x >> (2 * p + 1)) & 0x01010101u) << 4),
                      ((wA.y >> 4) & 0x0f0f0f0fu) | (((qA.y >> (2 * p + 1)) & 0x01010101u) << 4),
                      ((wB.y >> 4) & 0x0f0f0f0fu) | (((qB.y >> (2 * p + 1)) & 0x01010101u) << 4), bo.x, bo.y);
         sa = byte64(scA, 2 * p + 1); sb = byte64(scB, 2 * p + 1);
-        S[0] += sa * c[0]; S[1] += sa * c[1]; S[2] += sb * c[2]; S[3] += sb * c[3];
+        scale_add<NB>(S, sa, sb, c);
     }
-    const float2 dp = *reinterpret_cast<const float2*>(x.dpl + 8 * b + 2 * x.t);
-    const float fA = fmaf(dp.x, (float)S[0], dp.y * (float)S[1]);
-    const float fB = fmaf(dp.x, (float)S[2], dp.y * (float)S[3]);
+    float fA, fB;
+    plane_scale<NB>(x, b, S, fA, fB);
     const float dA = half_bits_to_float(hA.x & 0xFFFFu), dminA = half_bits_to_float(hA.x >> 16);
     const float dB = half_bits_to_float(hB.x & 0xFFFFu), dminB = half_bits_to_float(hB.x >> 16);
     if (NB == 1) {
@@ -227,7 +265,7 @@ __device__ __forceinline__ void tile_q6k(const uint8_t* rA, const uint8_t* rB, f
     const uint4 sB4 = *reinterpret_cast<const uint4*>(rB + 192);
     const uint32_t scwA[4] = {sA4.x, sA4.y, sA4.z, sA4.w}, scwB[4] = {sB4.x, sB4.y, sB4.z, sB4.w};
     auto sc_of = [](const uint32_t (&w)[4], int is) -> int { return ((int)(w[is >> 2] << (24 - 8 * (is & 3)))) >> 24; };
-    const uint8_t* ap = x.act + x.g * x.plane_stride + 256 * b + 4 * x.t;
+    const uint8_t* ap = x.act + 256 * b + 4 * x.t;
     int S[4] = {0, 0, 0, 0};
 #pragma unroll
     for (int n = 0; n < 2; ++n) {
@@ -251,13 +289,12 @@ __device__ __forceinline__ void tile_q6k(const uint8_t* rA, const uint8_t* rB, f
                 mma_u8s8_k16(c, qa[qd], qb[qd], bv);
                 const int is = 8 * n + cc + 2 * qd;
                 const int sa = sc_of(scwA, is), sb = sc_of(scwB, is);
-                S[0] += sa * c[0]; S[1] += sa * c[1]; S[2] += sb * c[2]; S[3] += sb * c[3];
+                scale_add<NB>(S, sa, sb, c);
             }
         }
     }
-    const float2 dp = *reinterpret_cast<const float2*>(x.dpl + 8 * b + 2 * x.t);
-    const float fA = fmaf(dp.x, (float)S[0], dp.y * (float)S[1]);
-    const float fB = fmaf(dp.x, (float)S[2], dp.y * (float)S[3]);
+    float fA, fB;
+    plane_scale<NB>(x, b, S, fA, fB);
     float tA = 0.f, tB = 0.f;
     if (NB == 1) {
         // offset term, this lane's four groups 4t..4t+3 (scale word t, selected without indexing the array dynamically)

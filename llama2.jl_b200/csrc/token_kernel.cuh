@@ -650,10 +650,7 @@ __global__ void __launch_bounds__(TK_THREADS, 1) token_kernel(const __grid_const
     cx.act = act;
     cx.dpl = dpl;
     cx.xs16 = xs16;
-    cx.plane_stride = S.plane_stride;
-    cx.g = lane >> 2;
-    cx.t = lane & 3;
-    cx.colv = cx.g < P;
+    tile_ctx_columns<1, P>(cx, act, S.plane_stride, lane);
     const int pj = ((cx.g & 3) << 1) | (cx.g >> 2);
     const int grp = warp / WG, wl = warp - grp * WG;
     int slot_i = grp * NSG;
