@@ -248,7 +248,7 @@ int32_t l2b_attention(float* host_out, const float* host_q, const float* host_k,
  * region where the CUDA allocator may not be entered.
  *   dev_q [n_heads][hs], dev_out [n_heads][hs]; dev_kcache, dev_vcache [n_kv_heads][seq_len][hs] f32, of which
  *   positions 0..n_pos-1 are attended.  The launch is asynchronous on `stream` (cudaStream_t; NULL = default).
- * Scratch for the partial results lives in one fixed device array inside the library (about 1 MiB per device), so:
+ * Scratch for the partial results lives in one fixed device array inside the library (about 0.26 MiB per device), so:
  *   - limits: n_heads <= 128, head_size <= 128 (a multiple of 8), at most 16 splits; larger shapes are rejected with
  *     L2B_ERR_BAD_ARG;
  *   - the first call on each device resolves the array's address and must be made outside any stream capture;

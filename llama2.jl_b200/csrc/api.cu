@@ -177,19 +177,31 @@ static int32_t query_device(DeviceInfo& di) {
     return L2B_OK;
 }
 
+// cluster > 1: the grid is launched as thread-block clusters of that many consecutive blocks.
 template <typename Kernel, typename Params>
-static cudaError_t launch_kernel(Kernel k, dim3 grid, dim3 block, size_t smem, cudaStream_t st, bool pdl, const Params& prm) {
+static cudaError_t launch_kernel(Kernel k, dim3 grid, dim3 block, size_t smem, cudaStream_t st, bool pdl, const Params& prm, int cluster = 1) {
     cudaLaunchConfig_t cfg;
     memset(&cfg, 0, sizeof(cfg));
     cfg.gridDim = grid;
     cfg.blockDim = block;
     cfg.dynamicSmemBytes = smem;
     cfg.stream = st;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchAttribute attr[2];
+    int n = 0;
+    if (pdl) {
+        attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[n].val.programmaticStreamSerializationAllowed = 1;
+        ++n;
+    }
+    if (cluster > 1) {
+        attr[n].id = cudaLaunchAttributeClusterDimension;
+        attr[n].val.clusterDim.x = (unsigned)cluster;
+        attr[n].val.clusterDim.y = 1;
+        attr[n].val.clusterDim.z = 1;
+        ++n;
+    }
     cfg.attrs = attr;
-    cfg.numAttrs = pdl ? 1 : 0;
+    cfg.numAttrs = n;
     return cudaLaunchKernelEx(&cfg, k, prm);
 }
 
@@ -387,12 +399,20 @@ static cudaError_t launch_attention(const AttnParams& a, int gq, cudaStream_t st
             case 2: return launch_kernel(attention_split_kernel<2, 2>, grid, block, 0, st, pdl, a);
             default: return launch_kernel(attention_split_kernel<1, 2>, grid, block, 0, st, pdl, a);
         }
+    // one query position: clusters of ATTN_CL blocks (a.nsplit is a multiple of it, see decode_splits)
+    const dim3 dblock(ATTN_DW * 32);
     switch (gq) {
-        case 8: return launch_kernel(attention_decode_kernel<8>, grid, block, 0, st, pdl, a);
-        case 4: return launch_kernel(attention_decode_kernel<4>, grid, block, 0, st, pdl, a);
-        case 2: return launch_kernel(attention_decode_kernel<2>, grid, block, 0, st, pdl, a);
-        default: return launch_kernel(attention_decode_kernel<1>, grid, block, 0, st, pdl, a);
+        case 8: return launch_kernel(attention_decode_kernel<8>, grid, dblock, 0, st, pdl, a, ATTN_CL);
+        case 4: return launch_kernel(attention_decode_kernel<4>, grid, dblock, 0, st, pdl, a, ATTN_CL);
+        case 2: return launch_kernel(attention_decode_kernel<2>, grid, dblock, 0, st, pdl, a, ATTN_CL);
+        default: return launch_kernel(attention_decode_kernel<1>, grid, dblock, 0, st, pdl, a, ATTN_CL);
     }
+}
+// Blocks per head group of the decode attention kernel for contexts of up to max_pos positions: one cluster per
+// ATTN_CLUSTER_POS positions, at most four clusters (the final merge holds one partial result per cluster in registers).
+static int decode_splits(int max_pos) {
+    const int ncl = std::max(1, std::min(4, (max_pos + ATTN_CLUSTER_POS - 1) / ATTN_CLUSTER_POS));
+    return ncl * ATTN_CL;
 }
 static int choose_gq(int n_heads, int n_kv) {
     const int r = n_heads / n_kv;
@@ -1082,9 +1102,13 @@ static int32_t enqueue_token(l2b_session* s, int* nlaunch, int nb = 1) {
             a.nq = nb; a.q_stride = m->l_qdim();
             a.min_chunk = (int)env_long("L2B_ATTN_MIN_CHUNK", 0);
 #ifdef L2B_MEASURE
-            if (s->attn_trace) a.trace = s->attn_trace + (size_t)l * 1024 * 8;
+            if (s->attn_trace) a.trace = s->attn_trace + (size_t)l * 1024 * 16;
+            a.late_trigger = (int)env_long("L2B_ATTN_LATE_TRIGGER", 0);
 #endif
             CU(launch_attention(a, s->gq, s->stream, true));
+#ifdef L2B_MEASURE
+            if (env_long("L2B_ATTN_TWICE", 0)) CU(launch_attention(a, s->gq, s->stream, true));  // the second launch finds its instructions cached
+#endif
             ++count;
         }
         // --- output projection + residual (inference.jl:281-284)
@@ -1498,14 +1522,11 @@ extern "C" int32_t l2b_session_create(l2b_model* m, void* stream, l2b_session** 
             s->own_stream = true;
         }
         s->gq = choose_gq(m->l_heads, m->l_kv);
-        const int groups = m->l_heads / s->gq;
-        // splits of the position range: about 1.3 blocks per SM for short contexts, where the launch is latency-bound (measured:
-        // 24 splits beat 19 and 32 at the 8-group 8B shape, seq_len 512), about 3.4 per SM for long ones, where it has to keep
-        // many loads in flight (Phi-3-mini shape, seq_len 4096, 32 groups: 16 splits gave 906 tok/s, 6 gave 708, 32 gave 893)
-        const int per_sm_x10 = c.seq_len >= 2048 ? 34 : 13;
-        int ns = (s->di.sms * per_sm_x10 / 10 + groups - 1) / groups;
-        ns = std::max(1, std::min(ns, std::min(32, (c.seq_len + 7) / 8)));
-        s->nsplit = (int)std::max<long>(1, std::min<long>(32, env_long("L2B_ATTN_SPLITS", ns)));  // the merge gives a lane to each split
+        // blocks per head group in the attention launches: whole clusters for the decode kernel (L2B_ATTN_SPLITS is rounded up)
+        {
+            const long want = env_long("L2B_ATTN_SPLITS", decode_splits(c.seq_len));
+            s->nsplit = (int)std::max<long>(ATTN_CL, std::min<long>(4 * ATTN_CL, (want + ATTN_CL - 1) / ATTN_CL * ATTN_CL));
+        }
         const size_t kvl = kv_layer_elems(m);
         // q, att, hb and the caches hold this rank's heads / hidden units only (everything, on one GPU)
         // (two of each vector: the two-position prompt passes keep both positions' activations side by side)
@@ -1549,8 +1570,8 @@ extern "C" int32_t l2b_session_create(l2b_model* m, void* stream, l2b_session** 
             const size_t n = (size_t)(4 * c.n_layers + 1) * s->di.sms * 16;
             CU(cudaMalloc(&s->trace, n * 8));
             CU(cudaMemset(s->trace, 0, n * 8));
-            CU(cudaMalloc(&s->attn_trace, (size_t)c.n_layers * 1024 * 8 * 8));
-            CU(cudaMemset(s->attn_trace, 0, (size_t)c.n_layers * 1024 * 8 * 8));
+            CU(cudaMalloc(&s->attn_trace, (size_t)c.n_layers * 1024 * 16 * 8));
+            CU(cudaMemset(s->attn_trace, 0, (size_t)c.n_layers * 1024 * 16 * 8));
         }
 #endif
         if (m->tp > 1) {
@@ -1841,20 +1862,24 @@ static void dump_token_trace(l2b_session* s) {
                     rel(mn[6]), rel(av[6] / nb), rel(mx[6]), rel(av[7] / nb), rel(mx[7]), nb, mx[7]);
         prev_end = std::max(mx[6], mx[7]);
         if (s->attn_trace && k % 4 == 0 && k / 4 < s->model->cfg.n_layers && k < 16) {  // the attention launch that follows this layer's qkv launch
-            std::vector<unsigned long long> a((size_t)1024 * 8);
-            if (cudaMemcpy(a.data(), s->attn_trace + (size_t)(k / 4) * 1024 * 8, a.size() * 8, cudaMemcpyDeviceToHost) != cudaSuccess) continue;
-            double amn[4], amx[4], aav[4];
-            int cnt[4] = {0, 0, 0, 0};
-            for (int i = 0; i < 4; ++i) amn[i] = 1e30, amx[i] = -1e30, aav[i] = 0;
+            std::vector<unsigned long long> a((size_t)1024 * 16);
+            if (cudaMemcpy(a.data(), s->attn_trace + (size_t)(k / 4) * 1024 * 16, a.size() * 8, cudaMemcpyDeviceToHost) != cudaSuccess) continue;
+            double amn[16], amx[16], aav[16];
+            int cnt[16];
+            for (int i = 0; i < 16; ++i) amn[i] = 1e30, amx[i] = -1e30, aav[i] = 0, cnt[i] = 0;
             for (int b = 0; b < 1024; ++b)
-                for (int i = 0; i < 4; ++i) {
-                    if (!a[(size_t)b * 8 + i]) continue;
-                    const double v = (double)(a[(size_t)b * 8 + i] - t0) / 1e3 - prev_end;
+                for (int i = 0; i < 16; ++i) {
+                    if (!a[(size_t)b * 16 + i]) continue;
+                    const double v = (double)(a[(size_t)b * 16 + i] - t0) / 1e3 - prev_end;
                     amn[i] = std::min(amn[i], v); amx[i] = std::max(amx[i], v); aav[i] += v; ++cnt[i];
                 }
             fprintf(stderr, "     attention: blocks %d | start %6.2f %6.2f %6.2f | wait over %6.2f %6.2f %6.2f | positions done %6.2f %6.2f %6.2f | merged %6.2f %6.2f %6.2f\n", cnt[0],
                     amn[0], aav[0] / std::max(cnt[0], 1), amx[0], amn[1], aav[1] / std::max(cnt[1], 1), amx[1], amn[2], aav[2] / std::max(cnt[2], 1), amx[2],
                     amn[3], aav[3] / std::max(cnt[3], 1), amx[3]);
+            fprintf(stderr, "                block barrier %6.2f %6.2f | pushed %6.2f %6.2f | cluster barrier over %6.2f %6.2f (avg, max)\n", aav[4] / std::max(cnt[4], 1), amx[4],
+                    aav[5] / std::max(cnt[5], 1), amx[5], aav[6] / std::max(cnt[6], 1), amx[6]);
+            fprintf(stderr, "                averages: block max known %6.2f | block sums done %6.2f | output pushed %6.2f | received max known %6.2f | received sums done %6.2f\n",
+                    aav[7] / std::max(cnt[7], 1), aav[8] / std::max(cnt[8], 1), aav[9] / std::max(cnt[9], 1), aav[10] / std::max(cnt[10], 1), aav[11] / std::max(cnt[11], 1));
         }
     }
 }
@@ -2350,7 +2375,7 @@ extern "C" int32_t l2b_attention(float* host_out, const float* host_q, const flo
             memcpy(&vc[((size_t)h * n_pos + t) * hs], host_v + ((size_t)t * n_kv + h) * hs, (size_t)hs * 4);
         }
     const int gq = choose_gq(n_heads, n_kv);
-    const int nsplit = std::max(1, std::min(32, std::min((n_pos + 7) / 8, (int)env_long("L2B_ATTN_SPLITS", 16))));
+    const int nsplit = decode_splits(n_pos);
     DevBuf q, k, v, pm, pl, pa, out, tickets;
     L2B_TRY(dev_upload(q, host_q, (size_t)n_heads * hs * 4));
     L2B_TRY(dev_upload(k, kc.data(), kc.size() * 4));
@@ -2592,8 +2617,8 @@ extern "C" int32_t l2b_matvec(int32_t type, const void* host_W, int64_t in_dim, 
 // ---------------------------------------------------------------------------------------------
 // Attention on device pointers that allocates nothing
 // ---------------------------------------------------------------------------------------------
-// The split-KV attention kernel needs scratch memory for the per-split partial results and the tickets that
-// elect the merging block.  l2b_attention allocates that scratch per call; this entry point keeps it in one
+// For contexts of more than 256 positions the decode attention kernel needs scratch memory: one partial result per
+// cluster of blocks and the tickets that elect the merging cluster.  l2b_attention allocates that scratch per call; this entry point keeps it in one
 // file-scope device array of fixed size instead, so the call makes no device, pinned or managed allocation and
 // frees nothing.  Consequences, all of them the caller's to respect:
 //   * the first call on each device looks the array's address up (cudaGetSymbolAddress) and must therefore be
@@ -2607,20 +2632,20 @@ namespace {
 
 constexpr int NA_MAX_HEADS = 128;   // query heads
 constexpr int NA_MAX_HS = 128;      // head size
-constexpr int NA_MAX_SPLITS = 16;   // splits of the position range
+constexpr int NA_MAX_CLUSTERS = 4;  // clusters per head group (decode_splits): one scratch row each
 constexpr int NA_MAX_DEVICES = 64;
-constexpr size_t NA_ACC_FLOATS = (size_t)NA_MAX_HEADS * NA_MAX_SPLITS * NA_MAX_HS;  // 262144 floats = 1 MiB
-constexpr size_t NA_ML_FLOATS = (size_t)NA_MAX_HEADS * NA_MAX_SPLITS;               // 2048 floats each for max and sum
+constexpr size_t NA_ACC_FLOATS = (size_t)NA_MAX_HEADS * NA_MAX_CLUSTERS * NA_MAX_HS;  // 65536 floats = 256 KiB
+constexpr size_t NA_ML_FLOATS = (size_t)NA_MAX_HEADS * NA_MAX_CLUSTERS;               // 512 floats each for max and sum
 constexpr size_t NA_SCRATCH_FLOATS = NA_ACC_FLOATS + 2 * NA_ML_FLOATS + NA_MAX_HEADS;  // + tickets (int32)
 
-// 1 MiB + 16.5 KiB of scratch per device, inside the module's global memory (no allocation at run time).
+// 256 KiB + 4.5 KiB of scratch per device, inside the module's global memory (no allocation at run time).
 static __device__ __align__(256) float g_attn_static_scratch[NA_SCRATCH_FLOATS];
 
 std::mutex g_na_mutex;
 float* g_na_scratch_addr[NA_MAX_DEVICES] = {nullptr};
 
 template <int GQ>
-__global__ void __launch_bounds__(ATTN_WARPS * 32) attention_static_scratch_kernel(const __grid_constant__ AttnParams p) {
+__global__ void __launch_bounds__(ATTN_DW * 32) attention_static_scratch_kernel(const __grid_constant__ AttnParams p) {
     attention_decode_body<GQ, false>(p);  // the arithmetic of l2b_attention, in the same order
 }
 
@@ -2650,8 +2675,8 @@ extern "C" int32_t l2b_attention_device_noalloc(float* dev_out, const float* dev
     }
     const int gq = choose_gq(n_heads, n_kv);
     // the same split rule as l2b_attention, so that both entry points add in the same order
-    const int nsplit = std::max(1, std::min(NA_MAX_SPLITS, std::min((n_pos + 7) / 8, (int)env_long("L2B_ATTN_SPLITS", 16))));
-    if ((size_t)n_heads * nsplit * hs > NA_ACC_FLOATS || (size_t)n_heads * nsplit > NA_ML_FLOATS)
+    const int nsplit = decode_splits(n_pos);
+    if ((size_t)n_heads * (nsplit / ATTN_CL) * hs > NA_ACC_FLOATS || (size_t)n_heads * (nsplit / ATTN_CL) > NA_ML_FLOATS)
         return fail(L2B_ERR_BAD_ARG, "l2b_attention_device_noalloc: shape exceeds the static scratch array");
     cudaStream_t st = (cudaStream_t)stream;
     AttnParams a;
@@ -2664,12 +2689,12 @@ extern "C" int32_t l2b_attention_device_noalloc(float* dev_out, const float* dev
     a.n_heads = n_heads; a.n_kv = n_kv; a.hs = hs; a.seq_len = seq_len; a.nsplit = nsplit; a.npos_override = n_pos;
     // the array keeps the last call's contents: the tickets must be zero when the kernel starts
     CU(cudaMemsetAsync(a.tickets, 0, (size_t)NA_MAX_HEADS * sizeof(int), st));
-    const dim3 grid((n_heads / gq) * nsplit), block(ATTN_WARPS * 32);
+    const dim3 grid((n_heads / gq) * nsplit), block(ATTN_DW * 32);
     switch (gq) {
-        case 8: attention_static_scratch_kernel<8><<<grid, block, 0, st>>>(a); break;
-        case 4: attention_static_scratch_kernel<4><<<grid, block, 0, st>>>(a); break;
-        case 2: attention_static_scratch_kernel<2><<<grid, block, 0, st>>>(a); break;
-        default: attention_static_scratch_kernel<1><<<grid, block, 0, st>>>(a); break;
+        case 8: CU(launch_kernel(attention_static_scratch_kernel<8>, grid, block, 0, st, false, a, ATTN_CL)); break;
+        case 4: CU(launch_kernel(attention_static_scratch_kernel<4>, grid, block, 0, st, false, a, ATTN_CL)); break;
+        case 2: CU(launch_kernel(attention_static_scratch_kernel<2>, grid, block, 0, st, false, a, ATTN_CL)); break;
+        default: CU(launch_kernel(attention_static_scratch_kernel<1>, grid, block, 0, st, false, a, ATTN_CL)); break;
     }
     CU(cudaGetLastError());
     return L2B_OK;

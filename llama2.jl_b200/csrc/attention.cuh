@@ -37,14 +37,15 @@ struct AttnParams {
     int pos_base;       // position of the first query when `pos` is null (launches outside the captured token graph)
     const int* pos_list;     // batched decode: query qi belongs to its own sequence, at position pos_list[qi] ...
     size_t cache_stride_q;   // ... whose caches start cache_stride_q * qi elements after kc / vc
-    unsigned long long* trace;  // measurement build only: 8 time stamps per block of the decode kernel, or null
+    int late_trigger;           // measurement build only: release the dependent kernel at the end instead of at the start
+    unsigned long long* trace;  // measurement build only: 16 time stamps per block of the decode kernel, or null
 };
 
 #ifdef L2B_MEASURE
 #define ATTN_TRACE(i)                                                                                                   \
     do {                                                                                                                \
         if (p.trace && threadIdx.x == 0) asm volatile("{.reg .u64 t; mov.u64 t, %%globaltimer; st.global.u64 [%0], t;}" \
-                                                      ::"l"(p.trace + (size_t)blockIdx.x * 8 + (i)) : "memory");          \
+                                                      ::"l"(p.trace + (size_t)blockIdx.x * 16 + (i)) : "memory");          \
     } while (0)
 #else
 #define ATTN_TRACE(i) do {} while (0)
@@ -245,27 +246,70 @@ __device__ __forceinline__ void attention_split_body(const AttnParams& p) {
     attention_merge<GQ>(p, m, l, acc, hg, sp, active, hq, obase, ticket_p, lane_active);
 }
 
-// One query position per launch (the decode path), built for latency.  The keys and values of earlier positions were
-// written by earlier tokens, so the first batch of every warp is fetched BEFORE the wait on the previous kernel (which
-// writes q and this position's key and value): the cache latency hides behind that kernel's tail.  A batch of
-// ATTN_UNROLL positions is scored without branches (all dot products and their lane reductions are independent), then
-// folded into the running softmax with one maximum and one set of exponentials per batch.
+// ---- decode: one query position per launch, built for latency ------------------------------------------------
+// Grid: (n_heads / GQ) * nsplit blocks of ATTN_DW warps, launched as thread-block clusters of ATTN_CL consecutive blocks
+// (nsplit is a multiple of ATTN_CL), so a head group is served by nsplit / ATTN_CL clusters.
+//  * The keys and values of earlier positions were written by earlier tokens: the first batch of every warp is fetched
+//    BEFORE the wait on the previous kernel (which writes q and this position's key and value), so the cache latency hides
+//    behind that kernel's tail.
+//  * A batch of ATTN_UNROLL positions is scored without branches (all dot products and their lane reductions are independent),
+//    then folded into the running softmax with one maximum and one set of exponentials per batch.
+//  * The blocks of a cluster merge through distributed shared memory: every block reduces its warps in its own shared memory
+//    and stores each part of the result into the shared memory of the block that finishes that part of the output; one
+//    cluster barrier later every block combines what it received and writes its slice.  Up to ATTN_CL * ATTN_DW * ATTN_UNROLL
+//    = 256 positions need no global scratch, fence or atomic at all.  Longer contexts use more clusters per head group; those
+//    exchange one partial result per cluster through scratch memory and a ticket.
+constexpr int ATTN_CL = 8;  // blocks per cluster (the portable maximum)
+constexpr int ATTN_DW = 8;  // warps per block
+constexpr int ATTN_CLUSTER_POS = ATTN_CL * ATTN_DW * ATTN_UNROLL;  // positions a cluster takes in one batch per warp
+
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t cluster_map(const void* smem_ptr, uint32_t rank) {  // the same variable in block `rank` of the cluster
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_u32(smem_ptr)), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void st_cluster_f32(uint32_t addr, float v) { asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory"); }
+__device__ __forceinline__ void st_cluster_f32x4(uint32_t addr, float4 v) {
+    asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w) : "memory");
+}
+__device__ __forceinline__ float ld_cluster_f32(uint32_t addr) {
+    float v;
+    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(addr) : "memory");
+    return v;
+}
+__device__ __forceinline__ float4 ld_cluster_f32x4(uint32_t addr) {
+    float4 v;
+    asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr) : "memory");
+    return v;
+}
+
 // PDL = false: launched without a programmatic dependency (no previous kernel to wait for).
 template <int GQ, bool PDL>
 __device__ __forceinline__ void attention_decode_body(const AttnParams& p) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     ATTN_TRACE(0);
     const int hg = (int)blockIdx.x / p.nsplit, sp = (int)blockIdx.x % p.nsplit;
+    const int cg = sp / ATTN_CL, rank = sp % ATTN_CL;  // cluster of the head group, block of the cluster (clusters are consecutive blocks)
+    const int ncl = p.nsplit / ATTN_CL;
     const int kvh = (hg * GQ) / (p.n_heads / p.n_kv);
     const int npos = p.npos_override > 0 ? p.npos_override : ((p.pos ? __ldcg(p.pos) : p.pos_base) + 1);  // the position is set before the token starts
-    const int mc = p.min_chunk > 0 ? p.min_chunk : ATTN_MIN_CHUNK;
-    const int active = min(p.nsplit, (npos + mc - 1) / mc);
-    if (sp >= active) return;
-    const int chunk = (npos + active - 1) / active;
-    const int t0 = sp * chunk, t1 = min(npos, t0 + chunk);
+    // clusters at work: one per ATTN_CLUSTER_POS positions (or per min_chunk); the others leave at once, whole
+    const int per = p.min_chunk > 0 ? p.min_chunk : ATTN_CLUSTER_POS;
+    const int ac = min(ncl, (npos + per - 1) / per);
+    if (cg >= ac) return;
+    const int nblk = ac * ATTN_CL;
+    const int chunk = (npos + nblk - 1) / nblk;
+    const int t0 = min(npos, (cg * ATTN_CL + rank) * chunk), t1 = min(npos, t0 + chunk);  // (an empty range contributes nothing)
     const int hs = p.hs;
     const bool lane_active = 4 * lane < hs;
-    const float div = sqrtf((float)hs);
+    // A warp's own instruction stream is the critical path of this kernel (dependent instructions issue every ten cycles or so),
+    // so the arithmetic is kept short: att ./= sqrt(Float32(head_size)) and the softmax's exp become one multiplication
+    // by log2(e) / sqrt(head_size) and exp2 (a single special-function instruction, 2 ulp); maxima are kept in the same
+    // log2 domain, in which all merges below work; normalisation multiplies by a correctly rounded reciprocal.
+    const float inv_div = 1.4426950408889634f / sqrtf((float)hs);
     const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
     const float* kbase = p.kc + (size_t)kvh * p.seq_len * hs;
     const float* vbase = p.vc + (size_t)kvh * p.seq_len * hs;
@@ -300,7 +344,7 @@ __device__ __forceinline__ void attention_decode_body(const AttnParams& p) {
             vv[u] = __ldcg(reinterpret_cast<const float4*>(vbase + (size_t)t * hs) + lane);
         }
     }
-    for (int tb = tb0; tb < t1; tb += ATTN_WARPS * ATTN_UNROLL) {
+    for (int tb = tb0; tb < t1; tb += ATTN_DW * ATTN_UNROLL) {
         if (tb != tb0) {
 #pragma unroll
             for (int u = 0; u < ATTN_UNROLL; ++u) {
@@ -332,15 +376,15 @@ __device__ __forceinline__ void attention_decode_body(const AttnParams& p) {
             float mx = m[g];
 #pragma unroll
             for (int u = 0; u < ATTN_UNROLL; ++u) {
-                s[u][g] = (tb + u < t1) ? s[u][g] / div : -INFINITY;  // att ./= sqrt(Float32(head_size)); positions beyond the range weigh nothing
+                s[u][g] = (tb + u < t1) ? s[u][g] * inv_div : -INFINITY;  // positions beyond the range weigh nothing
                 mx = fmaxf(mx, s[u][g]);
             }
-            const float corr = expf(m[g] - mx);  // 0 for the first batch (m = -inf; the batch's first position is always in range)
+            const float corr = exp2f(m[g] - mx);  // 0 for the first batch (m = -inf; the batch's first position is always in range)
             float ps = 0.f;
             float4 pv = zero4;
 #pragma unroll
             for (int u = 0; u < ATTN_UNROLL; ++u) {
-                const float pr = expf(s[u][g] - mx);
+                const float pr = exp2f(s[u][g] - mx);
                 ps += pr;
                 pv.x = fmaf(pr, vv[u].x, pv.x);
                 pv.y = fmaf(pr, vv[u].y, pv.y);
@@ -356,12 +400,148 @@ __device__ __forceinline__ void attention_decode_body(const AttnParams& p) {
         }
     }
     ATTN_TRACE(2);
-    attention_merge<GQ>(p, m, l, acc, hg, sp, active, 0, p.out, p.tickets + hg, lane_active);
+
+    // ---- the warps of this block, in its own shared memory
+    constexpr int PER_BLOCK = GQ * 32 / ATTN_CL;  // float4s of the head group's output that one block of the cluster finishes
+    __shared__ float sm[ATTN_DW][GQ], sl[ATTN_DW][GQ];
+    __shared__ float4 sacc[ATTN_DW][GQ][32];
+    // what the blocks of the cluster send to this one: per sending block, maximum and sum of every query head and the
+    // PER_BLOCK float4s of unnormalised output that this block finishes
+    __shared__ float rx_m[ATTN_CL][GQ], rx_l[ATTN_CL][GQ];
+    __shared__ float4 rx_a[ATTN_CL][PER_BLOCK];
+    __shared__ int s_last;
+#pragma unroll
+    for (int g = 0; g < GQ; ++g) {
+        if (lane == 0) {
+            sm[warp][g] = m[g];
+            sl[warp][g] = l[g];
+        }
+        sacc[warp][g][lane] = acc[g];
+    }
+    __syncthreads();
+    for (int g = warp; g < GQ; g += ATTN_DW) {
+        float M = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < ATTN_DW; ++w) M = fmaxf(M, sm[w][g]);
+        float Ls = 0.f;
+        float4 a = zero4;
+#pragma unroll
+        for (int w = 0; w < ATTN_DW; ++w) {
+            const float wgt = (sm[w][g] == -INFINITY) ? 0.f : exp2f(sm[w][g] - M);
+            Ls = fmaf(sl[w][g], wgt, Ls);
+            const float4 b = sacc[w][g][lane];
+            a.x = fmaf(b.x, wgt, a.x);
+            a.y = fmaf(b.y, wgt, a.y);
+            a.z = fmaf(b.z, wgt, a.z);
+            a.w = fmaf(b.w, wgt, a.w);
+        }
+        // ---- stored into the shared memory of the block that finishes this part of the output (remote stores): after ONE
+        // cluster barrier every block works on its own shared memory only, so nobody has to outlive a reader
+        const int item = g * 32 + lane;
+        st_cluster_f32x4(cluster_map(&rx_a[rank][item % PER_BLOCK], (uint32_t)(item / PER_BLOCK)), a);
+        if (lane < ATTN_CL) {
+            st_cluster_f32(cluster_map(&rx_m[rank][g], (uint32_t)lane), M);
+            st_cluster_f32(cluster_map(&rx_l[rank][g], (uint32_t)lane), Ls);
+        }
+    }
+    ATTN_TRACE(5);
+    cluster_sync_all();
+    ATTN_TRACE(6);
+    if ((int)threadIdx.x < PER_BLOCK) {
+        const int item = rank * PER_BLOCK + (int)threadIdx.x;
+        const int ig = item >> 5, il = item & 31;
+        float M = -INFINITY;
+#pragma unroll
+        for (int c = 0; c < ATTN_CL; ++c) M = fmaxf(M, rx_m[c][ig]);
+        float Ls = 0.f;
+        float4 a = zero4;
+#pragma unroll
+        for (int c = 0; c < ATTN_CL; ++c) {
+            const float wgt = (rx_m[c][ig] == -INFINITY) ? 0.f : exp2f(rx_m[c][ig] - M);
+            Ls = fmaf(rx_l[c][ig], wgt, Ls);
+            const float4 b = rx_a[c][threadIdx.x];
+            a.x = fmaf(b.x, wgt, a.x);
+            a.y = fmaf(b.y, wgt, a.y);
+            a.z = fmaf(b.z, wgt, a.z);
+            a.w = fmaf(b.w, wgt, a.w);
+        }
+        const int h = hg * GQ + ig;
+        if (4 * il < hs) {
+            if (ac == 1) {  // the cluster saw every position: this is the attention output
+                const float inv = __frcp_rn(Ls);
+                a.x *= inv; a.y *= inv; a.z *= inv; a.w *= inv;
+                reinterpret_cast<float4*>(p.out + (size_t)h * hs)[il] = a;
+            } else {
+                reinterpret_cast<float4*>(p.part_acc + ((size_t)h * ncl + cg) * hs)[il] = a;
+                if (il == 0) {
+                    p.part_m[(size_t)h * ncl + cg] = M;
+                    p.part_l[(size_t)h * ncl + cg] = Ls;
+                }
+            }
+        }
+    }
+    if (ac == 1) {
+        ATTN_TRACE(3);
+        return;
+    }
+    // ---- several clusters per head group: every block publishes its part of the cluster's partial result, the cluster that
+    // finishes last (a ticket counting blocks) merges the clusters' partial results
+    int* const ticket_p = p.tickets + hg;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence();  // cumulative: covers what the block's threads wrote before the barrier
+        const int ticket = atomicAdd(ticket_p, 1);
+        s_last = (ticket == ac * ATTN_CL - 1);
+        if (s_last) __threadfence();
+    }
+    __syncthreads();
     ATTN_TRACE(3);
+    if (!s_last) return;
+    for (int i = (int)threadIdx.x; i < GQ * 32; i += ATTN_DW * 32) {
+        const int g = i >> 5, l4 = i & 31, h = hg * GQ + g;
+        float Mc[4], Lc[4];
+        float4 Ac[4];
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {  // nsplit <= 4 * ATTN_CL
+            Mc[c] = -INFINITY;
+            Lc[c] = 0.f;
+            Ac[c] = zero4;
+            if (c < ac) {
+                Mc[c] = __ldcg(p.part_m + (size_t)h * ncl + c);
+                Lc[c] = __ldcg(p.part_l + (size_t)h * ncl + c);
+                if (4 * l4 < hs) Ac[c] = __ldcg(reinterpret_cast<const float4*>(p.part_acc + ((size_t)h * ncl + c) * hs) + l4);
+            }
+        }
+        const float M = fmaxf(fmaxf(Mc[0], Mc[1]), fmaxf(Mc[2], Mc[3]));
+        float Ls = 0.f;
+        float4 a = zero4;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            const float wgt = (Mc[c] == -INFINITY) ? 0.f : exp2f(Mc[c] - M);
+            Ls = fmaf(Lc[c], wgt, Ls);
+            a.x = fmaf(Ac[c].x, wgt, a.x);
+            a.y = fmaf(Ac[c].y, wgt, a.y);
+            a.z = fmaf(Ac[c].z, wgt, a.z);
+            a.w = fmaf(Ac[c].w, wgt, a.w);
+        }
+        if (4 * l4 < hs) {
+            const float inv = __frcp_rn(Ls);
+            a.x *= inv; a.y *= inv; a.z *= inv; a.w *= inv;
+            reinterpret_cast<float4*>(p.out + (size_t)h * hs)[l4] = a;
+        }
+    }
+    if (threadIdx.x == 0) *ticket_p = 0;  // ready for the next launch (ordered by the kernel boundary)
 }
 
 template <int GQ>
-__global__ void __launch_bounds__(ATTN_WARPS * 32) attention_decode_kernel(const __grid_constant__ AttnParams p) {
+__global__ void __launch_bounds__(ATTN_DW * 32) attention_decode_kernel(const __grid_constant__ AttnParams p) {
+#ifdef L2B_MEASURE
+    if (p.late_trigger) {  // measurement: the next kernel's blocks start only when this one is done
+        attention_decode_body<GQ, true>(p);
+        pdl_launch_dependents();
+        return;
+    }
+#endif
     pdl_launch_dependents();
     attention_decode_body<GQ, true>(p);
 }

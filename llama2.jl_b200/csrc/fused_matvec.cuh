@@ -336,6 +336,7 @@ __device__ __forceinline__ void build_activation(const MvParams& p, uint8_t* sme
         // once; the positive scalar 1/rms leaves them unchanged and only multiplies the plane scales and the per-16 sums,
         // which happens after the block-wide sum of squares (one barrier, whose wait the quantisation now overlaps).
         float ss = 0.f;
+        const float inv_n = 1.0f / (float)n;
         for (int t0 = 0; t0 < turns; t0 += MV_GAIN_BLOCKS) {
             float4 ka[MV_GAIN_BLOCKS], kb[MV_GAIN_BLOCKS], ga[MV_GAIN_BLOCKS], gb[MV_GAIN_BLOCKS];
 #pragma unroll
@@ -362,9 +363,11 @@ __device__ __forceinline__ void build_activation(const MvParams& p, uint8_t* sme
         consumer_sync(nwarps * 32);
         float tot = 0.f;
         for (int i = 0; i < nwarps; ++i) tot += red[i];  // same order in every thread
-        tot /= (float)n;
-        tot += 1e-5f;
-        const float scale = 1.0f / sqrtf(tot);
+        // 1 / sqrt(ss / n + eps) (src/inference.jl:105-107) with a multiplication by 1/n and a correctly rounded reciprocal
+        // square root: two divisions and a square root are about eighty dependent instructions, on the critical path of every
+        // layer twice.  The planes are an approximation of the f32 activations already (relative 1e-7); this is below it.
+        tot = fmaf(tot, inv_n, 1e-5f);
+        const float scale = __frsqrt_rn(tot);
         for (int turn = 0; turn < turns; ++turn) {  // this warp's blocks
             const int g0 = 32 * (warp + nwarps * turn);
             if (g0 >= n8) break;
