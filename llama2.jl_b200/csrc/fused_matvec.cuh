@@ -95,7 +95,7 @@ struct MvTp {
 
 // Offsets of the regions of a block's shared memory (mv_smem_layout).
 struct MvSmem {
-    int off_bar, off_red, off_dpl, off_xs, off_act, off_xf, off_ring, total;
+    int off_bar, off_ss, off_red, off_dpl, off_xs, off_act, off_xf, off_ring, total;
     int plane_stride, slot_bytes;
 };
 
@@ -150,7 +150,9 @@ __host__ __device__ inline MvSmem mv_smem_layout(int n_in, int planes, bool kqua
     const int nb = n_in / QK_K;
     int o = 0;
     s.off_bar = o;  // full[MV_MAX_SLOTS], empty[MV_MAX_SLOTS], red_full[MV_RED_BUFS], red_empty[MV_RED_BUFS]
-    o += (2 * MV_MAX_SLOTS + 2 * MV_RED_BUFS) * 8;
+    o += (2 * MV_MAX_SLOTS + 2 * MV_RED_BUFS + 1) * 8;  // ... and ss_ready (below)
+    s.off_ss = o;   // [MV_MAX_CONSUMERS] f32: the consumer warps' sums of squares, for the finisher warp (deferred rmsnorm scale)
+    o += MV_MAX_CONSUMERS * 4;
     o = (o + 15) & ~15;
     s.off_red = o;  // [MV_RED_BUFS][MV_MAX_CONSUMERS][16] f32 tile partials (also the block-sum scratch of the prologue)
     o += MV_RED_BUFS * MV_MAX_CONSUMERS * 16 * 4 * nbatch;
@@ -248,7 +250,10 @@ __device__ __noinline__ void quantise_block(float4 va, float4 vb, int lane, uint
 
 // Build the activation vector in shared memory.  KQ: int8 planes + sums; else f32 copy.
 // A warp takes 32 consecutive groups of 8 values (= one 256-value block) per turn.
-template <bool KQ, int P, bool TP = false, int ZHI = 8>
+// DEFER (k-quant weights behind an rmsnorm): the positive scalar 1/rms is not applied here at all.  The warps leave their sums of
+// squares at L.off_ss and the caller multiplies every RESULT by 1/rms instead (W (c z) = c (W z)); the block-wide reduction,
+// the square root and a second pass over the scales leave the critical path between "previous kernel done" and "first tile".
+template <bool KQ, int P, bool TP = false, int ZHI = 8, bool DEFER = false>
 __device__ __forceinline__ void build_activation(const MvParams& p, uint8_t* smem, const MvSmem& L, int warp, int lane, int nwarps, const float* x_in,
                                                  uint8_t* act, float* dpl, float* xs16) {
     const int n = p.n_in;
@@ -359,6 +364,14 @@ __device__ __forceinline__ void build_activation(const MvParams& p, uint8_t* sme
             }
         }
         ss = warp_sum(ss);
+        if (DEFER) {
+            if (lane == 0) {
+                reinterpret_cast<float*>(smem + L.off_ss)[warp] = ss;
+                mbar_arrive(reinterpret_cast<uint64_t*>(smem + L.off_bar) + 2 * MV_MAX_SLOTS + 2 * MV_RED_BUFS);  // ss_ready
+            }
+            consumer_sync(nwarps * 32);
+            return;
+        }
         if (lane == 0) red[warp] = ss;
         consumer_sync(nwarps * 32);
         float tot = 0.f;
@@ -734,6 +747,7 @@ __global__ void __launch_bounds__((MV_MAX_CONSUMERS + 2) * 32, 1) fused_matvec_k
     uint64_t* empty = full + MV_MAX_SLOTS;
     uint64_t* red_full = empty + MV_MAX_SLOTS;
     uint64_t* red_empty = red_full + MV_RED_BUFS;
+    uint64_t* ss_ready = red_empty + MV_RED_BUFS;  // every consumer warp has left its sum of squares (deferred rmsnorm scale)
     uint8_t* ring = smem + L.off_ring;
     // Waits of the producer and finisher warps on the consumer warps.  With tensor parallelism the consumers may themselves
     // be waiting, legitimately and for up to tp_timeout_ms, for another GPU's partial results: those waits are then bounded
@@ -752,6 +766,7 @@ __global__ void __launch_bounds__((MV_MAX_CONSUMERS + 2) * 32, 1) fused_matvec_k
             mbar_init(red_full + (threadIdx.x - 32), W / p.cgroups);
             mbar_init(red_empty + (threadIdx.x - 32), 1);
         }
+        if (threadIdx.x == 31) mbar_init(ss_ready, W);
         if (threadIdx.x < 32 + MV_RED_BUFS) {
             fence_barrier_init();
             fence_proxy_async();
@@ -893,6 +908,9 @@ __global__ void __launch_bounds__((MV_MAX_CONSUMERS + 2) * 32, 1) fused_matvec_k
         best.v = -INFINITY;
         best.i = 0x7fffffff;
         const float* red = reinterpret_cast<const float*>(smem + L.off_red);
+        // 1/rms of the input vector (deferred by the prologue, NB == 1): worked out from the warps' sums of squares when the first
+        // tile arrives, which orders their stores before these loads
+        float in_scale = 1.f;
         // lane = 16*q + 8*half + pair: sums the partials of warps w = q, q+2, ... of row `half` of pair `pair`
         const int fq = lane >> 4, fidx = lane & 15;
         const int WGf = W / p.cgroups;  // warps that contribute to one tile
@@ -900,6 +918,16 @@ __global__ void __launch_bounds__((MV_MAX_CONSUMERS + 2) * 32, 1) fused_matvec_k
         uint32_t par = 0;
         MvSegment sg = p.seg[0];
         bool dead = false;
+        if (NB == 1 && p.pro == PRO_RMSNORM && my_units > 0) {  // while the consumers work on the first tile
+            if (wait_partner(ss_ready, 0)) {
+                const float* ssw = reinterpret_cast<const float*>(smem + L.off_ss);
+                float tot = 0.f;
+                for (int i = 0; i < W; ++i) tot += ssw[i];  // same order in every block
+                in_scale = __frsqrt_rn(fmaf(tot, 1.0f / (float)p.n_in, 1e-5f));  // 1 / sqrt(ss / n + eps), src/inference.jl:105-107
+            } else {
+                dead = true;
+            }
+        }
         for (int j = 0; j < my_units && !dead; ++j, unit += (int)gridDim.x) {
             if (seg_i < 0 || unit >= seg_end) {
                 seg_i = find_unit<true>(p, unit).seg;
@@ -932,6 +960,7 @@ __global__ void __launch_bounds__((MV_MAX_CONSUMERS + 2) * 32, 1) fused_matvec_k
             __syncwarp();
             if (lane == 0) mbar_arrive(red_empty + rb);  // the buffer may be rewritten
             v += __shfl_xor_sync(0xffffffffu, v, 16);     // (even warps) + (odd warps)
+            if (NB == 1) v *= in_scale;
             const float vB = __shfl_sync(0xffffffffu, v, (lane & 7) + 8);
             if (mine) epilogue_pair<TP, true>(p, sg, t, v, vB, pos, best, 0, &pre0);
             if (NB == 2) {  // the second position
@@ -976,7 +1005,7 @@ __global__ void __launch_bounds__((MV_MAX_CONSUMERS + 2) * 32, 1) fused_matvec_k
         float* dpl = reinterpret_cast<float*>(smem + L.off_dpl);
         float* xs16 = reinterpret_cast<float*>(smem + L.off_xs);
         if (NB == 1) {
-            build_activation<KQ, P, TP>(p, smem, L, warp, lane, W, p.x_in, act, dpl, xs16);
+            build_activation<KQ, P, TP, 8, KQ>(p, smem, L, warp, lane, W, p.x_in, act, dpl, xs16);
         } else {
             build_activation_pair<P>(p, smem, L, warp, lane, W);
         }
