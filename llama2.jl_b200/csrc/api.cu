@@ -1523,8 +1523,12 @@ extern "C" int32_t l2b_session_create(l2b_model* m, void* stream, l2b_session** 
         }
         s->gq = choose_gq(m->l_heads, m->l_kv);
         // blocks per head group in the attention launches: whole clusters for the decode kernel (L2B_ATTN_SPLITS is rounded up)
+        // Enough clusters for the longest context, but no more blocks than about 1.75 per SM: with many head groups (Phi-3-mini
+        // shape, 32 groups, seq_len 4096) one cluster per group gave 631 tok/s, two 564, four 543.
         {
-            const long want = env_long("L2B_ATTN_SPLITS", decode_splits(c.seq_len));
+            const int groups = m->l_heads / s->gq;
+            const int by_sms = std::max(1, s->di.sms * 7 / 4 / (groups * ATTN_CL));
+            const long want = env_long("L2B_ATTN_SPLITS", std::min(decode_splits(c.seq_len), by_sms * ATTN_CL));
             s->nsplit = (int)std::max<long>(ATTN_CL, std::min<long>(4 * ATTN_CL, (want + ATTN_CL - 1) / ATTN_CL * ATTN_CL));
         }
         const size_t kvl = kv_layer_elems(m);
