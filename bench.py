@@ -227,8 +227,9 @@ def decode_roofline(cfg, wbytes, n_prompt, n_pos, decode_ms, peak, tp=1):
     return algo, achieved, achieved / peak
 
 
-def run_tp_70b(args, pkg, synth, L, torch, dist, world, rank, local, steps, positions=0, layers=0):
-    """The Llama-2-70B shape tensor-parallel over all `world` GPUs (one token stream, strong scaling).  Returns the result dict."""
+def run_tp_70b(args, pkg, synth, L, torch, dist, world, rank, local, steps, positions=0, layers=0, check_single=True):
+    """The Llama-2-70B shape tensor-parallel over all `world` GPUs (one token stream, strong scaling); world == 1: the same
+    shape on one GPU, the base of the strong-scaling curve.  Returns the result dict and the token stream."""
     from llama2_jl_b200 import tp
     spec, wl_name = workload_spec(synth, "70b-tp")
     if layers > 0:
@@ -239,13 +240,15 @@ def run_tp_70b(args, pkg, synth, L, torch, dist, world, rank, local, steps, posi
     # four distinct layers, reused in turn: the full host copy (38.7 GB per rank) would not fit beside the other ranks'
     weights = synth.model_weights(cfg, spec["types"], seed=2024, tied_output=spec["tied"], distinct_layers=4)
     model = pkg.LanguageModel(cfg, None, weights, act_planes=args.act_planes, device=local, tp_size=world, tp_rank=rank)
-    tp.connect(model)
+    if world > 1:
+        tp.connect(model)
     prompt = synth.prompt_tokens(spec, 2024)[:min(n_prompt, n_pos)]
     wbytes = model.weight_bytes_per_token()
 
     def barrier():
         torch.cuda.synchronize()
-        dist.barrier()
+        if world > 1:
+            dist.barrier()
         torch.cuda.synchronize()
     toks, _ = pkg.generate(model, prompt, n_pos)  # warm-up
     barrier()
@@ -255,20 +258,24 @@ def run_tp_70b(args, pkg, synth, L, torch, dist, world, rank, local, steps, posi
         a, b = model.last_phase_ms()
         pm, dm = pm + a, dm + b
     barrier()
-    t = torch.tensor([pm, dm], dtype=torch.float64, device="cuda")
-    dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    pm, dm = float(t[0]), float(t[1])
-    # every rank must have produced the same stream
-    mine = torch.tensor(np.asarray(toks, dtype=np.int64), device="cuda")
-    ref = mine.clone()
-    dist.broadcast(ref, 0)
-    same = torch.tensor([int(torch.equal(mine, ref))], device="cuda")
-    dist.all_reduce(same, op=dist.ReduceOp.MIN)
+    same = True
+    if world > 1:
+        t = torch.tensor([pm, dm], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        pm, dm = float(t[0]), float(t[1])
+        # every rank must have produced the same stream
+        mine = torch.tensor(np.asarray(toks, dtype=np.int64), device="cuda")
+        ref = mine.clone()
+        dist.broadcast(ref, 0)
+        eq = torch.tensor([int(torch.equal(mine, ref))], device="cuda")
+        dist.all_reduce(eq, op=dist.ReduceOp.MIN)
+        same = bool(int(eq[0]))
     peak, kind = measured_peak()
     n_dec = max(n_pos - len(prompt), 0)
     out = {"workload": wl_name + (f" [reduced to {layers} layers]" if layers else "") + (f" [shortened to {n_pos} positions]" if positions else ""),
-           "n_gpus": world, "scaling": "strong", "steps": steps, "tokens_equal_across_ranks": bool(int(same[0])),
-           "bytes_per_token_per_gpu": int(wbytes)}
+           "n_gpus": world, "scaling": "strong", "steps": steps, "bytes_per_token_per_gpu": int(wbytes)}
+    if world > 1:
+        out["tokens_equal_across_ranks"] = same
     if n_dec > 0 and dm > 0:
         _, ach, frac = decode_roofline(cfg, wbytes, len(prompt), n_pos, dm / steps, peak, tp=world)
         out.update({"decode_tok_s": round(n_dec * steps / (dm / 1e3), 2), "ms_per_decode_token": round(dm / steps / n_dec, 4),
@@ -276,6 +283,27 @@ def run_tp_70b(args, pkg, synth, L, torch, dist, world, rank, local, steps, posi
     if pm > 0:
         out["prefill_tok_s"] = round(len(prompt) * steps / (pm / 1e3), 2)
     model.close()
+    del model, weights
+    if world > 1 and check_single:
+        # the same ranks on a 2-layer model of the shape: the tensor-parallel stream against the one-GPU stream of rank 0
+        rspec = synth.scaled(spec, n_layers=2)
+        rcfg = rspec["config"]
+        rw = synth.model_weights(rcfg, rspec["types"], seed=2024, tied_output=rspec["tied"])
+        rprompt = synth.prompt_tokens(rspec, 2024)[:16]
+        tpm = pkg.LanguageModel(rcfg, None, rw, act_planes=args.act_planes, device=local, tp_size=world, tp_rank=rank)
+        tp.connect(tpm)
+        tp_toks, _ = pkg.generate(tpm, rprompt, 48)
+        barrier()
+        tpm.close()
+        eq1 = 1
+        if rank == 0:
+            one = pkg.LanguageModel(rcfg, None, rw, act_planes=args.act_planes, device=local)
+            one_toks, _ = pkg.generate(one, rprompt, 48)
+            one.close()
+            eq1 = int([int(x) for x in one_toks] == [int(x) for x in tp_toks])
+        e = torch.tensor([eq1], device="cuda")
+        dist.broadcast(e, 0)
+        out["tokens_equal_single_gpu"] = {"value": bool(int(e[0])), "how": "2-layer model of the shape, 16 prompt ids + 32 greedy tokens: the %d-rank stream against rank 0 alone" % world}
     return out, [int(x) for x in toks]
 
 
@@ -403,7 +431,8 @@ def run_ours(args):
     else:
         prefill_how = "position by position"
     line = {
-        "metric": METRIC, "value": round(value, 2), "unit": "tok/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "metric": METRIC if args.workload == "8b" else "decode tok/s @%s, batch 1; %% of HBM roofline" % wl_name.split(",")[0],
+        "value": round(value, 2), "unit": "tok/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": round((prompt_ms + decode_ms) / args.steps, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "int8 activation planes x k-quant integers on int8 tensor-core MMAs, f32 accumulate; %d int8 activation plane(s)" % (args.act_planes or 3),
         "data": "synthetic (seeded random weights and token ids)",
@@ -446,10 +475,20 @@ def run_ours(args):
             "kernel": "fused_matvec_kernel", "workload": "q4_K 14336x4096, batch 1, 8 rotating copies (264 MB > L2), back-to-back launches",
             "us_per_launch": round(k_us, 3), "bytes_per_launch": k_bytes, "achieved": round(k_bytes / k_us / 1e3, 1), "unit": "GB/s",
             "frac": round(k_bytes / k_us / 1e3 / peak, 4), "traffic": profiled_traffic("fused_matvec_kernel__q4_K_14336x4096.md")}
+        line["roofline"]["dominant_kernel"] = line["roofline"]["isolated_matvec"]  # (the same measurement under its earlier name)
+        line["roofline"]["traffic"] = line["roofline"]["isolated_matvec"]["traffic"]
+        line["roofline"]["traffic_scope"] = "one launch of the dominant kernel (isolated_matvec), from its ncu summary under profiles/"
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         line["parity"], line["cpu_baseline"] = oracle_check(pkg, synth, spec, model)
     model.close()
     del model, weights
+    if world == 1 and args.workload == "8b" and not args.no_tp and not args.positions and not args.layers:
+        # the base of the tensor-parallel curve: the 70B shape on this one GPU (38.7 GB of weights)
+        try:
+            base, _ = run_tp_70b(args, pkg, synth, L, torch, dist, 1, 0, local, steps=1, positions=args.tp_positions)
+            line["tp_70b_one_gpu"] = base
+        except Exception as e:
+            line["tp_70b_one_gpu"] = {"error": str(e)[:300]}
     if world > 1 and args.workload == "8b" and not args.no_tp:
         # the 70B shape over the same GPUs, tensor parallel: shortened so that the whole run stays within minutes
         try:
@@ -525,7 +564,7 @@ def main():
     ap.add_argument("--prompt-len", type=int, default=0, help="use only this many prompt ids (0 = the workload's prompt; for profiler captures)")
     ap.add_argument("--act-planes", type=int, default=0, help="int8 planes per activation (1..3; 0 = library default 3)")
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the oracle run (parity and cpu_baseline keys)")
-    ap.add_argument("--no-tp", action="store_true", help="with --gpus > 1: skip the tensor-parallel 70B leg")
+    ap.add_argument("--no-tp", action="store_true", help="skip the 70B-shape leg (one GPU: the base figure; several: the tensor-parallel run)")
     ap.add_argument("--tp-positions", type=int, default=576, help="positions of the tensor-parallel 70B leg (512 prompt ids, then decode)")
     ap.add_argument("--positions", type=int, default=0, help="run only this many positions per step (for profiler captures)")
     args = ap.parse_args()

@@ -297,13 +297,27 @@ __device__ __forceinline__ void build_activation(const MvParams& p, uint8_t* sme
             a = __ldcg(reinterpret_cast<const float4*>(x_in + 8 * g));
             b = __ldcg(reinterpret_cast<const float4*>(x_in + 8 * g + 4));
             if (tp_sum) {
+                // rank order on every GPU: identical sums everywhere.  The partial vectors of four ranks are fetched together:
+                // one at a time, every rank would add an L2 round trip to the prologue of every layer.
 #pragma unroll 1
-                for (int r = 0; r < tp_n; ++r) {  // rank order on every GPU: identical sums everywhere
-                    const float* src = part_src + (size_t)r * n + 8 * g;
-                    const float4 pa = __ldcg(reinterpret_cast<const float4*>(src));
-                    const float4 pb = __ldcg(reinterpret_cast<const float4*>(src + 4));
-                    a.x += pa.x; a.y += pa.y; a.z += pa.z; a.w += pa.w;
-                    b.x += pb.x; b.y += pb.y; b.z += pb.z; b.w += pb.w;
+                for (int r0 = 0; r0 < tp_n; r0 += 4) {
+                    float4 pa[4], pb[4];
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        pa[k] = pb[k] = zero4;
+                        if (r0 + k < tp_n) {
+                            const float* src = part_src + (size_t)(r0 + k) * n + 8 * g;
+                            pa[k] = __ldcg(reinterpret_cast<const float4*>(src));
+                            pb[k] = __ldcg(reinterpret_cast<const float4*>(src + 4));
+                        }
+                    }
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        if (r0 + k < tp_n) {
+                            a.x += pa[k].x; a.y += pa[k].y; a.z += pa[k].z; a.w += pa[k].w;
+                            b.x += pb[k].x; b.y += pb[k].y; b.z += pb[k].z; b.w += pb[k].w;
+                        }
+                    }
                 }
                 if (write_back && blockIdx.x == 0) {
                     *reinterpret_cast<float4*>(x_out + 8 * g) = a;
@@ -911,6 +925,11 @@ __global__ void __launch_bounds__((MV_MAX_CONSUMERS + 2) * 32, 1) fused_matvec_k
         // 1/rms of the input vector (deferred by the prologue, NB == 1): worked out from the warps' sums of squares when the first
         // tile arrives, which orders their stores before these loads
         float in_scale = 1.f;
+        // EPI_PUSH: where this GPU's partial vector goes on every GPU, read once (read per tile, each address would cost the
+        // finisher an L2 round trip per rank and tile, in series: the stores of the previous tile may alias the descriptor)
+        float* push_to[MV_MAX_TP];
+#pragma unroll
+        for (int r = 0; r < MV_MAX_TP; ++r) push_to[r] = (TP && p.tp_push && r < p.tp->tp_size) ? p.tp->push_dst[r] : nullptr;
         // lane = 16*q + 8*half + pair: sums the partials of warps w = q, q+2, ... of row `half` of pair `pair`
         const int fq = lane >> 4, fidx = lane & 15;
         const int WGf = W / p.cgroups;  // warps that contribute to one tile
@@ -962,7 +981,22 @@ __global__ void __launch_bounds__((MV_MAX_CONSUMERS + 2) * 32, 1) fused_matvec_k
             v += __shfl_xor_sync(0xffffffffu, v, 16);     // (even warps) + (odd warps)
             if (NB == 1) v *= in_scale;
             const float vB = __shfl_sync(0xffffffffu, v, (lane & 7) + 8);
-            if (mine) epilogue_pair<TP, true>(p, sg, t, v, vB, pos, best, 0, &pre0);
+            if (TP && p.tp_push) {
+                if (mine) {
+#pragma unroll
+                    for (int r = 0; r < MV_MAX_TP; ++r) {
+                        if (push_to[r] == nullptr) continue;
+                        if (pre0.rowB == pre0.rowA + 1 && !(pre0.rowA & 1)) {  // adjacent rows: one 8-byte store
+                            *reinterpret_cast<float2*>(push_to[r] + pre0.rowA) = make_float2(v, vB);
+                        } else {
+                            push_to[r][pre0.rowA] = v;
+                            push_to[r][pre0.rowB] = vB;
+                        }
+                    }
+                }
+            } else if (mine) {
+                epilogue_pair<TP, true>(p, sg, t, v, vB, pos, best, 0, &pre0);
+            }
             if (NB == 2) {  // the second position
                 v1 += __shfl_xor_sync(0xffffffffu, v1, 16);
                 const float v1B = __shfl_sync(0xffffffffu, v1, (lane & 7) + 8);
