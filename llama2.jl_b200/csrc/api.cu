@@ -586,11 +586,11 @@ struct l2b_session {
     unsigned long long* trace = nullptr;  // L2B_TRACE_TOKEN=1: per-launch, per-block timeline stamps (debugging aid)
     unsigned long long* attn_trace = nullptr;  // the same for the decode attention kernel: [layer][1024 blocks][8]
     int trace_launches = 0;
-    // tensor parallelism.  tp_mem = [n_exch][tp][dim] f32 partial vectors, then [n_exch][tp] u32 arrival counters;
+    // tensor parallelism.  tp_mem = [n_exch][tp][dim] partial vectors of {f32, tag} pairs;
     // n_exch = 2 * n_layers (one exchange after wo, one after w2).  Peers write into it through IPC mappings.
     float* x2 = nullptr;          // second buffer of the residual stream (the summing prologue reads one, writes the other)
     uint8_t* tp_mem = nullptr;
-    size_t tp_flag_off = 0, tp_bytes = 0;
+    size_t tp_bytes = 0;
     unsigned* tp_epoch = nullptr;  // tokens completed (device word)
     uint8_t* peer_mem[MV_MAX_TP] = {nullptr};  // [r]: rank r's tp_mem as seen from this process ([rank] = own)
     // many-token prompt pass through the tensor-core GEMM (kq_gemm.cuh): buffers for PF_MAX_TOK tokens, allocated on first use
@@ -1004,9 +1004,9 @@ static int32_t enqueue_token(l2b_session* s, int* nlaunch, int nb = 1) {
     // partial vectors the next rmsnorm prologue has to add (-1: none).
     const int tp = m->tp;
     float* xbuf[2] = {s->x, tp > 1 ? s->x2 : s->x};
-    int cur = 0, pending = -1, push_grid = 0;
-    auto xchg_vec = [&](uint8_t* base, int e, int r) { return reinterpret_cast<float*>(base) + ((size_t)e * tp + r) * c.dim; };
-    auto xchg_flag = [&](uint8_t* base, int e, int r) { return reinterpret_cast<unsigned*>(base + s->tp_flag_off) + (size_t)e * tp + r; };
+    int cur = 0, pending = -1;
+    // (every value of a partial vector travels as 8 bytes {f32 bits, token tag}: 2 * dim floats per vector)
+    auto xchg_vec = [&](uint8_t* base, int e, int r) { return reinterpret_cast<float*>(base) + ((size_t)e * tp + r) * c.dim * 2; };
     // rmsnorm prologue over the residual stream; with an exchange pending it first forms x + sum of the partial vectors
     // descriptors live in device memory; their contents are uploaded after the capture (capture_token_graph)
     auto new_desc = [&](MvLaunch& L) -> MvTp& {
@@ -1024,9 +1024,7 @@ static int32_t enqueue_token(l2b_session* s, int* nlaunch, int nb = 1) {
         if (pending >= 0) {
             MvTp& d = new_desc(L);
             d.part_src = xchg_vec(s->tp_mem, pending, 0);
-            d.part_flag = xchg_flag(s->tp_mem, pending, 0);
             d.tp_epoch = s->tp_epoch;
-            d.part_blocks = (unsigned)push_grid;
             d.tp_timeout_ms = (unsigned)env_long("L2B_TP_TIMEOUT_MS", 10000);
             d.x_out = xbuf[cur ^ 1];
         }
@@ -1048,9 +1046,10 @@ static int32_t enqueue_token(l2b_session* s, int* nlaunch, int nb = 1) {
         L.kb = w.kb;
         L.p.tp_push = 1;
         MvTp& d = new_desc(L);
+        d.tp_epoch = s->tp_epoch;  // the pushed values carry the token's number as their tag
+        d.tp_timeout_ms = (unsigned)env_long("L2B_TP_TIMEOUT_MS", 10000);
         for (int r = 0; r < tp; ++r) {
             d.push_dst[r] = xchg_vec(s->peer_mem[r], e, m->rank);
-            d.push_flag[r] = xchg_flag(s->peer_mem[r], e, m->rank);
         }
     };
     const int rope_mode = c.rope_is_neox ? PAIR_NEOX : PAIR_ADJACENT;
@@ -1119,7 +1118,7 @@ static int32_t enqueue_token(l2b_session* s, int* nlaunch, int nb = 1) {
             L.p.pro = PRO_COPY;
             L.p.x_in = s->att;
             L2B_TRY(mv(L));
-            if (tp > 1) pending = 2 * l, push_grid = last_grid;
+            if (tp > 1) pending = 2 * l;
         }
         // --- ffn rmsnorm + gate/up + SwiGLU (inference.jl:287-299)
         {
@@ -1144,7 +1143,7 @@ static int32_t enqueue_token(l2b_session* s, int* nlaunch, int nb = 1) {
             L.p.pro = PRO_COPY;
             L.p.x_in = s->hb;
             L2B_TRY(mv(L));
-            if (tp > 1) pending = 2 * l + 1, push_grid = last_grid;
+            if (tp > 1) pending = 2 * l + 1;
         }
     }
     if (nb == 2) {  // both positions are followed by prompt tokens: no classifier, no sampling, move on by two
@@ -1581,8 +1580,7 @@ extern "C" int32_t l2b_session_create(l2b_model* m, void* stream, l2b_session** 
         if (m->tp > 1) {
             // exchange memory; the token graph is captured by l2b_session_tp_connect, once the peers' mappings exist
             const size_t n_exch = 2 * (size_t)c.n_layers;
-            s->tp_flag_off = n_exch * m->tp * c.dim * 4;
-            s->tp_bytes = s->tp_flag_off + n_exch * m->tp * 4;
+            s->tp_bytes = n_exch * m->tp * c.dim * 8;
             CU(cudaMalloc(&s->tp_mem, s->tp_bytes));
             CU(cudaMemset(s->tp_mem, 0, s->tp_bytes));
             CU(cudaMalloc(&s->x2, (size_t)c.dim * 4));

@@ -87,6 +87,20 @@ __device__ __forceinline__ bool mbar_wait_bounded_ns(uint64_t* bar, uint32_t par
     }
 }
 
+// Volatile vector accesses for words that another GPU writes or reads while this kernel runs (tensor-parallel exchange):
+// each 8-byte half {value, tag} of a 16-byte access is written and read as a unit, so a value is valid when its tag is.
+__device__ __forceinline__ uint4 ld_volatile_u32x4(const uint4* p) {
+    uint4 v;
+    asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_volatile_u32x4(uint4* p, uint4 v) {
+    asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+__device__ __forceinline__ void st_volatile_u32x2(uint2* p, uint2 v) {
+    asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(v.x), "r"(v.y) : "memory");
+}
+
 // L2 policy for weight bytes: they are read once per token, so they should not evict the
 // activations and KV cache that live in L2 between kernels.
 __device__ __forceinline__ uint64_t policy_evict_first() {

@@ -40,9 +40,10 @@ enum : int { PRO_COPY = 0, PRO_RMSNORM = 1 };
 enum : int { EPI_STORE = 0, EPI_RESIDUAL = 1, EPI_SWIGLU = 2, EPI_ROPE_Q = 3, EPI_ROPE_K = 4, EPI_STORE_V = 5, EPI_LOGITS = 6, EPI_PUSH = 7 };
 // Tensor parallelism (no counterpart in the reference): a row-split matrix (wo, w2) yields a PARTIAL output vector
 // per GPU.  EPI_PUSH writes this GPU's partial vector into every GPU's exchange buffer with plain stores over
-// NVLink and, when a block has written all its rows, bumps an arrival counter on every GPU.  The next kernel's
-// rmsnorm prologue waits (bounded) until every GPU's counter has reached this token's value and then forms
-// x_new = x + sum_r partial_r in rank order, so that all GPUs hold bit-identical residual streams.
+// NVLink, every value as 8 bytes {f32 bits, tag} with tag = the token's number + 1.  The next kernel's rmsnorm
+// prologue reads those words until their tags are this token's (bounded by a time-out) and forms
+// x_new = x + sum_r partial_r in rank order, so that all GPUs hold bit-identical residual streams.  No fence,
+// arrival counter or separate wait is involved: a value is there when its tag is.
 constexpr int MV_MAX_TP = 8;
 // How the 8 row pairs (A, B) of a tile map to matrix rows.  Pair j of a tile occupies tile rows j and j+8.
 //   ADJACENT: rows (2t, 2t+1)            -- plain outputs and interleaved RoPE pairs
@@ -83,12 +84,9 @@ struct MvSegment {
 // What a tensor-parallel launch needs to know about the other GPUs.
 struct MvTp {
     int tp_size;
-    unsigned part_blocks;                 // blocks of the pushing launch (arrivals per GPU and token)
     unsigned tp_timeout_ms;               // bound on the wait for the other GPUs
-    float* push_dst[8];                   // [r]: where this GPU's partial vector lives in GPU r's exchange buffer
-    unsigned* push_flag[8];               // [r]: this GPU's arrival counter in GPU r's memory
-    const float* part_src;                // prologue: partial vectors [tp_size][n_in] in this GPU's exchange buffer, or null
-    const unsigned* part_flag;            // prologue: arrival counters [tp_size] in this GPU's memory
+    float* push_dst[8];                   // [r]: where this GPU's partial vector lives in GPU r's exchange buffer ({value, tag} pairs)
+    const float* part_src;                // prologue: partial vectors [tp_size][n_in] of {value, tag} pairs in this GPU's exchange buffer, or null
     const unsigned* tp_epoch;             // tokens completed so far (device word, advanced once per token)
     float* x_out;                         // prologue: block 0 writes x_new here (the residual stream is double-buffered)
 };
@@ -255,7 +253,7 @@ __device__ __noinline__ void quantise_block(float4 va, float4 vb, int lane, uint
 // the square root and a second pass over the scales leave the critical path between "previous kernel done" and "first tile".
 template <bool KQ, int P, bool TP = false, int ZHI = 8, bool DEFER = false>
 __device__ __forceinline__ void build_activation(const MvParams& p, uint8_t* smem, const MvSmem& L, int warp, int lane, int nwarps, const float* x_in,
-                                                 uint8_t* act, float* dpl, float* xs16) {
+                                                 uint8_t* act, float* dpl, float* xs16, unsigned tp_epoch = 0) {
     const int n = p.n_in;
     float* red = reinterpret_cast<float*>(smem + L.off_red);
     float* xf = reinterpret_cast<float*>(smem + L.off_xf);
@@ -269,26 +267,6 @@ __device__ __forceinline__ void build_activation(const MvParams& p, uint8_t* sme
     const int tp_n = tp_sum ? T->tp_size : 0;
     const float* part_src = tp_sum ? T->part_src : nullptr;
     float* x_out = tp_sum ? T->x_out : nullptr;
-    if (tp_sum) {
-        // one lane per GPU waits until that GPU's partial vector of this token has arrived in full
-        if (warp == 0 && lane < tp_n && __ldcg(p.status) == DEV_OK) {
-            const unsigned want = (__ldcg(T->tp_epoch) + 1u) * T->part_blocks;
-            const unsigned long long t0 = global_ns(), limit = (unsigned long long)T->tp_timeout_ms * 1000000ull;
-            bool ok = false;
-            for (;;) {
-                unsigned have;
-                asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(have) : "l"(T->part_flag + lane) : "memory");
-                if ((int)(have - want) >= 0) {
-                    ok = true;
-                    break;
-                }
-                if (global_ns() - t0 > limit) break;
-                __nanosleep(200);
-            }
-            if (!ok) atomicExch(p.status, DEV_ERR_PEER_TIMEOUT);
-        }
-        consumer_sync(nwarps * 32);
-    }
     // write_back: block 0 stores the summed residual stream (first pass over the vector only)
     auto fetch = [&](int turn, float4& a, float4& b, bool write_back = false) {
         const int g = group_of(turn);
@@ -297,27 +275,36 @@ __device__ __forceinline__ void build_activation(const MvParams& p, uint8_t* sme
             a = __ldcg(reinterpret_cast<const float4*>(x_in + 8 * g));
             b = __ldcg(reinterpret_cast<const float4*>(x_in + 8 * g + 4));
             if (tp_sum) {
-                // rank order on every GPU: identical sums everywhere.  The partial vectors of four ranks are fetched together:
-                // one at a time, every rank would add an L2 round trip to the prologue of every layer.
+                // Every value of a partial vector arrives as 8 bytes {f32 bits, tag}, tag = this token's number + 1, written by the
+                // pushing GPU's finisher warps with 16-byte stores (two values).  A value is there when its tag is: no fence, no
+                // arrival counter, no separate wait; each thread polls exactly what it is about to add (bounded by tp_timeout_ms).
+                // Rank order on every GPU: identical sums everywhere.
+                const unsigned want = tp_epoch + 1u;
+                const uint2* part2 = reinterpret_cast<const uint2*>(part_src);
 #pragma unroll 1
-                for (int r0 = 0; r0 < tp_n; r0 += 4) {
-                    float4 pa[4], pb[4];
-#pragma unroll
-                    for (int k = 0; k < 4; ++k) {
-                        pa[k] = pb[k] = zero4;
-                        if (r0 + k < tp_n) {
-                            const float* src = part_src + (size_t)(r0 + k) * n + 8 * g;
-                            pa[k] = __ldcg(reinterpret_cast<const float4*>(src));
-                            pb[k] = __ldcg(reinterpret_cast<const float4*>(src + 4));
+                for (int r = 0; r < tp_n; ++r) {
+                    const uint4* src = reinterpret_cast<const uint4*>(part2 + (size_t)r * n + 8 * g);
+                    uint4 q0, q1, q2, q3;
+                    unsigned long long t0 = 0;
+                    for (unsigned spins = 0;; ++spins) {
+                        q0 = ld_volatile_u32x4(src);
+                        q1 = ld_volatile_u32x4(src + 1);
+                        q2 = ld_volatile_u32x4(src + 2);
+                        q3 = ld_volatile_u32x4(src + 3);
+                        const bool ok = q0.y == want && q0.w == want && q1.y == want && q1.w == want && q2.y == want && q2.w == want && q3.y == want && q3.w == want;
+                        if (ok) break;
+                        if ((spins & 63u) == 63u) {  // not yet: look at the clock and at the status word now and then
+                            const unsigned long long now = global_ns();
+                            if (t0 == 0) t0 = now;
+                            if (now - t0 > (unsigned long long)T->tp_timeout_ms * 1000000ull) {
+                                atomicExch(p.status, DEV_ERR_PEER_TIMEOUT);
+                                break;
+                            }
+                            if (__ldcg(p.status) != DEV_OK) break;  // somebody has given up already: the token is lost
                         }
                     }
-#pragma unroll
-                    for (int k = 0; k < 4; ++k) {
-                        if (r0 + k < tp_n) {
-                            a.x += pa[k].x; a.y += pa[k].y; a.z += pa[k].z; a.w += pa[k].w;
-                            b.x += pb[k].x; b.y += pb[k].y; b.z += pb[k].z; b.w += pb[k].w;
-                        }
-                    }
+                    a.x += __uint_as_float(q0.x); a.y += __uint_as_float(q0.z); a.z += __uint_as_float(q1.x); a.w += __uint_as_float(q1.z);
+                    b.x += __uint_as_float(q2.x); b.y += __uint_as_float(q2.z); b.z += __uint_as_float(q3.x); b.w += __uint_as_float(q3.z);
                 }
                 if (write_back && blockIdx.x == 0) {
                     *reinterpret_cast<float4*>(x_out + 8 * g) = a;
@@ -930,6 +917,7 @@ __global__ void __launch_bounds__((MV_MAX_CONSUMERS + 2) * 32, 1) fused_matvec_k
         float* push_to[MV_MAX_TP];
 #pragma unroll
         for (int r = 0; r < MV_MAX_TP; ++r) push_to[r] = (TP && p.tp_push && r < p.tp->tp_size) ? p.tp->push_dst[r] : nullptr;
+        const unsigned push_tag = (TP && p.tp_push) ? __ldcg(p.tp->tp_epoch) + 1u : 0u;  // this token's number + 1 (see the summing prologue)
         // lane = 16*q + 8*half + pair: sums the partials of warps w = q, q+2, ... of row `half` of pair `pair`
         const int fq = lane >> 4, fidx = lane & 15;
         const int WGf = W / p.cgroups;  // warps that contribute to one tile
@@ -986,11 +974,12 @@ __global__ void __launch_bounds__((MV_MAX_CONSUMERS + 2) * 32, 1) fused_matvec_k
 #pragma unroll
                     for (int r = 0; r < MV_MAX_TP; ++r) {
                         if (push_to[r] == nullptr) continue;
-                        if (pre0.rowB == pre0.rowA + 1 && !(pre0.rowA & 1)) {  // adjacent rows: one 8-byte store
-                            *reinterpret_cast<float2*>(push_to[r] + pre0.rowA) = make_float2(v, vB);
+                        uint2* dst2 = reinterpret_cast<uint2*>(push_to[r]);  // {value, tag} pairs
+                        if (pre0.rowB == pre0.rowA + 1 && !(pre0.rowA & 1)) {  // adjacent rows: one 16-byte store
+                            st_volatile_u32x4(reinterpret_cast<uint4*>(dst2 + pre0.rowA), make_uint4(__float_as_uint(v), push_tag, __float_as_uint(vB), push_tag));
                         } else {
-                            push_to[r][pre0.rowA] = v;
-                            push_to[r][pre0.rowB] = vB;
+                            st_volatile_u32x2(dst2 + pre0.rowA, make_uint2(__float_as_uint(v), push_tag));
+                            st_volatile_u32x2(dst2 + pre0.rowB, make_uint2(__float_as_uint(vB), push_tag));
                         }
                     }
                 }
@@ -1008,11 +997,6 @@ __global__ void __launch_bounds__((MV_MAX_CONSUMERS + 2) * 32, 1) fused_matvec_k
             }
         }
         if (dead && lane == 0) atomicExch(p.status, DEV_ERR_TMA_TIMEOUT);
-        if (TP && p.tp_push) {  // every row of this block is on its way: tell each GPU (blocks without rows report too)
-            __threadfence_system();
-            __syncwarp();
-            if (lane < p.tp->tp_size) atomicAdd_system(p.tp->push_flag[lane], 1u);
-        }
         if (p.amax_val) {  // EPI_LOGITS: first maximal index over this block's rows
             for (int o = 16; o > 0; o >>= 1) {
                 const float ov = __shfl_xor_sync(0xffffffffu, best.v, o);
@@ -1031,6 +1015,10 @@ __global__ void __launch_bounds__((MV_MAX_CONSUMERS + 2) * 32, 1) fused_matvec_k
     // ================================ consumer warps ============================================
     // Weights are constants; everything below reads what the previous kernel wrote.
     pdl_launch_dependents();
+    // The exchange descriptor and the token count do not change during a token (the count advances in the token's last
+    // kernel): fetched now, behind the previous kernel's tail, instead of as two dependent round trips after the wait.
+    unsigned tp_epoch = 0;
+    if (TP && p.tp && p.tp->part_src != nullptr) tp_epoch = __ldcg(p.tp->tp_epoch);
     pdl_wait();
     MV_TRACE(2);
 
@@ -1039,7 +1027,7 @@ __global__ void __launch_bounds__((MV_MAX_CONSUMERS + 2) * 32, 1) fused_matvec_k
         float* dpl = reinterpret_cast<float*>(smem + L.off_dpl);
         float* xs16 = reinterpret_cast<float*>(smem + L.off_xs);
         if (NB == 1) {
-            build_activation<KQ, P, TP, 8, KQ>(p, smem, L, warp, lane, W, p.x_in, act, dpl, xs16);
+            build_activation<KQ, P, TP, 8, KQ>(p, smem, L, warp, lane, W, p.x_in, act, dpl, xs16, tp_epoch);
         } else {
             build_activation_pair<P>(p, smem, L, warp, lane, W);
         }

@@ -264,7 +264,14 @@ __device__ __forceinline__ void tile_q6k(const uint8_t* rA, const uint8_t* rB, f
     const uint4 sA4 = *reinterpret_cast<const uint4*>(rA + 192);
     const uint4 sB4 = *reinterpret_cast<const uint4*>(rB + 192);
     const uint32_t scwA[4] = {sA4.x, sA4.y, sA4.z, sA4.w}, scwB[4] = {sB4.x, sB4.y, sB4.z, sB4.w};
-    auto sc_of = [](const uint32_t (&w)[4], int is) -> int { return ((int)(w[is >> 2] << (24 - 8 * (is & 3)))) >> 24; };
+    // int8 scale number `is`, sign-extended by one byte permute (selector nibble 8 + i replicates the sign bit of byte i)
+    // (prmt in PTX: the __byte_perm intrinsic ignores the sign-replication bit of a selector nibble)
+    auto sc_of = [](const uint32_t (&w)[4], int is) -> int {
+        const unsigned i = (unsigned)(is & 3), sgn = 8u + i;
+        int r;
+        asm("prmt.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(w[is >> 2]), "r"(0u), "r"((sgn << 12) | (sgn << 8) | (sgn << 4) | i));
+        return r;
+    };
     const uint8_t* ap = x.act + 256 * b + 4 * x.t;
     int S[4] = {0, 0, 0, 0};
 #pragma unroll
