@@ -315,33 +315,16 @@ __device__ __forceinline__ void attention_decode_body(const AttnParams& p) {
     const float* vbase = p.vc + (size_t)kvh * p.seq_len * hs;
     const int tb0 = t0 + warp * ATTN_UNROLL;
 
-    // Two batches per warp are fetched ahead of the wait (a cluster covers 512 positions that way); the position the previous
-    // kernel is writing (npos - 1) is left out and fetched after the wait.
-    constexpr int STRIDE = ATTN_DW * ATTN_UNROLL;
-    float4 kkA[ATTN_UNROLL], vvA[ATTN_UNROLL], kkB[ATTN_UNROLL], vvB[ATTN_UNROLL];
-    auto fetch = [&](float4 (&kk)[ATTN_UNROLL], float4 (&vv)[ATTN_UNROLL], int tb, int limit) {  // positions tb .. tb+3 below `limit`
+    float4 kk[ATTN_UNROLL], vv[ATTN_UNROLL];
 #pragma unroll
-        for (int u = 0; u < ATTN_UNROLL; ++u) {
-            kk[u] = vv[u] = zero4;
-            const int t = tb + u;
-            if (lane_active && t < t1 && t < limit) {
-                kk[u] = __ldcg(reinterpret_cast<const float4*>(kbase + (size_t)t * hs) + lane);
-                vv[u] = __ldcg(reinterpret_cast<const float4*>(vbase + (size_t)t * hs) + lane);
-            }
+    for (int u = 0; u < ATTN_UNROLL; ++u) {
+        kk[u] = vv[u] = zero4;
+        const int t = tb0 + u;
+        if (lane_active && t < t1 && t < npos - 1) {
+            kk[u] = __ldcg(reinterpret_cast<const float4*>(kbase + (size_t)t * hs) + lane);
+            vv[u] = __ldcg(reinterpret_cast<const float4*>(vbase + (size_t)t * hs) + lane);
         }
-    };
-    auto fetch_newest = [&](float4 (&kk)[ATTN_UNROLL], float4 (&vv)[ATTN_UNROLL], int tb) {  // npos - 1, if it is in this batch
-#pragma unroll
-        for (int u = 0; u < ATTN_UNROLL; ++u) {
-            const int t = tb + u;
-            if (lane_active && t < t1 && t == npos - 1) {
-                kk[u] = __ldcg(reinterpret_cast<const float4*>(kbase + (size_t)t * hs) + lane);
-                vv[u] = __ldcg(reinterpret_cast<const float4*>(vbase + (size_t)t * hs) + lane);
-            }
-        }
-    };
-    fetch(kkA, vvA, tb0, npos - 1);
-    fetch(kkB, vvB, tb0 + STRIDE, npos - 1);
+    }
     if (PDL) pdl_wait();
     ATTN_TRACE(1);
     float4 qv[GQ], acc[GQ];
@@ -353,10 +336,25 @@ __device__ __forceinline__ void attention_decode_body(const AttnParams& p) {
         m[g] = -INFINITY;
         l[g] = 0.f;
     }
-    fetch_newest(kkA, vvA, tb0);
-    fetch_newest(kkB, vvB, tb0 + STRIDE);
-    // one batch of ATTN_UNROLL positions starting at tb (the batch's first position is in range)
-    auto score = [&](const float4 (&kk)[ATTN_UNROLL], const float4 (&vv)[ATTN_UNROLL], int tb) {
+#pragma unroll
+    for (int u = 0; u < ATTN_UNROLL; ++u) {  // the position the previous kernel has just written, if it is in this batch
+        const int t = tb0 + u;
+        if (lane_active && t < t1 && t == npos - 1) {
+            kk[u] = __ldcg(reinterpret_cast<const float4*>(kbase + (size_t)t * hs) + lane);
+            vv[u] = __ldcg(reinterpret_cast<const float4*>(vbase + (size_t)t * hs) + lane);
+        }
+    }
+    for (int tb = tb0; tb < t1; tb += ATTN_DW * ATTN_UNROLL) {
+        if (tb != tb0) {
+#pragma unroll
+            for (int u = 0; u < ATTN_UNROLL; ++u) {
+                kk[u] = vv[u] = zero4;
+                if (lane_active && tb + u < t1) {
+                    kk[u] = __ldcg(reinterpret_cast<const float4*>(kbase + (size_t)(tb + u) * hs) + lane);
+                    vv[u] = __ldcg(reinterpret_cast<const float4*>(vbase + (size_t)(tb + u) * hs) + lane);
+                }
+            }
+        }
         float s[ATTN_UNROLL][GQ];
 #pragma unroll
         for (int u = 0; u < ATTN_UNROLL; ++u)
@@ -400,14 +398,6 @@ __device__ __forceinline__ void attention_decode_body(const AttnParams& p) {
             acc[g].w = fmaf(acc[g].w, corr, pv.w);
             m[g] = mx;
         }
-    };
-    for (int tb = tb0; tb < t1; tb += 2 * STRIDE) {
-        if (tb != tb0) {  // (beyond the two batches fetched ahead: long contexts)
-            fetch(kkA, vvA, tb, npos);
-            fetch(kkB, vvB, tb + STRIDE, npos);
-        }
-        score(kkA, vvA, tb);
-        if (tb + STRIDE < t1) score(kkB, vvB, tb + STRIDE);
     }
     ATTN_TRACE(2);
 
