@@ -256,9 +256,10 @@ __device__ __forceinline__ void attention_split_body(const AttnParams& p) {
 //    then folded into the running softmax with one maximum and one set of exponentials per batch.
 //  * The blocks of a cluster merge through distributed shared memory: every block reduces its warps in its own shared memory
 //    and stores each part of the result into the shared memory of the block that finishes that part of the output; one
-//    cluster barrier later every block combines what it received and writes its slice.  Up to ATTN_CL * ATTN_DW * ATTN_UNROLL
-//    = 256 positions need no global scratch, fence or atomic at all.  Longer contexts use more clusters per head group; those
-//    exchange one partial result per cluster through scratch memory and a ticket.
+//    cluster barrier later every block combines what it received and writes its slice.  A launch with one cluster per head
+//    group (the host's choice up to 512 positions), and any launch up to ATTN_CL * ATTN_DW * ATTN_UNROLL = 256 positions, needs
+//    no global scratch, fence or atomic at all.  Beyond that the clusters of a head group exchange one partial result per
+//    cluster through scratch memory and a ticket.
 constexpr int ATTN_CL = 8;  // blocks per cluster (the portable maximum)
 constexpr int ATTN_DW = 8;  // warps per block
 constexpr int ATTN_CLUSTER_POS = ATTN_CL * ATTN_DW * ATTN_UNROLL;  // positions a cluster takes in one batch per warp
