@@ -109,8 +109,7 @@ __device__ __forceinline__ void attention_merge(const AttnParams& p, const float
     }
     if (active == 1) return;
     // The last block of this head group merges the splits.  One thread per block publishes: the barrier orders the block's
-    // partial results before its fence, and fences are cumulative, so the 127 other fences (about a microsecond of waiting
-    // each, all on the critical path of a token) are not needed.
+    // partial results before its fence, and fences are cumulative, so the other threads need none.
     __syncthreads();
     if (threadIdx.x == 0) {
         __threadfence();
