@@ -278,20 +278,28 @@ __device__ __forceinline__ void build_activation(const MvParams& p, uint8_t* sme
                 // Every value of a partial vector arrives as 8 bytes {f32 bits, tag}, tag = this token's number + 1, written by the
                 // pushing GPU's finisher warps with 16-byte stores (two values).  A value is there when its tag is: no fence, no
                 // arrival counter, no separate wait; each thread polls exactly what it is about to add (bounded by tp_timeout_ms).
-                // Rank order on every GPU: identical sums everywhere.
+                // Two ranks' words are in flight together (one L2 round trip per pair of ranks instead of per rank); the sums
+                // are formed in rank order on every GPU: identical bits everywhere.
                 const unsigned want = tp_epoch + 1u;
                 const uint2* part2 = reinterpret_cast<const uint2*>(part_src);
 #pragma unroll 1
-                for (int r = 0; r < tp_n; ++r) {
-                    const uint4* src = reinterpret_cast<const uint4*>(part2 + (size_t)r * n + 8 * g);
-                    uint4 q0, q1, q2, q3;
+                for (int r = 0; r < tp_n; r += 2) {
+                    const bool two = r + 1 < tp_n;
+                    const uint4* src0 = reinterpret_cast<const uint4*>(part2 + (size_t)r * n + 8 * g);
+                    const uint4* src1 = reinterpret_cast<const uint4*>(part2 + (size_t)(two ? r + 1 : r) * n + 8 * g);
+                    uint4 q0, q1, q2, q3, u0, u1, u2, u3;
                     unsigned long long t0 = 0;
                     for (unsigned spins = 0;; ++spins) {
-                        q0 = ld_volatile_u32x4(src);
-                        q1 = ld_volatile_u32x4(src + 1);
-                        q2 = ld_volatile_u32x4(src + 2);
-                        q3 = ld_volatile_u32x4(src + 3);
-                        const bool ok = q0.y == want && q0.w == want && q1.y == want && q1.w == want && q2.y == want && q2.w == want && q3.y == want && q3.w == want;
+                        q0 = ld_volatile_u32x4(src0);
+                        q1 = ld_volatile_u32x4(src0 + 1);
+                        q2 = ld_volatile_u32x4(src0 + 2);
+                        q3 = ld_volatile_u32x4(src0 + 3);
+                        u0 = ld_volatile_u32x4(src1);
+                        u1 = ld_volatile_u32x4(src1 + 1);
+                        u2 = ld_volatile_u32x4(src1 + 2);
+                        u3 = ld_volatile_u32x4(src1 + 3);
+                        const bool ok = q0.y == want && q0.w == want && q1.y == want && q1.w == want && q2.y == want && q2.w == want && q3.y == want && q3.w == want &&
+                                        u0.y == want && u0.w == want && u1.y == want && u1.w == want && u2.y == want && u2.w == want && u3.y == want && u3.w == want;
                         if (ok) break;
                         if ((spins & 63u) == 63u) {  // not yet: look at the clock and at the status word now and then
                             const unsigned long long now = global_ns();
@@ -305,6 +313,10 @@ __device__ __forceinline__ void build_activation(const MvParams& p, uint8_t* sme
                     }
                     a.x += __uint_as_float(q0.x); a.y += __uint_as_float(q0.z); a.z += __uint_as_float(q1.x); a.w += __uint_as_float(q1.z);
                     b.x += __uint_as_float(q2.x); b.y += __uint_as_float(q2.z); b.z += __uint_as_float(q3.x); b.w += __uint_as_float(q3.z);
+                    if (two) {
+                        a.x += __uint_as_float(u0.x); a.y += __uint_as_float(u0.z); a.z += __uint_as_float(u1.x); a.w += __uint_as_float(u1.z);
+                        b.x += __uint_as_float(u2.x); b.y += __uint_as_float(u2.z); b.z += __uint_as_float(u3.x); b.w += __uint_as_float(u3.z);
+                    }
                 }
                 if (write_back && blockIdx.x == 0) {
                     *reinterpret_cast<float4*>(x_out + 8 * g) = a;
