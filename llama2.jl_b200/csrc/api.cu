@@ -942,7 +942,7 @@ static void session_free(l2b_session* s) {
     if (s->graph) cudaGraphExecDestroy(s->graph);
     if (s->graph2) cudaGraphExecDestroy(s->graph2);
     void* bufs[] = {s->x, s->q, s->att, s->tickets, s->hb, s->logits, s->kc, s->vc, s->part_m, s->part_l, s->part_acc, s->amax_val, s->amax_idx,
-                    s->rope_cs, s->ctl, s->status, s->prompt, s->out_tokens, s->next_token};
+                    s->rope_cs, s->ctl, s->prompt, s->out_tokens, s->next_token};  // (status lives behind next_token)
     for (void* b : bufs)
         if (b) cudaFree(b);
     if (s->trace) cudaFree(s->trace);
@@ -1550,10 +1550,10 @@ extern "C" int32_t l2b_session_create(l2b_model* m, void* stream, l2b_session** 
         CU(cudaMalloc(&s->amax_val, (size_t)s->di.sms * 4));
         CU(cudaMalloc(&s->amax_idx, (size_t)s->di.sms * 4));
         CU(cudaMalloc(&s->ctl, sizeof(Control)));
-        CU(cudaMalloc(&s->status, 4));
+        CU(cudaMalloc(&s->next_token, 8));  // next token and status word side by side: one copy brings both back
+        s->status = s->next_token + 1;
         CU(cudaMalloc(&s->prompt, (size_t)c.seq_len * 4));
         CU(cudaMalloc(&s->out_tokens, (size_t)c.seq_len * 4));
-        CU(cudaMalloc(&s->next_token, 4));
         CU(cudaMallocHost(&s->h_ctl, sizeof(Control)));
         CU(cudaMallocHost(&s->h_small, 16));
         CU(cudaEventCreate(&s->ev0));
@@ -1694,8 +1694,7 @@ static int32_t run_one(l2b_session* s, int token, int pos, float temperature, do
     CU(cudaMemcpyAsync(s->ctl, s->h_ctl, sizeof(Control), cudaMemcpyHostToDevice, s->stream));
     CU(cudaGraphLaunch(s->graph, s->stream));
     s->last_launches = s->kernels_per_token;
-    CU(cudaMemcpyAsync(&s->h_small[0], s->next_token, 4, cudaMemcpyDeviceToHost, s->stream));
-    CU(cudaMemcpyAsync(&s->h_small[1], s->status, 4, cudaMemcpyDeviceToHost, s->stream));
+    CU(cudaMemcpyAsync(&s->h_small[0], s->next_token, 8, cudaMemcpyDeviceToHost, s->stream));  // [0] next token, [1] status
     CU(cudaEventRecord(s->ev1, s->stream));
     CU(cudaStreamSynchronize(s->stream));
     CU(cudaEventElapsedTime(&s->last_ms, s->ev0, s->ev1));
