@@ -85,7 +85,7 @@ __device__ __forceinline__ void attention_merge(const AttnParams& p, const float
         float4 a = zero4;
 #pragma unroll
         for (int w = 0; w < ATTN_WARPS; ++w) {
-            const float wgt = (sm[w][g] == -INFINITY) ? 0.f : expf(sm[w][g] - M);
+            const float wgt = (sm[w][g] == -INFINITY) ? 0.f : exp2f(sm[w][g] - M);
             Ls = fmaf(sl[w][g], wgt, Ls);
             const float4 b = sacc[w][g][lane];
             a.x = fmaf(b.x, wgt, a.x);
@@ -96,7 +96,8 @@ __device__ __forceinline__ void attention_merge(const AttnParams& p, const float
         const int h = hg * GQ + g;
         if (active == 1) {  // nothing to merge across blocks
             if (lane_active) {
-                a.x /= Ls; a.y /= Ls; a.z /= Ls; a.w /= Ls;
+                const float inv = __frcp_rn(Ls);
+                a.x *= inv; a.y *= inv; a.z *= inv; a.w *= inv;
                 reinterpret_cast<float4*>(obase + (size_t)h * hs)[lane] = a;
             }
         } else {
@@ -141,7 +142,7 @@ __device__ __forceinline__ void attention_merge(const AttnParams& p, const float
         const float ms = lane < active ? __ldcg(pm + lane) : -INFINITY;
         const float ls = lane < active ? __ldcg(pl + lane) : 0.f;
         const float M = warp_max(ms);
-        const float wgt = (ms == -INFINITY) ? 0.f : expf(ms - M);
+        const float wgt = (ms == -INFINITY) ? 0.f : exp2f(ms - M);
         const float Ls = warp_sum(ls * wgt);
         float4 a = zero4;
         for (int s0 = 0; s0 < active; s0 += ATTN_MERGE_BATCH) {
@@ -158,7 +159,8 @@ __device__ __forceinline__ void attention_merge(const AttnParams& p, const float
             }
         }
         if (lane_active) {
-            a.x /= Ls; a.y /= Ls; a.z /= Ls; a.w /= Ls;
+            const float inv = __frcp_rn(Ls);
+            a.x *= inv; a.y *= inv; a.z *= inv; a.w *= inv;
             reinterpret_cast<float4*>(obase + (size_t)h * hs)[lane] = a;
         }
     }
@@ -192,7 +194,9 @@ __device__ __forceinline__ void attention_split_body(const AttnParams& p) {
     const int t0 = sp * chunk, t1 = min(npos, t0 + chunk);
     const int hs = p.hs;
     const bool lane_active = 4 * lane < hs;  // lane owns elements 4*lane .. 4*lane+3 of the head
-    const float div = sqrtf((float)hs);
+    // scores carry the factor log2(e) / sqrt(head_size) and the softmax uses exp2, as in the decode kernel: a division and two
+    // natural exponentials per position and head are most of this loop's instructions otherwise
+    const float scale2 = 1.4426950408889634f / sqrtf((float)hs);
     const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
 
     float4 qv[GQ], acc[GQ];
@@ -228,10 +232,10 @@ __device__ __forceinline__ void attention_split_body(const AttnParams& p) {
                     s = fmaf(qv[g].z, kk[u].z, s);
                     s = fmaf(qv[g].w, kk[u].w, s);
                     s = warp_sum(s);
-                    s = s / div;  // att ./= sqrt(Float32(head_size))
+                    s = s * scale2;  // att ./= sqrt(Float32(head_size)), in the log2 domain
                     const float mn = fmaxf(m[g], s);
-                    const float corr = expf(m[g] - mn);  // 0 on the first position (m = -inf)
-                    const float pr = expf(s - mn);
+                    const float corr = exp2f(m[g] - mn);  // 0 on the first position (m = -inf)
+                    const float pr = exp2f(s - mn);
                     l[g] = fmaf(l[g], corr, pr);
                     acc[g].x = fmaf(acc[g].x, corr, pr * vv[u].x);
                     acc[g].y = fmaf(acc[g].y, corr, pr * vv[u].y);
