@@ -249,8 +249,8 @@ int32_t l2b_attention(float* host_out, const float* host_q, const float* host_k,
  *   dev_q [n_heads][hs], dev_out [n_heads][hs]; dev_kcache, dev_vcache [n_kv_heads][seq_len][hs] f32, of which
  *   positions 0..n_pos-1 are attended.  The launch is asynchronous on `stream` (cudaStream_t; NULL = default).
  * Scratch for the partial results lives in one fixed device array inside the library (about 0.26 MiB per device), so:
- *   - limits: n_heads <= 128, head_size <= 128 (a multiple of 8), at most 16 splits; larger shapes are rejected with
- *     L2B_ERR_BAD_ARG;
+ *   - limits: n_heads <= 128, head_size <= 128 (a multiple of 8); larger shapes are rejected with L2B_ERR_BAD_ARG
+ *     (the scratch holds one partial result per cluster of blocks, at most four per head group);
  *   - the first call on each device resolves the array's address and must be made outside any stream capture;
  *   - the array is shared by all calls on a device and keeps the previous call's contents (the words that must be
  *     zero are cleared on `stream` before each launch); calls whose execution overlaps race on it, so callers
